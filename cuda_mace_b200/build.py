@@ -1,0 +1,86 @@
+"""Builds the C-ABI library (and the host-compiled math check library) in-tree with nvcc.
+
+    python -m cuda_mace_b200.build [--force] [-v]
+
+Output: cuda_mace_b200/lib/libcuda_mace_b200.so (sm_100a cubin + compute_100a PTX).  nvcc
+cross-compiles, so this runs on a machine without a GPU.  Sources are compiled one object per
+file in parallel and only rebuilt when they (or a header) changed.
+"""
+import argparse
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB_DIR = os.path.join(HERE, "lib")
+OBJ_DIR = os.path.join(HERE, "build")
+LIB_PATH = os.path.join(LIB_DIR, "libcuda_mace_b200.so")
+HOSTCHECK_PATH = os.path.join(LIB_DIR, "libcmace_hostcheck.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-lineinfo", "-std=c++17", "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC",
+]
+
+
+def _nvcc():
+    home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cand = os.path.join(home, "bin", "nvcc")
+    return cand if os.path.exists(cand) else "nvcc"
+
+
+def _newest(paths):
+    return max(os.path.getmtime(p) for p in paths)
+
+
+def build(force=False, verbose=False):
+    os.makedirs(LIB_DIR, exist_ok=True)
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    sources = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inc"))]
+    headers.append(os.path.join(HERE, "..", "include", "cuda_mace_b200.h"))
+    hdr_time = _newest(headers)
+
+    def compile_one(src):
+        obj = os.path.join(OBJ_DIR, src[:-3] + ".o")
+        srcp = os.path.join(CSRC, src)
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(srcp), hdr_time):
+            return obj, None
+        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", srcp, "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+        return obj, r.stderr
+    with ThreadPoolExecutor(max_workers=min(8, len(sources))) as ex:
+        results = list(ex.map(compile_one, sources))
+    objs = [o for o, _ in results]
+    if verbose:
+        for _, log in results:
+            if log:
+                print(log)
+    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < _newest(objs):
+        cmd = [_nvcc(), "-shared", "-o", LIB_PATH] + objs + ["-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    # host-compiled copy of the per-edge math, used by the CPU tests of the kernel formulas
+    hc_src = os.path.join(CSRC, "hostcheck.cpp")
+    if os.path.exists(hc_src) and (force or not os.path.exists(HOSTCHECK_PATH)
+                                   or os.path.getmtime(HOSTCHECK_PATH) < max(os.path.getmtime(hc_src), hdr_time)):
+        r = subprocess.run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", HOSTCHECK_PATH, hc_src],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"g++ failed for hostcheck.cpp:\n{r.stdout}\n{r.stderr}")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("-v", "--verbose", action="store_true")
+    a = ap.parse_args()
+    print(build(force=a.force, verbose=a.verbose))
+    sys.exit(0)

@@ -1,0 +1,188 @@
+/*
+ * C-ABI of the B200 (sm_100a) invariant-MACE energy+force hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the stream it is
+ * given, returns 0 on success or one of the CMACE_ERR_* codes, never throws and never
+ * allocates unless stated (only the *_plan_create calls allocate).  cmace_last_error()
+ * returns a thread-local description of the last failure.
+ *
+ * Each declaration names the entry point of the cuda-mace project it replaces (paths relative
+ * to that project).  Layouts are the reference's: node features X [N, C]; per-edge harmonics
+ * Y [16, E] (component-major); radial weights R [E, 4, C]; messages [N, 16, C]; all row-major
+ * and contiguous; indices int32; edges sorted by receiver.
+ * C (channels) must be a multiple of 32.  Offsets are 64-bit throughout.
+ */
+#ifndef CUDA_MACE_B200_H
+#define CUDA_MACE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CMACE_OK 0
+#define CMACE_ERR_ARG 1         /* bad size, null or misaligned pointer */
+#define CMACE_ERR_CUDA 2        /* a CUDA runtime call or launch failed */
+#define CMACE_ERR_UNSUPPORTED 3 /* shape outside what the kernels cover */
+
+typedef void *cmace_stream_t; /* a cudaStream_t */
+
+const char *cmace_last_error(void);
+int cmace_abi_version(void);
+
+/* ---- topology -------------------------------------------------------------------------
+ * Replaces jit_calculate_first_occurences (jit_wrappers/src/invariant_message_passing_wrapper.cpp:19-70,
+ * kernel cuda/src/invariant_message_passing_impl.cu:8-72).  row_ptr[n]..row_ptr[n+1] is the
+ * edge range of receiver n; receivers without edges get an empty range (the reference leaves
+ * theirs unwritten).  row_ptr has nnodes+1 entries. */
+int cmace_receiver_csr(const int32_t *receiver, int64_t nedges, int64_t nnodes, int32_t *row_ptr,
+                       cmace_stream_t stream);
+
+/* Sender-side ordering used by the node backward; stands in for the reference's N x N reverse-edge
+ * table (invariant_message_passing_wrapper.cpp:91-93, impl.cu:112-116).  perm lists the edge ids
+ * grouped by sender (stable), send_ptr [nnodes+1] the group bounds.  workspace must hold
+ * cmace_sender_order_workspace_bytes(nedges) bytes. */
+int64_t cmace_sender_order_workspace_bytes(int64_t nedges);
+int cmace_sender_order(const int32_t *sender, int64_t nedges, int64_t nnodes, int32_t *perm,
+                       int32_t *send_ptr, void *workspace, int64_t workspace_bytes,
+                       cmace_stream_t stream);
+
+/* Groups nodes by chemical element for ElementalLinear; stands in for the per-element
+ * torch::where + host sync of jit_elemental_linear (jit_wrappers/src/linear_wrapper.cpp:137-143).
+ * node_order [nnodes] lists node ids grouped by element, elem_start [nelements+1] the bounds;
+ * workspace as for cmace_sender_order with nedges = nnodes. */
+int cmace_group_by_element(const int32_t *elem, int64_t nnodes, int nelements, int32_t *node_order,
+                           int32_t *elem_start, void *workspace, int64_t workspace_bytes,
+                           cmace_stream_t stream);
+
+/* ---- per-edge basis: spherical harmonics (+ Bessel x cutoff) -----------------------------
+ * cmace_sph_* replace jit_spherical_harmonics / jit_spherical_harmonics_backward
+ * (jit_wrappers/src/spherical_harmonics_wrapper.cpp:15-137, kernels
+ * cuda/src/spherical_harmonics_impl.cu:21-334): xyz [E,3] -> Y [16,E], normalised input,
+ * e3nn component order, sqrt(4 pi) scaling.  The backward recomputes the derivatives from xyz
+ * instead of reading a saved dY [16,3,E].
+ * cmace_edge_basis_* additionally emit the radial basis B [E, nbessel] =
+ * sqrt(2/r_max) sin(n pi r/r_max)/r * polynomial cutoff(p), which the reference obtains from
+ * upstream MACE's radial_embedding before tabulating it (models/InvariantMACE.py:226-240).
+ * Pass B / gB = NULL to skip the radial part. */
+int cmace_sph_fwd_f32(const float *xyz, int64_t nedges, float *Y, cmace_stream_t stream);
+int cmace_sph_fwd_f64(const double *xyz, int64_t nedges, double *Y, cmace_stream_t stream);
+int cmace_sph_bwd_f32(const float *xyz, const float *gY, int64_t nedges, float *gxyz,
+                      cmace_stream_t stream);
+int cmace_sph_bwd_f64(const double *xyz, const double *gY, int64_t nedges, double *gxyz,
+                      cmace_stream_t stream);
+int cmace_edge_basis_fwd_f32(const float *xyz, int64_t nedges, double r_max, int nbessel, int p,
+                             float *Y, float *B, cmace_stream_t stream);
+int cmace_edge_basis_fwd_f64(const double *xyz, int64_t nedges, double r_max, int nbessel, int p,
+                             double *Y, double *B, cmace_stream_t stream);
+int cmace_edge_basis_bwd_f32(const float *xyz, const float *gY, const float *gB, int64_t nedges,
+                             double r_max, int nbessel, int p, float *gxyz, cmace_stream_t stream);
+int cmace_edge_basis_bwd_f64(const double *xyz, const double *gY, const double *gB, int64_t nedges,
+                             double r_max, int nbessel, int p, double *gxyz, cmace_stream_t stream);
+
+/* ---- cubic spline of the radial weights ----------------------------------------------------
+ * Replace jit_evaluate_spline / jit_backward_spline (jit_wrappers/src/cubic_spline_wrapper.cpp:14-153,
+ * kernels cuda/src/cubic_spline_impl.cu:5-107).  coeffs [nintervals, 4, noutputs]; R [E, noutputs];
+ * R is zero for r > r_max.  The backward recomputes dR/dr instead of reading a saved table. */
+int cmace_spline_fwd_f32(const float *r, const float *r_knots, const float *coeffs, int64_t nedges,
+                         int nintervals, int noutputs, double r_width, double r_max, float *R,
+                         cmace_stream_t stream);
+int cmace_spline_fwd_f64(const double *r, const double *r_knots, const double *coeffs,
+                         int64_t nedges, int nintervals, int noutputs, double r_width, double r_max,
+                         double *R, cmace_stream_t stream);
+int cmace_spline_bwd_f32(const float *r, const float *r_knots, const float *coeffs, const float *gR,
+                         int64_t nedges, int nintervals, int noutputs, double r_width, double r_max,
+                         float *gr, cmace_stream_t stream);
+int cmace_spline_bwd_f64(const double *r, const double *r_knots, const double *coeffs,
+                         const double *gR, int64_t nedges, int nintervals, int noutputs,
+                         double r_width, double r_max, double *gr, cmace_stream_t stream);
+
+/* ---- invariant message passing ------------------------------------------------------------
+ * cmace_imp_fwd_* replace jit_forward_message_passing (invariant_message_passing_wrapper.cpp:72-155,
+ * kernel impl.cu:74-165): out[i,lm,c] = sum_{e in row i} X[sender[e],c] * Y[lm,e] * R[e,l(lm),c].
+ * Every row of out is written (zeros for receivers without edges).
+ * cmace_imp_bwd_edge_* + cmace_imp_bwd_node_* replace jit_backward_message_passing
+ * (wrapper :157-284, kernels impl.cu:167-399).  The edge pass writes gradR [E,4,C], gradY [16,E]
+ * and, when T != NULL, the per-edge sender contribution T [E,C]; the node pass sums T over each
+ * sender's group into gradX [N,C].  A warp covers 32*VEC channels (VEC = 4, 2 or 1 scalars per
+ * lane, the widest that divides C/32 within 16 bytes); when C needs several such chunks (e.g.
+ * float64 with C = 128) each chunk writes its own partial of gradY into gradY_partial, a scratch
+ * of cmace_imp_bwd_scratch_elems(...) scalars, and a second small kernel sums them.  Pass NULL
+ * when that query returns 0. */
+int cmace_imp_fwd_f32(const float *X, const float *Y, const float *R, const int32_t *sender,
+                      const int32_t *row_ptr, int64_t nnodes, int64_t nedges, int channels,
+                      float *out, cmace_stream_t stream);
+int cmace_imp_fwd_f64(const double *X, const double *Y, const double *R, const int32_t *sender,
+                      const int32_t *row_ptr, int64_t nnodes, int64_t nedges, int channels,
+                      double *out, cmace_stream_t stream);
+int64_t cmace_imp_bwd_scratch_elems(int64_t nedges, int channels, int is_f64);
+int cmace_imp_bwd_edge_f32(const float *X, const float *Y, const float *R, const float *G,
+                           const int32_t *sender, const int32_t *row_ptr, int64_t nnodes,
+                           int64_t nedges, int channels, float *gradR, float *gradY, float *T,
+                           float *gradY_partial, cmace_stream_t stream);
+int cmace_imp_bwd_edge_f64(const double *X, const double *Y, const double *R, const double *G,
+                           const int32_t *sender, const int32_t *row_ptr, int64_t nnodes,
+                           int64_t nedges, int channels, double *gradR, double *gradY, double *T,
+                           double *gradY_partial, cmace_stream_t stream);
+int cmace_imp_bwd_node_f32(const float *T, const int32_t *perm, const int32_t *send_ptr,
+                           int64_t nnodes, int channels, float *gradX, cmace_stream_t stream);
+int cmace_imp_bwd_node_f64(const double *T, const int32_t *perm, const int32_t *send_ptr,
+                           int64_t nnodes, int channels, double *gradX, cmace_stream_t stream);
+
+/* ---- Linear / ElementalLinear -------------------------------------------------------------
+ * Replace jit_linear and jit_elemental_linear (jit_wrappers/src/linear_wrapper.cpp:23-191, kernels
+ * cuda/src/linear_impl.cu:16-255): out[n, l^2+m, :] = X[n, l^2+m, :] @ W[z_n, l] / sqrt(K).
+ * X [N,16,K]; W [nelements,4,K,Nout]; out [N,16,Nout].  For Linear pass nelements = 1 and
+ * node_order = elem_start = NULL.  For ElementalLinear pass the outputs of
+ * cmace_group_by_element.  The backward of both is the same call with the transposed weights,
+ * as in the reference (src/linear.cpp:29-44, :77-93).  One launch, no host synchronisation. */
+int cmace_linear_f32(const float *X, const float *W, const int32_t *node_order,
+                     const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
+                     float *out, cmace_stream_t stream);
+int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order,
+                     const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
+                     double *out, cmace_stream_t stream);
+
+/* ---- symmetric contraction (correlation 3, invariant output) ------------------------------
+ * Replace jit_symmetric_contraction_forward / _backward
+ * (jit_wrappers/src/symmetric_contraction_wrapper.cpp:15-205, kernels
+ * cuda/src/symmetric_contraction_impl.cu:6-234).  The plan is built once from HOST copies of the
+ * reference's sparse U tables (layout of cuda_mace/ops/symmetric_contraction.py:91-187; the values
+ * are taken as double so that a float64 caller keeps full precision, a float32 table is simply
+ * widened); it symmetrises them into a list of monomial terms kept in device memory.
+ * forward: out [N,C] (the reference returns the same data shaped [N,1,C]);
+ * backward: gradX[n,i,c] = gout[n,c] * d out[n,c] / d X[n,i,c], recomputed from X (the reference
+ * reads a saved [N,16,C] derivative written by its forward).
+ * X [N,16,C]; atom_types [N] int32; W3 [nelements,w3,C], W2 [nelements,w2,C], W1 [nelements,w1,C]
+ * (slice of the output irrep 0 of the reference's [nlout,Z,w,C] buffers). */
+typedef struct cmace_symcon_plan cmace_symcon_plan;
+int cmace_symcon_plan_create(int u3_max_nonzero, const int16_t *u3_num_nonzero /*[16,16]*/,
+                             const int32_t *u3_indices /*[maxnz,16,16]*/,
+                             const double *u3_values /*[maxnz,16,16]*/,
+                             const int16_t *u2_num_nonzero /*[16,16]*/,
+                             const int16_t *u2_indices /*[16,16]*/,
+                             const double *u2_values /*[16,16]*/, int w3_size, int w2_size,
+                             int w1_size, cmace_symcon_plan **plan);
+void cmace_symcon_plan_destroy(cmace_symcon_plan *plan);
+int cmace_symcon_plan_nterms(const cmace_symcon_plan *plan);
+int cmace_symcon_plan_nclasses(const cmace_symcon_plan *plan);
+int cmace_symcon_fwd_f32(const cmace_symcon_plan *plan, const float *X, const int32_t *atom_types,
+                         const float *W3, const float *W2, const float *W1, int nelements,
+                         int64_t nnodes, int channels, float *out, cmace_stream_t stream);
+int cmace_symcon_fwd_f64(const cmace_symcon_plan *plan, const double *X, const int32_t *atom_types,
+                         const double *W3, const double *W2, const double *W1, int nelements,
+                         int64_t nnodes, int channels, double *out, cmace_stream_t stream);
+int cmace_symcon_bwd_f32(const cmace_symcon_plan *plan, const float *X, const int32_t *atom_types,
+                         const float *W3, const float *W2, const float *W1, const float *gout,
+                         int nelements, int64_t nnodes, int channels, float *gradX,
+                         cmace_stream_t stream);
+int cmace_symcon_bwd_f64(const cmace_symcon_plan *plan, const double *X, const int32_t *atom_types,
+                         const double *W3, const double *W2, const double *W1, const double *gout,
+                         int nelements, int64_t nnodes, int channels, double *gradX,
+                         cmace_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,145 @@
+"""Float64 CPU restatement of the invariant-MACE energy+force evaluation (test infrastructure).
+
+Wiring follows cuda_mace/models/InvariantMACE.py:
+  * edge convention  receiver = edge_index[0], sender = edge_index[1]      (:99-100, :141-142)
+  * layer 0  linear_up -> message passing -> Linear / avg_num_neighbors -> ElementalLinear, no residual  (:90-121)
+  * layer 1  sc = skip(node_feats, node_attrs); linear_up -> message passing -> Linear / avg_num_neighbors (:136-165)
+  * product  symmetric contraction -> linear (+ sc)                         (:30-38, :216-224, :330)
+  * readouts in float64, scale-shift, scatter to energy, forces = -dE/dpositions (:335-364)
+
+The parts the reference borrows from upstream MACE / e3nn modules (Bessel basis with polynomial
+cutoff, radial multilayer perceptron, o3.Linear 1/sqrt(fan_in) normalisation, second-moment
+normalised SiLU, FullyConnectedTensorProduct normalisation, readout blocks, scale-shift) are
+restated from their published definitions; upstream itself is not installable here, so those
+conventions are UNPINNED against upstream.  Instead of the reference's cubic-spline tabulation
+of the radial weights (InvariantMACE.py:226-240) the exact radial function is evaluated, as the
+float64 1e-10 parity target requires; `radial="spline"` reproduces the tabulated variant.
+"""
+import math
+
+import torch
+
+from . import ops
+from .sh import real_sh_l3
+
+# second-moment normalisation of SiLU, 1/sqrt(E_{x~N(0,1)}[silu(x)^2]), by Gauss-Hermite quadrature
+# (e3nn's normalize2mom estimates the same constant by sampling)
+SILU_2MOM = 1.676532470331092
+
+
+def silu_n(x):
+    return torch.nn.functional.silu(x) * SILU_2MOM
+
+
+def bessel_basis(r, r_max, num_basis=8):
+    """sqrt(2/r_max) * sin(n pi r / r_max) / r, n = 1..num_basis.  r [E] -> [E, num_basis]."""
+    n = torch.arange(1, num_basis + 1, dtype=r.dtype)
+    return math.sqrt(2.0 / r_max) * torch.sin(n * math.pi / r_max * r[:, None]) / r[:, None]
+
+
+def polynomial_cutoff(r, r_max, p=5):
+    """1 - (p+1)(p+2)/2 x^p + p(p+2) x^(p+1) - p(p+1)/2 x^(p+2) for x = r/r_max < 1, else 0."""
+    x = r / r_max
+    env = (
+        1.0
+        - (p + 1.0) * (p + 2.0) / 2.0 * x**p
+        + p * (p + 2.0) * x ** (p + 1)
+        - p * (p + 1.0) / 2.0 * x ** (p + 2)
+    )
+    return env * (x < 1.0)
+
+
+def radial_embedding(r, r_max, num_basis=8, p=5):
+    return bessel_basis(r, r_max, num_basis) * polynomial_cutoff(r, r_max, p)[:, None]
+
+
+def radial_mlp(b, weights):
+    """e3nn FullyConnectedNet: h <- silu_n(h @ W / sqrt(fan_in)); last layer linear."""
+    h = b
+    for i, W in enumerate(weights):
+        h = h @ W / math.sqrt(W.shape[0])
+        if i + 1 < len(weights):
+            h = silu_n(h)
+    return h
+
+
+def edge_geometry(positions, edge_index, shifts):
+    """vectors = positions[edge_index[1]] - positions[edge_index[0]] + shifts; lengths."""
+    vec = positions[edge_index[1].long()] - positions[edge_index[0].long()] + shifts
+    return vec, vec.norm(dim=-1)
+
+
+def node_energies(params, U, positions, node_attrs, edge_index, shifts, exchange=None,
+                  radial="exact"):
+    """Per-node interaction energies [N] (before the sum); differentiable wrt positions.
+
+    `exchange(h, layer)` is an optional hook applied to the node features that enter message
+    passing of `layer` (used by the domain-decomposition tests to refresh ghost rows).
+    """
+    U3, U2, U1 = U
+    r_max = float(params["r_max"])
+    N, Z = node_attrs.shape
+    C = params["W_embed"].shape[1]
+    recv, send = edge_index[0], edge_index[1]
+    z = node_attrs.argmax(dim=-1)
+
+    vec, length = edge_geometry(positions, edge_index, shifts)
+    Y = real_sh_l3(vec)  # [16, E]
+    if radial == "exact":
+        bess = radial_embedding(length, r_max)  # [E, 8]
+
+    h = node_attrs @ params["W_embed"] / math.sqrt(Z)  # [N, C]
+    es = []
+    for t in range(2):
+        P = params["layers"][t]
+        if radial == "exact":
+            R = radial_mlp(bess, P["W_radial"]).view(-1, 4, C)
+        else:
+            R = ops.cubic_spline_eval(length, P["spline_knots"], P["spline_coeffs"],
+                                      P["spline_h"], r_max).view(-1, 4, C)
+        if exchange is not None:
+            h = exchange(h, t)
+        sc = None
+        if t == 1:
+            # FullyConnectedTensorProduct(C x0e, Z x0e -> C x0e), 1/sqrt(C*Z)
+            sc = torch.einsum("nc,nz,czo->no", h, node_attrs, P["W_sc"]) / math.sqrt(C * Z)
+        up = h @ P["W_up"] / math.sqrt(C)
+        m = ops.invariant_message_passing(up, Y, R, send, recv, N)
+        m = ops.linear(m, P["W_lin"]) / P["avg_num_neighbors"]
+        if t == 0:
+            # weights [Z,4,C,C] already carry the 1/sqrt(Z) of element_linear_to_cuda
+            m = ops.elemental_linear(m, P["W_skip"] / math.sqrt(Z), node_attrs)
+        b = ops.symmetric_contraction_chunked(m, z, U3, U2, U1, P["W3"], P["W2"], P["W1"])[:, 0, :]
+        h = b @ P["W_prod"] / math.sqrt(C)
+        if sc is not None:
+            h = h + sc
+        if t == 0:
+            es.append((h @ P["W_readout"] / math.sqrt(C))[:, 0])
+        else:
+            hid = silu_n(h @ P["W_readout1"] / math.sqrt(C))
+            es.append((hid @ P["W_readout2"] / math.sqrt(P["W_readout2"].shape[0]))[:, 0])
+    return params["scale"] * (es[0] + es[1]) + params["shift"]
+
+
+def energy_and_forces(params, U, positions, node_attrs, edge_index, shifts, radial="exact"):
+    """Returns (total energy scalar, interaction energy, forces [N,3]) in float64."""
+    pos = positions.detach().clone().requires_grad_(True)
+    e_nodes = node_energies(params, U, pos, node_attrs, edge_index, shifts, radial=radial)
+    e_inter = e_nodes.sum()
+    (g,) = torch.autograd.grad(e_inter, pos)
+    e0 = (node_attrs @ params["atomic_energies"]).sum()
+    return (e0 + e_inter).detach(), e_inter.detach(), -g
+
+
+def add_spline_tables(params, nknots=256):
+    """Tabulates the radial weights like InvariantMACE.py:226-240 (256 knots on [1e-12, r_max+1])."""
+    r_max = float(params["r_max"])
+    r = torch.linspace(1e-12, r_max + 1.0, nknots, dtype=torch.float64)
+    h = float(r[1] - r[0])
+    bess = radial_embedding(r, r_max)
+    for P in params["layers"]:
+        R = radial_mlp(bess, P["W_radial"])
+        P["spline_knots"] = r
+        P["spline_h"] = h
+        P["spline_coeffs"] = ops.cubic_spline_coefficients(r, R, h)
+    return params

@@ -1,0 +1,571 @@
+"""Host-side mirror of the reference's operator layer (cuda_mace/ops/*.py and the autograd
+Functions of cuda_mace/src/*.cpp) on top of the C-ABI library.
+
+Each class keeps the reference's ``forward`` signature and autograd contract:
+
+* ``InvariantMessagePassingTP.forward(X, Y, radial, sender_list, receiver_list, nnodes)``
+  (src/invariant_message_passing.cpp:73-90) -> [N,16,C]; grads for X, Y, radial.
+* ``Linear.forward(X, W, W_T)``, ``ElementalLinear.forward(X, W, W_T, one_hot)``
+  (src/linear.cpp:105-138); grad for X only, computed with the transposed weights.
+* ``SymmetricContraction.forward(X, atom_types, <sparse U tables>, W3, W2, W1, sizes)``
+  (src/symmetric_contraction.cpp:124-158) -> [N,1,C]; grad for X only.
+* ``SphericalHarmonics.forward(xyz)`` (src/spherical_harmonics.cpp:52-69) -> [16,E].
+* ``CubicSpline.forward(r, r_knots, coeffs, r_width, r_max)`` (src/cubic_spline.cpp:54-68) -> [E,F].
+
+All tensors must live on a CUDA device; float32 and float64 are supported everywhere (the
+reference's Linear is float32 only).  Kernels run on torch's current stream.  There is no
+fallback: a CPU tensor raises.
+"""
+import math
+from collections import OrderedDict
+
+import torch
+
+from . import _abi
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _suffix(t):
+    if t.dtype == torch.float32:
+        return "f32"
+    if t.dtype == torch.float64:
+        return "f64"
+    raise TypeError(f"float32 or float64 expected, got {t.dtype}")
+
+
+def _check_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("cuda_mace_b200 operators need CUDA tensors (there is no CPU path)")
+
+
+class _RefCache:
+    """Small LRU keyed by the identity of live tensors.  The cached entry keeps a reference to its
+    key tensors, so their storage cannot be recycled for other data while the entry lives, and
+    in-place edits are caught by the version counter."""
+
+    def __init__(self, size=8):
+        self.size = size
+        self.entries = OrderedDict()
+
+    @staticmethod
+    def key(*tensors):
+        return tuple((t.data_ptr(), tuple(t.shape), t.dtype, t._version) for t in tensors)
+
+    def get(self, key):
+        hit = self.entries.get(key)
+        if hit is not None:
+            self.entries.move_to_end(key)
+            return hit[1]
+        return None
+
+    def put(self, key, tensors, value):
+        self.entries[key] = (tensors, value)
+        while len(self.entries) > self.size:
+            self.entries.popitem(last=False)
+        return value
+
+
+# --------------------------------------------------------------------------------------
+# edge topology
+# --------------------------------------------------------------------------------------
+class EdgeTopology:
+    """Receiver CSR and (lazily) the sender-grouped edge order of one neighbour list.
+
+    Replaces the per-call first-occurrence kernel and the N x N reverse-edge table of the
+    reference (jit_wrappers/src/invariant_message_passing_wrapper.cpp:19-70, :91-93).  Build it
+    once per neighbour list and reuse it for every layer and step.
+    """
+
+    def __init__(self, sender, receiver, nnodes, nsenders=None):
+        _check_cuda(sender, receiver)
+        self.sender = sender.to(torch.int32).contiguous()
+        self.receiver = receiver.to(torch.int32).contiguous()
+        self.nnodes = int(nnodes)  # receiver rows
+        # rows of the node-feature matrix the senders index; larger than nnodes when ghost atoms send
+        self.nsenders = self.nnodes if nsenders is None else int(nsenders)
+        self.nedges = int(self.sender.numel())
+        self.row_ptr = torch.empty(self.nnodes + 1, dtype=torch.int32, device=sender.device)
+        _abi.call("cmace_receiver_csr", _ptr(self.receiver), self.nedges, self.nnodes,
+                  _ptr(self.row_ptr), _stream())
+        self._perm = None
+        self._send_ptr = None
+
+    def sender_order(self):
+        if self._perm is None:
+            dev = self.sender.device
+            nbytes = _abi.call("cmace_sender_order_workspace_bytes", self.nedges)
+            ws = torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=dev)
+            perm = torch.empty(max(self.nedges, 1), dtype=torch.int32, device=dev)
+            send_ptr = torch.empty(self.nsenders + 1, dtype=torch.int32, device=dev)
+            _abi.call("cmace_sender_order", _ptr(self.sender), self.nedges, self.nsenders, _ptr(perm),
+                      _ptr(send_ptr), _ptr(ws), int(nbytes), _stream())
+            self._perm, self._send_ptr = perm, send_ptr
+        return self._perm, self._send_ptr
+
+
+_topology_cache = _RefCache(8)
+
+
+def topology_for(sender, receiver, nnodes, nsenders=None):
+    key = _RefCache.key(sender, receiver) + (int(nnodes), nsenders)
+    topo = _topology_cache.get(key)
+    if topo is None:
+        topo = _topology_cache.put(key, (sender, receiver), EdgeTopology(sender, receiver, nnodes, nsenders))
+    return topo
+
+
+# --------------------------------------------------------------------------------------
+# invariant message passing
+# --------------------------------------------------------------------------------------
+class _IMPFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, Y, radial, topo):
+        X, Y, radial = X.contiguous(), Y.contiguous(), radial.contiguous()
+        N, C = topo.nnodes, X.shape[1]
+        E = topo.nedges
+        if X.dim() != 2 or X.shape[0] != topo.nsenders or Y.shape != (16, E) or radial.shape != (E, 4, C):
+            raise RuntimeError(f"shape mismatch: X {tuple(X.shape)}, Y {tuple(Y.shape)}, radial "
+                               f"{tuple(radial.shape)} for {N} nodes and {E} edges")
+        if Y.dtype != X.dtype or radial.dtype != X.dtype:
+            raise TypeError("X, Y and radial must have the same dtype")
+        out = torch.empty(N, 16, C, dtype=X.dtype, device=X.device)
+        _abi.call("cmace_imp_fwd_" + _suffix(X), _ptr(X), _ptr(Y), _ptr(radial), _ptr(topo.sender),
+                  _ptr(topo.row_ptr), N, E, C, _ptr(out), _stream())
+        ctx.save_for_backward(X, Y, radial)
+        ctx.topo = topo
+        return out
+
+    @staticmethod
+    def backward(ctx, G):
+        X, Y, radial = ctx.saved_tensors
+        topo = ctx.topo
+        G = G.contiguous()
+        N, C, E = topo.nnodes, X.shape[1], topo.nedges
+        need_x = ctx.needs_input_grad[0]
+        gradR = torch.empty_like(radial)
+        gradY = torch.empty_like(Y)
+        T = torch.empty(E, C, dtype=X.dtype, device=X.device) if need_x else None
+        nscratch = _abi.call("cmace_imp_bwd_scratch_elems", E, C, 1 if X.dtype == torch.float64 else 0)
+        scratch = torch.empty(nscratch, dtype=X.dtype, device=X.device) if nscratch > 0 else None
+        _abi.call("cmace_imp_bwd_edge_" + _suffix(X), _ptr(X), _ptr(Y), _ptr(radial), _ptr(G),
+                  _ptr(topo.sender), _ptr(topo.row_ptr), N, E, C, _ptr(gradR), _ptr(gradY), _ptr(T),
+                  _ptr(scratch), _stream())
+        gradX = None
+        if need_x:
+            perm, send_ptr = topo.sender_order()
+            gradX = torch.empty(topo.nsenders, C, dtype=X.dtype, device=X.device)
+            _abi.call("cmace_imp_bwd_node_" + _suffix(X), _ptr(T), _ptr(perm), _ptr(send_ptr), topo.nsenders, C,
+                      _ptr(gradX), _stream())
+        return gradX, gradY, gradR, None
+
+
+class InvariantMessagePassingTP(torch.nn.Module):
+    """out[i,lm,c] = sum_{e: receiver(e)=i} X[sender(e),c] * Y[lm,e] * radial[e,l(lm),c].
+
+    Same call as cuda_mace/ops/invariant_message_passing.py:8-22: X [N,C], Y [16,E], radial [E,4,C],
+    int32 sender/receiver lists sorted by receiver.  Unlike the reference, receivers without edges
+    get zero rows, any neighbour count per receiver is allowed, and the list need not be symmetric.
+    """
+
+    def forward(self, node_feats, edge_attrs, tp_weights, sender_list, receiver_list, nnodes, topology=None):
+        _check_cuda(node_feats, edge_attrs, tp_weights, sender_list, receiver_list)
+        topo = topology if topology is not None else topology_for(sender_list, receiver_list, int(nnodes),
+                                                                  int(node_feats.shape[0]))
+        return _IMPFunction.apply(node_feats, edge_attrs, tp_weights, topo)
+
+
+# --------------------------------------------------------------------------------------
+# Linear / ElementalLinear
+# --------------------------------------------------------------------------------------
+def _linear_call(X, W, node_order, elem_start, nelements):
+    X = X.contiguous()
+    N, K = X.shape[0], X.shape[2]
+    Nout = W.shape[-1]
+    if X.shape[1] != 16 or W.shape[-2] != K or W.numel() != nelements * 4 * K * Nout:
+        raise RuntimeError(f"shape mismatch: X {tuple(X.shape)}, W {tuple(W.shape)}")
+    if W.dtype != X.dtype:
+        raise TypeError("X and W must have the same dtype")
+    out = torch.empty(N, 16, Nout, dtype=X.dtype, device=X.device)
+    _abi.call("cmace_linear_" + _suffix(X), _ptr(X), _ptr(W.contiguous()), _ptr(node_order), _ptr(elem_start),
+              nelements, N, K, Nout, _ptr(out), _stream())
+    return out
+
+
+class _LinearFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, W, W_T, node_order, elem_start, nelements):
+        ctx.save_for_backward(W_T)
+        ctx.grouping = (node_order, elem_start, nelements)
+        return _linear_call(X, W, node_order, elem_start, nelements)
+
+    @staticmethod
+    def backward(ctx, G):
+        (W_T,) = ctx.saved_tensors
+        node_order, elem_start, nelements = ctx.grouping
+        return _linear_call(G, W_T, node_order, elem_start, nelements), None, None, None, None, None
+
+
+def linear_forward(X, W, W_T):
+    """torch.classes.linear_wmma.Linear.forward equivalent: W [4,K,N], W_T [4,N,K]."""
+    _check_cuda(X, W, W_T)
+    return _LinearFunction.apply(X, W, W_T, None, None, 1)
+
+
+_grouping_cache = _RefCache(8)
+
+
+def group_by_element(elem, nelements):
+    """(node_order, elem_start) of an int32 element index per node, on the device, no host sync."""
+    key = _RefCache.key(elem) + (int(nelements),)
+    hit = _grouping_cache.get(key)
+    if hit is not None:
+        return hit
+    n = elem.numel()
+    dev = elem.device
+    nbytes = _abi.call("cmace_sender_order_workspace_bytes", n)
+    ws = torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=dev)
+    order = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    start = torch.empty(nelements + 1, dtype=torch.int32, device=dev)
+    _abi.call("cmace_group_by_element", _ptr(elem), n, int(nelements), _ptr(order), _ptr(start), _ptr(ws),
+              int(nbytes), _stream())
+    return _grouping_cache.put(key, (elem,), (order, start))
+
+
+def elemental_linear_forward(X, W, W_T, one_hot_or_index):
+    """torch.classes.linear_wmma.ElementalLinear.forward equivalent: W [Z,4,K,N]; the last argument
+    is the one-hot node attribute matrix [N,Z] of the reference or an int32 element index [N]."""
+    _check_cuda(X, W, W_T, one_hot_or_index)
+    Z = W.shape[0]
+    if one_hot_or_index.dim() == 2:
+        hit = _onehot_cache.get(_RefCache.key(one_hot_or_index))
+        if hit is None:
+            hit = _onehot_cache.put(_RefCache.key(one_hot_or_index), (one_hot_or_index,),
+                                    one_hot_or_index.argmax(dim=-1).to(torch.int32))
+        elem = hit
+    else:
+        elem = one_hot_or_index.to(torch.int32)
+    if Z == 1:
+        return _LinearFunction.apply(X, W, W_T, None, None, 1)
+    order, start = group_by_element(elem, Z)
+    return _LinearFunction.apply(X, W, W_T, order, start, Z)
+
+
+_onehot_cache = _RefCache(8)
+
+
+class Linear(torch.nn.Module):
+    """Per-l channel mixing of [N,16,K] features, weights [4,K,N] (one matrix per l).
+
+    Mirrors cuda_mace/ops/linear.py:6-54; the e3nn weight split is done by the caller because e3nn
+    is not a dependency: pass the four per-l matrices.  `scale` is folded into the weights (used
+    for the 1/avg_num_neighbors of models/InvariantMACE.py:114)."""
+
+    def __init__(self, weights, scale=1.0):
+        super().__init__()
+        w = (weights * scale).contiguous()
+        self.register_buffer("weights", w)
+        self.register_buffer("weights_transposed", w.transpose(-1, -2).contiguous())
+
+    def forward(self, x):
+        return linear_forward(x, self.weights, self.weights_transposed)
+
+
+class ElementalLinear(torch.nn.Module):
+    """Element-dependent per-l channel mixing, weights [Z,4,K,N] (cuda_mace/ops/linear.py:57-108)."""
+
+    def __init__(self, weights):
+        super().__init__()
+        w = weights.contiguous()
+        self.register_buffer("weights", w)
+        self.register_buffer("weights_transposed", w.transpose(-1, -2).contiguous())
+
+    def forward(self, x, y):
+        return elemental_linear_forward(x, self.weights, self.weights_transposed, y)
+
+
+# --------------------------------------------------------------------------------------
+# symmetric contraction
+# --------------------------------------------------------------------------------------
+class _Plan:
+    def __init__(self, handle):
+        self.handle = handle
+
+    def __del__(self):
+        try:
+            _abi.call("cmace_symcon_plan_destroy", self.handle)
+        except Exception:
+            pass
+
+
+def make_plan(u3_max, U3_num_nonzero, U3_indices, U3_values, U2_num_nonzero, U2_indices, U2_values,
+              w3, w2, w1):
+    """Builds the device program from (host copies of) the reference's sparse tables."""
+    import ctypes
+
+    n3 = U3_num_nonzero.detach().to("cpu", torch.int16).contiguous()
+    i3 = U3_indices.detach().to("cpu", torch.int32).contiguous()
+    v3 = U3_values.detach().to("cpu", torch.float64).contiguous()
+    n2 = U2_num_nonzero.detach().to("cpu", torch.int16).contiguous()
+    i2 = U2_indices.detach().to("cpu", torch.int16).contiguous()
+    v2 = U2_values.detach().to("cpu", torch.float64).contiguous()
+    handle = ctypes.c_void_p()
+    _abi.call("cmace_symcon_plan_create", int(u3_max), _ptr(n3), _ptr(i3), _ptr(v3), _ptr(n2), _ptr(i2),
+              _ptr(v2), int(w3), int(w2), int(w1), ctypes.byref(handle))
+    return _Plan(handle)
+
+
+class _SymConFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, atom_types, W3, W2, W1, plan, nelements):
+        X = X.contiguous()
+        N, C = X.shape[0], X.shape[2]
+        out = torch.empty(N, 1, C, dtype=X.dtype, device=X.device)
+        _abi.call("cmace_symcon_fwd_" + _suffix(X), plan.handle, _ptr(X), _ptr(atom_types), _ptr(W3), _ptr(W2),
+                  _ptr(W1), nelements, N, C, _ptr(out), _stream())
+        ctx.save_for_backward(X, atom_types, W3, W2, W1)
+        ctx.plan, ctx.nelements = plan, nelements
+        return out
+
+    @staticmethod
+    def backward(ctx, G):
+        X, atom_types, W3, W2, W1 = ctx.saved_tensors
+        G = G.contiguous()
+        N, C = X.shape[0], X.shape[2]
+        gradX = torch.empty_like(X)
+        _abi.call("cmace_symcon_bwd_" + _suffix(X), ctx.plan.handle, _ptr(X), _ptr(atom_types), _ptr(W3),
+                  _ptr(W2), _ptr(W1), _ptr(G), ctx.nelements, N, C, _ptr(gradX), _stream())
+        return gradX, None, None, None, None, None, None
+
+
+_plan_cache = _RefCache(4)
+
+
+def symmetric_contraction_forward(X, atom_types, U3_max_nonsparse, U3_num_nonzero, U3_indices, U3_values,
+                                  U2_num_nonzero, U2_indices, U2_values, U1_num_nonzero, U1_index, W3, W2, W1,
+                                  W3_size, W2_size, W1_size, plan=None):
+    """torch.classes.symm_contract.SymmetricContraction.forward equivalent (same argument list).
+
+    W3/W2/W1 may be the reference's [nlout, Z, w, C] buffers (output irrep 0 is used, as in
+    symmetric_contraction_impl.cu:64-76) or plain [Z, w, C].  The device program is built from the
+    tables on first use and cached per table set."""
+    _check_cuda(X, atom_types, W3, W2, W1)
+    if plan is None:
+        key = _RefCache.key(U3_indices, U3_values, U2_indices, U2_values)
+        plan = _plan_cache.get(key)
+        if plan is None:
+            plan = _plan_cache.put(
+                key, (U3_indices, U3_values, U2_indices, U2_values),
+                make_plan(U3_max_nonsparse, U3_num_nonzero, U3_indices, U3_values, U2_num_nonzero, U2_indices,
+                          U2_values, W3_size, W2_size, W1_size))
+    W3, W2, W1 = [w[0] if w.dim() == 4 else w for w in (W3, W2, W1)]
+    if W3.dtype != X.dtype:
+        raise TypeError("X and the weights must have the same dtype")
+    if W3.shape[1] != W3_size or W2.shape[1] != W2_size or W1.shape[1] != W1_size:
+        raise RuntimeError("weight buffers do not match W3_size/W2_size/W1_size")
+    return _SymConFunction.apply(X, atom_types.to(torch.int32).contiguous(), W3.contiguous(), W2.contiguous(),
+                                 W1.contiguous(), plan, W3.shape[0])
+
+
+def pack_sparse_u(U3, U2, U1):
+    """Sparse U tables in the reference's layout (cuda_mace/ops/symmetric_contraction.py:91-187) from
+    dense tensors U3 [16,16,16,P3], U2 [16,16,P2], U1 [16,P1].  The values are returned in the dense
+    tensors' dtype (the reference stores float32); the packed int32 carries, per (i,j) and per k-th
+    non-zero, bits 7:0 the path, 15:8 k, 23:16 / 31:24 the partner paths the reference's gradient uses."""
+    U3c, U2c, U1c = U3.cpu(), U2.cpu(), U1.cpu()
+    nz3 = U3c != 0
+    n3 = nz3.sum(dim=(2, 3)).to(torch.int16)
+    maxnz = int(n3.max())
+    idx3 = torch.zeros(maxnz, 16, 16, dtype=torch.int32)
+    val3 = torch.zeros(maxnz, 16, 16, dtype=U3c.dtype)
+    for i in range(16):
+        for j in range(16):
+            k1, p1 = torch.where(nz3[i, j])
+            _, p2 = torch.where(nz3[j, i])
+            _, p3 = torch.where(nz3[j, :, i, :])
+            for t in range(k1.shape[0]):
+                lo = (int(k1[t]) << 8) | int(p1[t])
+                hi = ((int(p2[t]) << 8) | int(p3[t])) if t < p2.shape[0] and t < p3.shape[0] else 0
+                idx3[t, i, j] = (hi << 16) | lo
+                val3[t, i, j] = U3c[i, j, k1[t], p1[t]]
+    nz2 = U2c != 0
+    n2 = nz2.sum(dim=2).to(torch.int16)
+    idx2 = torch.zeros(16, 16, dtype=torch.int16)
+    val2 = torch.zeros(16, 16, dtype=U2c.dtype)
+    for i in range(16):
+        for j in range(16):
+            (p,) = torch.where(nz2[i, j])
+            if p.shape[0] > 0:
+                idx2[i, j] = int(p[0])
+                val2[i, j] = U2c[i, j, p[0]]
+    n1 = (U1c != 0).any(dim=1).to(torch.int16)
+    idx1 = (U1c != 0).to(torch.int16).argmax(dim=1).to(torch.int16)
+    return maxnz, n3, idx3, val3, n2, idx2, val2, n1, idx1
+
+
+class SymmetricContraction(torch.nn.Module):
+    """Correlation-3, L=0 symmetric contraction with per-element weights.
+
+    Mirrors cuda_mace/ops/symmetric_contraction.py:6-232: keeps the sparse U tables and the weight
+    buffers [1, Z, w, C] as registered buffers and forwards them with the reference's argument list.
+    Built from dense U tensors and weights [Z, P, C] because upstream's SymmetricContraction module
+    and U_matrix_real are not dependencies here (see cuda_mace_b200.cg.u_matrices)."""
+
+    def __init__(self, U3, U2, U1, W3, W2, W1):
+        super().__init__()
+        maxnz, n3, i3, v3, n2, i2, v2, n1, i1 = pack_sparse_u(U3, U2, U1)
+        self.u3_max_nonsparse = maxnz
+        for name, t in (("U3_num_nonsparse", n3), ("U3_indices", i3), ("U3_values", v3),
+                        ("U2_num_nonsparse", n2), ("U2_indices", i2), ("U2_values", v2),
+                        ("U1_num_values", n1), ("U1_index", i1)):
+            self.register_buffer(name, t)
+        self.register_buffer("weights_3", W3[None].contiguous())
+        self.register_buffer("weights_2", W2[None].contiguous())
+        self.register_buffer("weights_1", W1[None].contiguous())
+        self.W3_L0_size, self.W2_L0_size, self.W1_L0_size = W3.shape[1], W2.shape[1], W1.shape[1]
+        self._plan = None
+
+    def forward(self, x, atom_types):
+        assert x.shape[-1] % 32 == 0, "channel dimension of x ([-1]) must be a multiple of 32."
+        assert x.shape[1] == 16, "l dimension of x ([1]) must be 16."
+        if self._plan is None:
+            self._plan = make_plan(self.u3_max_nonsparse, self.U3_num_nonsparse, self.U3_indices, self.U3_values,
+                                   self.U2_num_nonsparse, self.U2_indices, self.U2_values, self.W3_L0_size,
+                                   self.W2_L0_size, self.W1_L0_size)
+        return symmetric_contraction_forward(
+            x, atom_types, self.u3_max_nonsparse, self.U3_num_nonsparse, self.U3_indices, self.U3_values,
+            self.U2_num_nonsparse, self.U2_indices, self.U2_values, self.U1_num_values, self.U1_index,
+            self.weights_3, self.weights_2, self.weights_1, self.W3_L0_size, self.W2_L0_size, self.W1_L0_size,
+            plan=self._plan)
+
+
+# --------------------------------------------------------------------------------------
+# spherical harmonics / edge basis
+# --------------------------------------------------------------------------------------
+class _EdgeBasisFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, xyz, r_max, nbessel, p, with_radial):
+        xyz = xyz.contiguous()
+        E = xyz.shape[0]
+        Y = torch.empty(16, E, dtype=xyz.dtype, device=xyz.device)
+        B = torch.empty(E, nbessel, dtype=xyz.dtype, device=xyz.device) if with_radial else None
+        _abi.call("cmace_edge_basis_fwd_" + _suffix(xyz), _ptr(xyz), E, float(r_max), int(nbessel), int(p),
+                  _ptr(Y), _ptr(B), _stream())
+        ctx.save_for_backward(xyz)
+        ctx.cfg = (float(r_max), int(nbessel), int(p), with_radial)
+        if with_radial:
+            return Y, B
+        return Y
+
+    @staticmethod
+    def backward(ctx, gY, gB=None):
+        (xyz,) = ctx.saved_tensors
+        r_max, nbessel, p, with_radial = ctx.cfg
+        E = xyz.shape[0]
+        gY = torch.zeros(16, E, dtype=xyz.dtype, device=xyz.device) if gY is None else gY.contiguous()
+        if with_radial:
+            gB = torch.zeros(E, nbessel, dtype=xyz.dtype, device=xyz.device) if gB is None else gB.contiguous()
+        gxyz = torch.empty_like(xyz)
+        _abi.call("cmace_edge_basis_bwd_" + _suffix(xyz), _ptr(xyz), _ptr(gY), _ptr(gB if with_radial else None),
+                  E, r_max, nbessel, p, _ptr(gxyz), _stream())
+        return gxyz, None, None, None, None
+
+
+class SphericalHarmonics(torch.nn.Module):
+    """xyz [E,3] -> Y [16,E]: real harmonics to l=3 of the normalised vectors, e3nn component order and
+    normalisation; same call as torch.classes.spherical_harmonics.SphericalHarmonics.forward
+    (src/spherical_harmonics.cpp:52-69)."""
+
+    def forward(self, xyz):
+        _check_cuda(xyz)
+        return _EdgeBasisFunction.apply(xyz, 1.0, 0, 1, False)
+
+
+class EdgeBasis(torch.nn.Module):
+    """xyz [E,3] -> (Y [16,E], B [E,nbessel]) in one pass: harmonics plus the Bessel basis with
+    polynomial cutoff, i.e. upstream MACE's radial_embedding evaluated exactly rather than through the
+    reference's spline table (models/InvariantMACE.py:226-240)."""
+
+    def __init__(self, r_max, num_bessel=8, p=5):
+        super().__init__()
+        self.r_max, self.num_bessel, self.p = float(r_max), int(num_bessel), int(p)
+
+    def forward(self, xyz):
+        _check_cuda(xyz)
+        return _EdgeBasisFunction.apply(xyz, self.r_max, self.num_bessel, self.p, True)
+
+
+# --------------------------------------------------------------------------------------
+# cubic spline
+# --------------------------------------------------------------------------------------
+class _SplineFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, r, r_knots, coeffs, r_width, r_max):
+        r = r.contiguous()
+        E, nint, nout = r.shape[0], coeffs.shape[0], coeffs.shape[2]
+        R = torch.empty(E, nout, dtype=r.dtype, device=r.device)
+        _abi.call("cmace_spline_fwd_" + _suffix(r), _ptr(r), _ptr(r_knots), _ptr(coeffs), E, nint, nout,
+                  float(r_width), float(r_max), _ptr(R), _stream())
+        ctx.save_for_backward(r, r_knots, coeffs)
+        ctx.cfg = (float(r_width), float(r_max))
+        return R
+
+    @staticmethod
+    def backward(ctx, gR):
+        r, r_knots, coeffs = ctx.saved_tensors
+        gR = gR.contiguous()
+        E, nint, nout = r.shape[0], coeffs.shape[0], coeffs.shape[2]
+        gr = torch.empty_like(r)
+        _abi.call("cmace_spline_bwd_" + _suffix(r), _ptr(r), _ptr(r_knots), _ptr(coeffs), _ptr(gR), E, nint,
+                  nout, ctx.cfg[0], ctx.cfg[1], _ptr(gr), _stream())
+        return gr, None, None, None, None
+
+
+def cubic_spline_forward(r, r_knots, coeffs, r_width, r_max):
+    """torch.classes.cubic_spline.CubicSpline.forward equivalent: coeffs [nintervals,4,F] -> R [E,F]."""
+    _check_cuda(r, r_knots, coeffs)
+    if coeffs.dim() != 3 or coeffs.shape[1] != 4:
+        raise RuntimeError("coeffs must be [nintervals, 4, noutputs]")
+    return _SplineFunction.apply(r, r_knots.contiguous(), coeffs.contiguous(), r_width, r_max)
+
+
+def cubic_spline_coefficients(x, y, h):
+    """Natural-spline coefficients [n,4,F] of y [n+1,F] on equidistant knots (the solve of
+    cuda_mace/ops/cubic_spline.py:41-84, vectorised over the channel axis)."""
+    n, F = x.shape[0] - 1, y.shape[1]
+    alpha = torch.zeros(n, F, dtype=y.dtype, device=y.device)
+    alpha[1:] = 3.0 / h * (y[2:] - y[1:-1]) - 3.0 / h * (y[1:-1] - y[:-2])
+    mu = [0.0] * n
+    z = torch.zeros(n + 1, F, dtype=y.dtype, device=y.device)
+    xs = x.tolist()
+    for i in range(1, n):
+        li = 2.0 * (xs[i + 1] - xs[i - 1]) - h * mu[i - 1]
+        mu[i] = h / li
+        z[i] = (alpha[i] - h * z[i - 1]) / li
+    c = torch.zeros(n + 1, F, dtype=y.dtype, device=y.device)
+    for j in range(n - 1, -1, -1):
+        c[j] = z[j] - mu[j] * c[j + 1]
+    b = (y[1:] - y[:-1]) / h - h * (c[1:] + 2.0 * c[:-1]) / 3.0
+    d = (c[1:] - c[:-1]) / (3.0 * h)
+    return torch.stack((y[:-1], b, c[:-1], d), dim=1).contiguous()
+
+
+class CubicSpline(torch.nn.Module):
+    """Tabulated radial weights: natural cubic spline through R_out [nknots,F] at r_knots, zero
+    beyond rmax (cuda_mace/ops/cubic_spline.py:4-39)."""
+
+    def __init__(self, r_knots, R_out, h, rmax):
+        super().__init__()
+        self.register_buffer("r_knots", r_knots.contiguous())
+        self.register_buffer("coefficients", cubic_spline_coefficients(r_knots, R_out, float(h)))
+        self.h, self.rmax = float(h), float(rmax)
+
+    def forward(self, r_trial):
+        return cubic_spline_forward(r_trial, self.r_knots, self.coefficients, self.h, self.rmax)

@@ -70,18 +70,21 @@ def edge_geometry(positions, edge_index, shifts):
 
 
 def node_energies(params, U, positions, node_attrs, edge_index, shifts, exchange=None,
-                  radial="exact"):
-    """Per-node interaction energies [N] (before the sum); differentiable wrt positions.
+                  radial="exact", n_owned=None):
+    """Per-node interaction energies of the receiving nodes [n_owned]; differentiable wrt positions.
 
-    `exchange(h, layer)` is an optional hook applied to the node features that enter message
-    passing of `layer` (used by the domain-decomposition tests to refresh ghost rows).
+    With a domain decomposition only the first `n_owned` rows receive (the rest are ghost atoms that
+    only send) and `exchange(h_owned) -> h_local` refreshes the ghost rows of the node features before
+    the second interaction; without one, n_owned = N and no hook is needed.
     """
     U3, U2, U1 = U
     r_max = float(params["r_max"])
     N, Z = node_attrs.shape
+    n_owned = N if n_owned is None else n_owned
     C = params["W_embed"].shape[1]
     recv, send = edge_index[0], edge_index[1]
-    z = node_attrs.argmax(dim=-1)
+    attrs_owned = node_attrs[:n_owned]
+    z = attrs_owned.argmax(dim=-1)
 
     vec, length = edge_geometry(positions, edge_index, shifts)
     Y = real_sh_l3(vec)  # [16, E]
@@ -97,18 +100,18 @@ def node_energies(params, U, positions, node_attrs, edge_index, shifts, exchange
         else:
             R = ops.cubic_spline_eval(length, P["spline_knots"], P["spline_coeffs"],
                                       P["spline_h"], r_max).view(-1, 4, C)
-        if exchange is not None:
-            h = exchange(h, t)
         sc = None
         if t == 1:
             # FullyConnectedTensorProduct(C x0e, Z x0e -> C x0e), 1/sqrt(C*Z)
-            sc = torch.einsum("nc,nz,czo->no", h, node_attrs, P["W_sc"]) / math.sqrt(C * Z)
+            sc = torch.einsum("nc,nz,czo->no", h, attrs_owned, P["W_sc"]) / math.sqrt(C * Z)
+            if exchange is not None:
+                h = exchange(h)
         up = h @ P["W_up"] / math.sqrt(C)
-        m = ops.invariant_message_passing(up, Y, R, send, recv, N)
+        m = ops.invariant_message_passing(up, Y, R, send, recv, n_owned)
         m = ops.linear(m, P["W_lin"]) / P["avg_num_neighbors"]
         if t == 0:
             # weights [Z,4,C,C] already carry the 1/sqrt(Z) of element_linear_to_cuda
-            m = ops.elemental_linear(m, P["W_skip"] / math.sqrt(Z), node_attrs)
+            m = ops.elemental_linear(m, P["W_skip"] / math.sqrt(Z), attrs_owned)
         b = ops.symmetric_contraction_chunked(m, z, U3, U2, U1, P["W3"], P["W2"], P["W1"])[:, 0, :]
         h = b @ P["W_prod"] / math.sqrt(C)
         if sc is not None:

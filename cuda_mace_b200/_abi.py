@@ -62,6 +62,17 @@ _VALUE_FUNCS = {"cmace_abi_version", "cmace_sender_order_workspace_bytes", "cmac
 
 _lib = None
 
+# entry points that launch kernels, with the number of kernels of ours each call launches
+# (cub's radix sort inside the two grouping calls is counted as one)
+KERNEL_LAUNCHES = {
+    "cmace_receiver_csr": 1, "cmace_sender_order": 3, "cmace_group_by_element": 3,
+    "cmace_sph_fwd": 1, "cmace_sph_bwd": 1, "cmace_edge_basis_fwd": 1, "cmace_edge_basis_bwd": 1,
+    "cmace_spline_fwd": 1, "cmace_spline_bwd": 1, "cmace_imp_fwd": 1, "cmace_imp_bwd_edge": 1,
+    "cmace_imp_bwd_node": 1, "cmace_linear": 1, "cmace_symcon_fwd": 1, "cmace_symcon_bwd": 1,
+}
+launch_count = 0       # kernels launched through this binding since import
+_timing = None         # list of (name, start_event, end_event) while timing is on
+
 
 def load():
     """Loads the shared library once and declares every prototype."""
@@ -86,10 +97,43 @@ def load():
 
 def call(name, *args):
     """Calls a status-returning entry point; raises RuntimeError with the library's message."""
+    global launch_count
     lib = load()
-    rc = getattr(lib, name)(*args)
     if name in _VALUE_FUNCS:
-        return rc
+        return getattr(lib, name)(*args)
+    base = name[:-4] if name.endswith(("_f32", "_f64")) else name
+    n_launch = KERNEL_LAUNCHES.get(base, 0)
+    if _timing is not None and n_launch:
+        import torch
+
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        rc = getattr(lib, name)(*args)
+        ev1.record()
+        _timing.append((name, ev0, ev1))
+    else:
+        rc = getattr(lib, name)(*args)
+    launch_count += n_launch
     if rc != 0:
         raise RuntimeError(f"{name} failed ({rc}): {lib.cmace_last_error().decode()}")
     return 0
+
+
+def start_timing():
+    """Brackets every kernel-launching call with CUDA events on torch's current stream."""
+    global _timing
+    _timing = []
+
+
+def stop_timing():
+    """Returns {entry point: (calls, total milliseconds)}; synchronises the device."""
+    global _timing
+    import torch
+
+    torch.cuda.synchronize()
+    out = {}
+    for name, ev0, ev1 in _timing or []:
+        calls, ms = out.get(name, (0, 0.0))
+        out[name] = (calls + 1, ms + ev0.elapsed_time(ev1))
+    _timing = None
+    return out

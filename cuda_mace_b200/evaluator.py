@@ -1,0 +1,77 @@
+"""Energy+force evaluation of one slab (or of the whole periodic box on a single GPU): the call a
+user of the package makes per step.
+
+    ev = EnergyForceEvaluator(model, domain, device, group)
+    energy, forces = ev(positions_owned)            # tensors already on the device
+    energy, forces = ev.evaluate_host(host_batch)   # pinned host buffers in, host results out
+
+`evaluate_host` moves the step's inputs (positions, species, edge list, shifts) to the device,
+rebuilds the edge topology for the list it was given, runs the model and copies energy and forces
+back, so it is the end-to-end path including every host<->device byte.
+"""
+import torch
+
+from . import domain as _domain
+from . import ops
+
+
+class EnergyForceEvaluator:
+    def __init__(self, model, dom, device, group=None):
+        self.model = model
+        self.dom = dom
+        self.device = torch.device(device)
+        self.plan = _domain.HaloPlan(dom, self.device, group)
+        self.species = None
+        self.edge_index = None
+        self.shifts = None
+        self.topology = None
+
+    def set_neighbor_list(self, species, edge_index, shifts):
+        """Device tensors: species [n_local] int32, edge_index [2,E] int32 (receivers sorted), shifts [E,3]."""
+        self.species = species
+        self.edge_index = edge_index
+        self.shifts = shifts
+        self.topology = ops.EdgeTopology(edge_index[1], edge_index[0], self.dom.n_owned, self.dom.n_local)
+        return self
+
+    def load_domain(self, pos_dtype=torch.float64):
+        d = self.dom
+        dev = self.device
+        self.set_neighbor_list(torch.as_tensor(d.species, dtype=torch.int32, device=dev),
+                               torch.as_tensor(d.edge_index, dtype=torch.int32, device=dev),
+                               torch.as_tensor(d.shifts, dtype=pos_dtype, device=dev))
+        return torch.as_tensor(d.positions[: d.n_owned], dtype=pos_dtype, device=dev)
+
+    def __call__(self, positions_owned):
+        def node_energy(pos_local, exchange):
+            return self.model.node_energies(pos_local, self.species, self.edge_index, self.shifts,
+                                            topology=self.topology, exchange=exchange, n_owned=self.dom.n_owned)
+
+        return _domain.distributed_energy_forces(node_energy, self.dom, self.plan, positions_owned)
+
+    # ---- end-to-end path with host buffers ----------------------------------------------------
+    def host_batch(self, pos_dtype=torch.float64):
+        """Pinned host copies of one step's inputs, as a data loader would hand them over."""
+        d = self.dom
+        pin = lambda t: t.pin_memory() if torch.cuda.is_available() else t
+        return {
+            "positions": pin(torch.as_tensor(d.positions[: d.n_owned], dtype=pos_dtype)),
+            "species": pin(torch.as_tensor(d.species, dtype=torch.int32)),
+            "edge_index": pin(torch.as_tensor(d.edge_index, dtype=torch.int32)),
+            "shifts": pin(torch.as_tensor(d.shifts, dtype=pos_dtype)),
+        }
+
+    @staticmethod
+    def h2d_bytes(batch):
+        return int(sum(t.numel() * t.element_size() for t in batch.values()))
+
+    def evaluate_host(self, batch, out_forces=None):
+        dev = self.device
+        moved = {k: v.to(dev, non_blocking=True) for k, v in batch.items()}
+        self.set_neighbor_list(moved["species"], moved["edge_index"], moved["shifts"])
+        energy, forces = self(moved["positions"])
+        if out_forces is None:
+            out_forces = torch.empty(forces.shape, dtype=forces.dtype, pin_memory=torch.cuda.is_available())
+        out_forces.copy_(forces, non_blocking=True)
+        e = float(energy.cpu())  # synchronises
+        return e, out_forces

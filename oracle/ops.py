@@ -69,12 +69,19 @@ def symmetric_contraction(X, atom_types, U3, U2, U1, W3, W2, W1):
     Returns [N, 1, C] like the reference wrapper (symmetric_contraction_wrapper.cpp:39-41).
     """
     z = atom_types.long()
-    T3 = torch.einsum("ijkp,zpc->zijkc", U3, W3)
-    T2 = torch.einsum("ijp,zpc->zijc", U2, W2)
-    T1 = torch.einsum("ip,zpc->zic", U1, W1)
-    out = torch.einsum("nijkc,nic,njc,nkc->nc", T3[z], X, X, X)
-    out = out + torch.einsum("nijc,nic,njc->nc", T2[z], X, X)
-    out = out + torch.einsum("nic,nic->nc", T1[z], X)
+    out = torch.zeros(X.shape[0], X.shape[2], dtype=X.dtype)
+    for e in range(W3.shape[0]):
+        (idx,) = torch.where(z == e)
+        if idx.numel() == 0:
+            continue
+        x = X[idx]
+        T3 = torch.einsum("ijkp,pc->ijkc", U3, W3[e])
+        T2 = torch.einsum("ijp,pc->ijc", U2, W2[e])
+        T1 = torch.einsum("ip,pc->ic", U1, W1[e])
+        # nested like the kernel: innermost k, then j, then i
+        t = torch.einsum("ijkc,nkc->nijc", T3, x) + T2[None]
+        t = torch.einsum("nijc,njc->nic", t, x) + T1[None]
+        out = out.index_add(0, idx, torch.einsum("nic,nic->nc", t, x))
     return out[:, None, :]
 
 

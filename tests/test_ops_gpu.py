@@ -1,0 +1,269 @@
+"""Parity of every CUDA operator (through the C-ABI) with the float64 CPU oracle: outputs and all
+input gradients with loss (out**2).sum(), float32 and float64, edge cases included."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.util import TOL, random_graph, rel_err, unit_vectors
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+DTYPES = [torch.float64, torch.float32]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "the gpu tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def imp_case(seed, N, deg, C, dtype, dev, nsend=None, empty_every=0):
+    send, recv = random_graph(seed, N, deg, n_senders=nsend, empty_every=empty_every)
+    E = send.numel()
+    g = torch.Generator().manual_seed(seed + 100)
+    X = torch.randn(nsend or N, C, generator=g, dtype=torch.float64)
+    Y = torch.randn(16, E, generator=g, dtype=torch.float64)
+    R = torch.randn(E, 4, C, generator=g, dtype=torch.float64)
+    return send, recv, X, Y, R
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,deg,C,nsend,empty", [
+    (97, 7, 128, None, 0),      # odd degrees, one f32 chunk / two f64 chunks
+    (64, 30, 64, None, 5),      # isolated receivers
+    (33, 3, 96, None, 0),       # three 32-channel chunks
+    (50, 5, 32, 80, 3),         # more sender rows than receivers (ghost atoms), isolated receivers
+    (5, 600, 128, None, 0),     # more than 512 neighbours per receiver
+])
+def test_message_passing(dtype, N, deg, C, nsend, empty, dev):
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    send, recv, X, Y, R = imp_case(N + C, N, deg, C, dtype, dev, nsend, empty)
+    Xo, Yo, Ro = (t.to(dtype).double().requires_grad_(True) for t in (X, Y, R))
+    ref = oops.invariant_message_passing(Xo, Yo, Ro, send, recv, N)
+    (ref ** 2).sum().backward()
+
+    Xg, Yg, Rg = (t.to(dtype).to(dev).requires_grad_(True) for t in (X, Y, R))
+    tp = ops.InvariantMessagePassingTP()
+    out = tp(Xg, Yg, Rg, send.to(dev), recv.to(dev), N)
+    assert out.shape == (N, 16, C)
+    (out ** 2).sum().backward()
+    tol = TOL[dtype]
+    assert rel_err(out, ref) < tol["out"]
+    assert rel_err(Xg.grad, Xo.grad) < tol["grad"]
+    assert rel_err(Yg.grad, Yo.grad) < tol["grad"]
+    assert rel_err(Rg.grad, Ro.grad) < tol["grad"]
+    if empty:  # receivers without edges are written as zeros, not left as garbage
+        assert out[::empty].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_message_passing_without_edges_and_determinism(dtype, dev):
+    from cuda_mace_b200 import ops
+
+    tp = ops.InvariantMessagePassingTP()
+    e = torch.zeros(0, dtype=torch.int32, device=dev)
+    out = tp(torch.randn(4, 32, dtype=dtype, device=dev), torch.zeros(16, 0, dtype=dtype, device=dev),
+             torch.zeros(0, 4, 32, dtype=dtype, device=dev), e, e, 4)
+    assert out.shape == (4, 16, 32) and out.abs().max().item() == 0.0
+    send, recv, X, Y, R = imp_case(5, 300, 20, 128, dtype, dev)
+    args = [t.to(dtype).to(dev) for t in (X, Y, R)] + [send.to(dev), recv.to(dev), 300]
+    assert torch.equal(tp(*args), tp(*args))  # no atomics: bitwise reproducible
+
+
+def test_topology(dev):
+    from cuda_mace_b200 import ops
+
+    send, recv = random_graph(3, 1000, 9, empty_every=7)
+    topo = ops.EdgeTopology(send.to(dev), recv.to(dev), 1000)
+    counts = torch.bincount(recv.long(), minlength=1000)
+    ref_ptr = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)])
+    assert torch.equal(topo.row_ptr.cpu().long(), ref_ptr)
+    perm, send_ptr = topo.sender_order()
+    perm = perm.cpu().long()[: send.numel()]
+    assert torch.equal(send[perm].long(), torch.sort(send.long(), stable=True).values)
+    assert torch.equal(perm, torch.sort(send.long(), stable=True).indices)
+    sc = torch.bincount(send.long(), minlength=1000)
+    assert torch.equal(send_ptr.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), sc.cumsum(0)]))
+    # empty list
+    e = torch.zeros(0, dtype=torch.int32, device=dev)
+    assert ops.EdgeTopology(e, e, 5).row_ptr.cpu().tolist() == [0] * 6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,K,Nout", [(130, 128, 128), (9, 64, 64), (40, 96, 32), (1, 32, 96)])
+def test_linear(dtype, N, K, Nout, dev):
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(N)
+    X = torch.randn(N, 16, K, generator=g, dtype=torch.float64).to(dtype)
+    W = torch.randn(4, K, Nout, generator=g, dtype=torch.float64).to(dtype)
+    Xo = X.double().requires_grad_(True)
+    ref = oops.linear(Xo, W.double())
+    (ref ** 2).sum().backward()
+    Xg = X.to(dev).requires_grad_(True)
+    Wg = W.to(dev)
+    out = ops.linear_forward(Xg, Wg, Wg.transpose(-1, -2).contiguous())
+    (out ** 2).sum().backward()
+    assert rel_err(out, ref) < TOL[dtype]["out"]
+    assert rel_err(Xg.grad, Xo.grad) < TOL[dtype]["grad"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,Z,K", [(200, 4, 128), (37, 10, 64), (5, 3, 32)])
+def test_elemental_linear(dtype, N, Z, K, dev):
+    from cuda_mace_b200 import ops, systems
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(N + Z)
+    X = torch.randn(N, 16, K, generator=g, dtype=torch.float64).to(dtype)
+    W = torch.randn(Z, 4, K, K, generator=g, dtype=torch.float64).to(dtype)
+    at = torch.randint(0, Z, (N,), generator=g)
+    at[at == 1] = 0  # one element with no atoms at all
+    onehot = systems.one_hot(at, Z)
+    Xo = X.double().requires_grad_(True)
+    ref = oops.elemental_linear(Xo, W.double(), onehot)
+    (ref ** 2).sum().backward()
+    Xg = X.to(dev).requires_grad_(True)
+    Wg = W.to(dev)
+    out = ops.elemental_linear_forward(Xg, Wg, Wg.transpose(-1, -2).contiguous(), onehot.to(dtype).to(dev))
+    (out ** 2).sum().backward()
+    assert rel_err(out, ref) < TOL[dtype]["out"]
+    assert rel_err(Xg.grad, Xo.grad) < TOL[dtype]["grad"]
+    # int32 element index instead of one-hot
+    out2 = ops.elemental_linear_forward(X.to(dev), Wg, Wg.transpose(-1, -2).contiguous(), at.to(torch.int32).to(dev))
+    assert torch.equal(out2, out.detach())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,C,Z", [(256, 128, 10), (19, 32, 1), (64, 64, 4)])
+def test_symmetric_contraction(dtype, N, C, Z, dev, U):
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(N + C)
+    X = torch.randn(N, 16, C, generator=g, dtype=torch.float64).to(dtype)
+    at = torch.randint(0, Z, (N,), generator=g, dtype=torch.int32)
+    W3, W2, W1 = (torch.randn(Z, n, C, generator=g, dtype=torch.float64).to(dtype) / n for n in (23, 4, 1))
+    Xo = X.double().requires_grad_(True)
+    ref = oops.symmetric_contraction_chunked(Xo, at, *U, W3.double(), W2.double(), W1.double())
+    (ref ** 2).sum().backward()
+    mod = ops.SymmetricContraction(*U, W3, W2, W1).to(dev)
+    Xg = X.to(dev).requires_grad_(True)
+    out = mod(Xg, at.to(dev))
+    assert out.shape == (N, 1, C)
+    (out ** 2).sum().backward()
+    assert rel_err(out, ref) < TOL[dtype]["out"]
+    assert rel_err(Xg.grad, Xo.grad) < TOL[dtype]["grad"]
+
+
+def test_symmetric_contraction_reference_argument_list(dev, U):
+    """The reference's float32 sparse tables passed positionally, as torch.classes.symm_contract does."""
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    maxnz, n3, i3, v3, n2, i2, v2, n1, i1 = oops.pack_sparse_u(*U)  # float32 values like the reference
+    g = torch.Generator().manual_seed(0)
+    N, C, Z = 40, 64, 3
+    X = torch.randn(N, 16, C, generator=g)
+    at = torch.randint(0, Z, (N,), generator=g, dtype=torch.int32)
+    W = [torch.randn(1, Z, n, C, generator=g) / n for n in (23, 4, 1)]
+    ref = oops.symmetric_contraction(X.double(), at, *U, *[w[0].double() for w in W])
+    d = lambda t: t.to(dev)
+    out = ops.symmetric_contraction_forward(d(X), d(at), maxnz, d(n3), d(i3), d(v3), d(n2), d(i2), d(v2), d(n1), d(i1),
+                                            d(W[0]), d(W[1]), d(W[2]), 23, 4, 1)
+    assert rel_err(out, ref) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_spherical_harmonics_and_edge_basis(dtype, dev):
+    from cuda_mace_b200 import ops
+    from oracle import model as omodel
+    from oracle.sh import real_sh_l3
+
+    E = 5000
+    g = torch.Generator().manual_seed(9)
+    xyz = unit_vectors(9, E) * (0.7 + 4.6 * torch.rand(E, 1, generator=g, dtype=torch.float64))
+    xyz = xyz.to(dtype)
+    xo = xyz.double().requires_grad_(True)
+    Yo = real_sh_l3(xo)
+    Bo = omodel.radial_embedding(xo.norm(dim=-1), 5.0)
+    gy = torch.randn(16, E, generator=g, dtype=torch.float64)
+    gb = torch.randn(E, 8, generator=g, dtype=torch.float64)
+    (go_y,) = torch.autograd.grad((Yo * gy).sum(), xo, retain_graph=True)
+    (go_all,) = torch.autograd.grad((Yo * gy).sum() + (Bo * gb).sum(), xo)
+    tol = TOL[dtype]
+
+    xg = xyz.to(dev).requires_grad_(True)
+    Y = ops.SphericalHarmonics()(xg)
+    assert Y.shape == (16, E) and rel_err(Y, Yo) < tol["out"]
+    (gx,) = torch.autograd.grad((Y * gy.to(dtype).to(dev)).sum(), xg)
+    assert rel_err(gx, go_y) < tol["grad"]
+
+    xg = xyz.to(dev).requires_grad_(True)
+    Y, B = ops.EdgeBasis(5.0, 8, 5)(xg)
+    assert rel_err(Y, Yo) < tol["out"] and rel_err(B, Bo) < tol["out"]
+    assert B[xyz.norm(dim=-1).to(dev) >= 5.0].abs().max().item() == 0.0
+    (gx,) = torch.autograd.grad((Y * gy.to(dtype).to(dev)).sum() + (B * gb.to(dtype).to(dev)).sum(), xg)
+    assert rel_err(gx, go_all) < tol["grad"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cubic_spline(dtype, dev):
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(4)
+    nk, F, E = 256, 512, 3000
+    knots = torch.linspace(1e-12, 6.0, nk, dtype=torch.float64)
+    h = float(knots[1] - knots[0])
+    table = torch.randn(nk, F, generator=g, dtype=torch.float64).cumsum(0) * 0.1
+    coeffs = oops.cubic_spline_coefficients(knots, table, h)
+    assert rel_err(ops.cubic_spline_coefficients(knots, table, h), coeffs) < 1e-13
+    r = (0.5 + 5.2 * torch.rand(E, generator=g, dtype=torch.float64)).to(dtype)
+    ro = r.double().requires_grad_(True)
+    ko, co = knots.to(dtype).double(), coeffs.to(dtype).double()
+    ref = oops.cubic_spline_eval(ro, ko, co, float(torch.tensor(h, dtype=dtype)), 5.0)
+    (ref ** 2).sum().backward()
+    rg = r.to(dev).requires_grad_(True)
+    out = ops.cubic_spline_forward(rg, knots.to(dtype).to(dev), coeffs.to(dtype).to(dev), h, 5.0)
+    (out ** 2).sum().backward()
+    assert out.shape == (E, F)
+    assert out[r.to(dev) > 5.0].abs().max().item() == 0.0
+    assert rel_err(out, ref) < TOL[dtype]["out"] * 10
+    assert rel_err(rg.grad, ro.grad) < TOL[dtype]["grad"] * 10
+
+
+def test_golden_fixture_through_the_kernels(dev, U):
+    """The committed small fixture (generated by tests/golden/make_golden.py) through the CUDA path."""
+    from cuda_mace_b200 import ops
+
+    z = np.load(os.path.join(GOLD, "ops_small.npz"))
+    t = {k: torch.from_numpy(z[k]) for k in z.files}
+    d = lambda x: x.to(dev)
+    N = t["X"].shape[0]
+    Y = ops.SphericalHarmonics()(d(t["vec"]))
+    assert rel_err(Y, t["Y"]) < 1e-12
+    out = ops.InvariantMessagePassingTP()(d(t["X"]), Y, d(t["R"]), d(t["send"]).int(), d(t["recv"]).int(), N)
+    assert rel_err(out, t["imp"]) < 1e-12
+    W = d(t["W"])
+    assert rel_err(ops.linear_forward(d(t["M"]), W, W.transpose(-1, -2).contiguous()), t["lin"]) < 1e-12
+    WZ = d(t["WZ"])
+    assert rel_err(ops.elemental_linear_forward(d(t["M"]), WZ, WZ.transpose(-1, -2).contiguous(), d(t["at"]).int()),
+                   t["elin"]) < 1e-12
+    mod = ops.SymmetricContraction(*U, t["W3"], t["W2"], t["W1"]).to(dev)
+    assert rel_err(mod(d(t["M"]), d(t["at"]).int()), t["con"]) < 1e-11
+    _, B = ops.EdgeBasis(5.0, 8, 5)(d(t["vec"]))
+    assert rel_err(B, t["bessel"]) < 1e-12
+
+
+def test_cpu_tensors_are_rejected():
+    from cuda_mace_b200 import ops
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.SphericalHarmonics()(torch.randn(4, 3))

@@ -40,8 +40,8 @@ SIGNATURES = {
     "cmace_imp_bwd_edge_f64": [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P, _P, _P, _P, _P],
     "cmace_imp_bwd_node_f32": [_P, _P, _P, _L, _I, _P, _P],
     "cmace_imp_bwd_node_f64": [_P, _P, _P, _L, _I, _P, _P],
-    "cmace_linear_f32": [_P, _P, _P, _P, _I, _L, _I, _I, _P, _P],
-    "cmace_linear_f64": [_P, _P, _P, _P, _I, _L, _I, _I, _P, _P],
+    "cmace_linear_f32": [_P, _P, _P, _P, _I, _L, _I, _I, _D, _P, _P],
+    "cmace_linear_f64": [_P, _P, _P, _P, _I, _L, _I, _I, _D, _P, _P],
     "cmace_symcon_plan_create": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, ctypes.POINTER(_P)],
     "cmace_symcon_plan_destroy": [_P],
     "cmace_symcon_plan_nterms": [_P],

@@ -1,4 +1,4 @@
-// Per-l channel mixing:  out[n, l^2+m, :] = X[n, l^2+m, :] @ W[z_n, l] / sqrt(K).
+// Per-l channel mixing:  out[n, l^2+m, :] = scale * X[n, l^2+m, :] @ W[z_n, l],  scale = 1/sqrt(K).
 //
 // One launch covers the four l blocks and, for ElementalLinear, all chemical elements: the rows
 // (node, m) of one (element, l) pair form a dense GEMM problem of (#nodes of the element)*(2l+1)
@@ -103,7 +103,8 @@ __global__ void __launch_bounds__(LIN_THREADS)
 
 template <typename T>
 static int linear(const T *X, const T *W, const int32_t *node_order, const int32_t *elem_start,
-                  int nelements, int64_t nnodes, int K, int Nout, T *out, cmace_stream_t stream) {
+                  int nelements, int64_t nnodes, int K, int Nout, double scale, T *out,
+                  cmace_stream_t stream) {
   if (nnodes < 0 || K < 1 || Nout < 1 || nelements < 1) return fail(CMACE_ERR_ARG, "cmace_linear: bad size");
   if (nnodes == 0) return CMACE_OK;
   if (!X || !W || !out) return fail(CMACE_ERR_ARG, "cmace_linear: null pointer");
@@ -113,7 +114,7 @@ static int linear(const T *X, const T *W, const int32_t *node_order, const int32
   if (max_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear: too many rows");
   dim3 grid((unsigned)max_tiles, 4, (unsigned)((Nout + TILE_N - 1) / TILE_N));
   linear_tile_kernel<T><<<grid, LIN_THREADS, 0, (cudaStream_t)stream>>>(
-      X, W, node_order, elem_start, nelements, nnodes, K, Nout, (T)(1.0 / sqrt((double)K)), out);
+      X, W, node_order, elem_start, nelements, nnodes, K, Nout, (T)scale, out);
   return check_launch("cmace_linear");
 }
 
@@ -123,11 +124,13 @@ using namespace cmace;
 
 extern "C" {
 int cmace_linear_f32(const float *X, const float *W, const int32_t *node_order, const int32_t *elem_start,
-                     int nelements, int64_t nnodes, int K, int Nout, float *out, cmace_stream_t stream) {
-  return linear<float>(X, W, node_order, elem_start, nelements, nnodes, K, Nout, out, stream);
+                     int nelements, int64_t nnodes, int K, int Nout, double scale, float *out,
+                     cmace_stream_t stream) {
+  return linear<float>(X, W, node_order, elem_start, nelements, nnodes, K, Nout, scale, out, stream);
 }
 int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order, const int32_t *elem_start,
-                     int nelements, int64_t nnodes, int K, int Nout, double *out, cmace_stream_t stream) {
-  return linear<double>(X, W, node_order, elem_start, nelements, nnodes, K, Nout, out, stream);
+                     int nelements, int64_t nnodes, int K, int Nout, double scale, double *out,
+                     cmace_stream_t stream) {
+  return linear<double>(X, W, node_order, elem_start, nelements, nnodes, K, Nout, scale, out, stream);
 }
 }

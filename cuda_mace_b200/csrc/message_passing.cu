@@ -263,7 +263,7 @@ static int imp_fwd(const T *X, const T *Y, const T *R, const int32_t *sender, co
   int rc = check_common<T>(X, R, out, nnodes, nedges, C, "cmace_imp_fwd");
   if (rc) return rc;
   if (nnodes == 0) return CMACE_OK;
-  if (!X || !R || !out || !row_ptr || (nedges > 0 && (!Y || !sender)))
+  if (!out || !row_ptr || (nedges > 0 && (!X || !R || !Y || !sender)))
     return fail(CMACE_ERR_ARG, "cmace_imp_fwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   switch (pick_vec<T>(C)) {

@@ -185,7 +185,7 @@ class InvariantMessagePassingTP(torch.nn.Module):
 # --------------------------------------------------------------------------------------
 # Linear / ElementalLinear
 # --------------------------------------------------------------------------------------
-def _linear_call(X, W, node_order, elem_start, nelements):
+def _linear_call(X, W, node_order, elem_start, nelements, scale):
     X = X.contiguous()
     N, K = X.shape[0], X.shape[2]
     Nout = W.shape[-1]
@@ -195,7 +195,7 @@ def _linear_call(X, W, node_order, elem_start, nelements):
         raise TypeError("X and W must have the same dtype")
     out = torch.empty(N, 16, Nout, dtype=X.dtype, device=X.device)
     _abi.call("cmace_linear_" + _suffix(X), _ptr(X), _ptr(W.contiguous()), _ptr(node_order), _ptr(elem_start),
-              nelements, N, K, Nout, _ptr(out), _stream())
+              nelements, N, K, Nout, float(scale), _ptr(out), _stream())
     return out
 
 
@@ -203,14 +203,15 @@ class _LinearFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, X, W, W_T, node_order, elem_start, nelements):
         ctx.save_for_backward(W_T)
-        ctx.grouping = (node_order, elem_start, nelements)
-        return _linear_call(X, W, node_order, elem_start, nelements)
+        scale = 1.0 / math.sqrt(X.shape[2])  # the path weight of linear_impl.cu:33
+        ctx.grouping = (node_order, elem_start, nelements, scale)
+        return _linear_call(X, W, node_order, elem_start, nelements, scale)
 
     @staticmethod
     def backward(ctx, G):
         (W_T,) = ctx.saved_tensors
-        node_order, elem_start, nelements = ctx.grouping
-        return _linear_call(G, W_T, node_order, elem_start, nelements), None, None, None, None, None
+        node_order, elem_start, nelements, scale = ctx.grouping
+        return _linear_call(G, W_T, node_order, elem_start, nelements, scale), None, None, None, None, None
 
 
 def linear_forward(X, W, W_T):

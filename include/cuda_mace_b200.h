@@ -132,17 +132,20 @@ int cmace_imp_bwd_node_f64(const double *T, const int32_t *perm, const int32_t *
 
 /* ---- Linear / ElementalLinear -------------------------------------------------------------
  * Replace jit_linear and jit_elemental_linear (jit_wrappers/src/linear_wrapper.cpp:23-191, kernels
- * cuda/src/linear_impl.cu:16-255): out[n, l^2+m, :] = X[n, l^2+m, :] @ W[z_n, l] / sqrt(K).
- * X [N,16,K]; W [nelements,4,K,Nout]; out [N,16,Nout].  For Linear pass nelements = 1 and
- * node_order = elem_start = NULL.  For ElementalLinear pass the outputs of
+ * cuda/src/linear_impl.cu:16-255): out[n, l^2+m, :] = scale * X[n, l^2+m, :] @ W[z_n, l].
+ * X [N,16,K]; W [nelements,4,K,Nout]; out [N,16,Nout].  The reference hard-codes
+ * scale = 1/sqrt(K) (linear_impl.cu:33); pass that for the forward.  For Linear pass
+ * nelements = 1 and node_order = elem_start = NULL.  For ElementalLinear pass the outputs of
  * cmace_group_by_element.  The backward of both is the same call with the transposed weights,
- * as in the reference (src/linear.cpp:29-44, :77-93).  One launch, no host synchronisation. */
+ * as in the reference (src/linear.cpp:29-44, :77-93), and with the FORWARD's scale (the
+ * reference re-derives it from the transposed shape, which is only right for K = Nout).
+ * One launch, no host synchronisation. */
 int cmace_linear_f32(const float *X, const float *W, const int32_t *node_order,
                      const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
-                     float *out, cmace_stream_t stream);
+                     double scale, float *out, cmace_stream_t stream);
 int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order,
                      const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
-                     double *out, cmace_stream_t stream);
+                     double scale, double *out, cmace_stream_t stream);
 
 /* ---- symmetric contraction (correlation 3, invariant output) ------------------------------
  * Replace jit_symmetric_contraction_forward / _backward

@@ -40,5 +40,5 @@ def test_argument_errors_are_reported_not_raised(built_library):
     rc = lib.cmace_imp_fwd_f32(None, None, None, None, None, 4, 4, 33, None, None)
     assert rc == 3  # CMACE_ERR_UNSUPPORTED: channels not a multiple of 32
     assert b"multiple of 32" in lib.cmace_last_error()
-    rc = lib.cmace_linear_f32(None, None, None, None, 1, 5, 32, 32, None, None)
+    rc = lib.cmace_linear_f32(None, None, None, None, 1, 5, 32, 32, 1.0, None, None)
     assert rc == 1 and b"null" in lib.cmace_last_error()

@@ -37,9 +37,10 @@ def test_cfg0_matches_fixture_and_oracle(dtype, tol_e, tol_f, U):
     assert abs(float(out["energy"]) - float(z["energy"])) < tol_e * abs(float(z["energy"]))
     assert abs(float(out["interaction_energy"]) - float(z["interaction"])) < tol_e * abs(float(z["interaction"]))
     assert rel_err(out["forces"], torch.from_numpy(z["forces"])) < tol_f
-    # a second call reuses the cached topology and gives identical numbers
+    # a second call reuses the cached topology; the kernels are bitwise reproducible, torch's
+    # index_add in the position gradient is not, so compare to rounding
     out2 = m(data)
-    assert torch.equal(out2["forces"], out["forces"])
+    assert rel_err(out2["forces"], out["forces"]) < (1e-13 if dtype == torch.float64 else 1e-5)
 
 
 @pytest.mark.parametrize("dtype,tol_e,tol_f", [(torch.float64, 1e-10, 1e-10), (torch.float32, 1e-5, 1e-4)])

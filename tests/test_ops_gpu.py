@@ -43,11 +43,11 @@ def test_message_passing(dtype, N, deg, C, nsend, empty, dev):
     from oracle import ops as oops
 
     send, recv, X, Y, R = imp_case(N + C, N, deg, C, dtype, dev, nsend, empty)
-    Xo, Yo, Ro = (t.to(dtype).double().requires_grad_(True) for t in (X, Y, R))
+    Xo, Yo, Ro = (t.to(dtype).double().clone().requires_grad_(True) for t in (X, Y, R))
     ref = oops.invariant_message_passing(Xo, Yo, Ro, send, recv, N)
     (ref ** 2).sum().backward()
 
-    Xg, Yg, Rg = (t.to(dtype).to(dev).requires_grad_(True) for t in (X, Y, R))
+    Xg, Yg, Rg = (t.to(dtype).to(dev).clone().requires_grad_(True) for t in (X, Y, R))
     tp = ops.InvariantMessagePassingTP()
     out = tp(Xg, Yg, Rg, send.to(dev), recv.to(dev), N)
     assert out.shape == (N, 16, C)
@@ -103,10 +103,10 @@ def test_linear(dtype, N, K, Nout, dev):
     g = torch.Generator().manual_seed(N)
     X = torch.randn(N, 16, K, generator=g, dtype=torch.float64).to(dtype)
     W = torch.randn(4, K, Nout, generator=g, dtype=torch.float64).to(dtype)
-    Xo = X.double().requires_grad_(True)
+    Xo = X.double().clone().requires_grad_(True)
     ref = oops.linear(Xo, W.double())
     (ref ** 2).sum().backward()
-    Xg = X.to(dev).requires_grad_(True)
+    Xg = X.to(dev).clone().requires_grad_(True)
     Wg = W.to(dev)
     out = ops.linear_forward(Xg, Wg, Wg.transpose(-1, -2).contiguous())
     (out ** 2).sum().backward()
@@ -126,10 +126,10 @@ def test_elemental_linear(dtype, N, Z, K, dev):
     at = torch.randint(0, Z, (N,), generator=g)
     at[at == 1] = 0  # one element with no atoms at all
     onehot = systems.one_hot(at, Z)
-    Xo = X.double().requires_grad_(True)
+    Xo = X.double().clone().requires_grad_(True)
     ref = oops.elemental_linear(Xo, W.double(), onehot)
     (ref ** 2).sum().backward()
-    Xg = X.to(dev).requires_grad_(True)
+    Xg = X.to(dev).clone().requires_grad_(True)
     Wg = W.to(dev)
     out = ops.elemental_linear_forward(Xg, Wg, Wg.transpose(-1, -2).contiguous(), onehot.to(dtype).to(dev))
     (out ** 2).sum().backward()
@@ -150,11 +150,11 @@ def test_symmetric_contraction(dtype, N, C, Z, dev, U):
     X = torch.randn(N, 16, C, generator=g, dtype=torch.float64).to(dtype)
     at = torch.randint(0, Z, (N,), generator=g, dtype=torch.int32)
     W3, W2, W1 = (torch.randn(Z, n, C, generator=g, dtype=torch.float64).to(dtype) / n for n in (23, 4, 1))
-    Xo = X.double().requires_grad_(True)
+    Xo = X.double().clone().requires_grad_(True)
     ref = oops.symmetric_contraction_chunked(Xo, at, *U, W3.double(), W2.double(), W1.double())
     (ref ** 2).sum().backward()
     mod = ops.SymmetricContraction(*U, W3, W2, W1).to(dev)
-    Xg = X.to(dev).requires_grad_(True)
+    Xg = X.to(dev).clone().requires_grad_(True)
     out = mod(Xg, at.to(dev))
     assert out.shape == (N, 1, C)
     (out ** 2).sum().backward()
@@ -190,7 +190,7 @@ def test_spherical_harmonics_and_edge_basis(dtype, dev):
     g = torch.Generator().manual_seed(9)
     xyz = unit_vectors(9, E) * (0.7 + 4.6 * torch.rand(E, 1, generator=g, dtype=torch.float64))
     xyz = xyz.to(dtype)
-    xo = xyz.double().requires_grad_(True)
+    xo = xyz.double().clone().requires_grad_(True)
     Yo = real_sh_l3(xo)
     Bo = omodel.radial_embedding(xo.norm(dim=-1), 5.0)
     gy = torch.randn(16, E, generator=g, dtype=torch.float64)
@@ -226,11 +226,11 @@ def test_cubic_spline(dtype, dev):
     coeffs = oops.cubic_spline_coefficients(knots, table, h)
     assert rel_err(ops.cubic_spline_coefficients(knots, table, h), coeffs) < 1e-13
     r = (0.5 + 5.2 * torch.rand(E, generator=g, dtype=torch.float64)).to(dtype)
-    ro = r.double().requires_grad_(True)
+    ro = r.double().clone().requires_grad_(True)
     ko, co = knots.to(dtype).double(), coeffs.to(dtype).double()
     ref = oops.cubic_spline_eval(ro, ko, co, float(torch.tensor(h, dtype=dtype)), 5.0)
     (ref ** 2).sum().backward()
-    rg = r.to(dev).requires_grad_(True)
+    rg = r.to(dev).clone().requires_grad_(True)
     out = ops.cubic_spline_forward(rg, knots.to(dtype).to(dev), coeffs.to(dtype).to(dev), h, 5.0)
     (out ** 2).sum().backward()
     assert out.shape == (E, F)

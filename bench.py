@@ -44,6 +44,7 @@ def parse():
     ap.add_argument("--atoms-per-gpu", type=int, default=64000)
     ap.add_argument("--cpu-sample-atoms", type=int, default=400)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     return ap.parse_args()
 
 
@@ -230,23 +231,25 @@ def main():
     value = n_total / (ms_per_step * 1e-3)
 
     # ---- end-to-end timing with host buffers -----------------------------------------------------
-    batch = ev.host_batch()
-    out_forces = torch.empty(N, 3, dtype=torch.float64, pin_memory=True)
-    for _ in range(3):
-        ev.evaluate_host(batch, out_forces)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        e_host, _ = ev.evaluate_host(batch, out_forces)
-    e1.record()
-    barrier()
-    ems = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(ems, op=dist.ReduceOp.MAX)
-    e2e_value = n_total / (float(ems) / args.steps * 1e-3)
-    h2d = evaluator.EnergyForceEvaluator.h2d_bytes(batch)
-    d2h = out_forces.numel() * out_forces.element_size() + 8
+    e2e_value, h2d, d2h = None, 0, 0
+    if not args.no_e2e:
+        batch = ev.host_batch()
+        out_forces = torch.empty(N, 3, dtype=torch.float64, pin_memory=True)
+        for _ in range(3):
+            ev.evaluate_host(batch, out_forces)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            e_host, _ = ev.evaluate_host(batch, out_forces)
+        e1.record()
+        barrier()
+        ems = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+        e2e_value = n_total / (float(ems) / args.steps * 1e-3)
+        h2d = evaluator.EnergyForceEvaluator.h2d_bytes(batch)
+        d2h = out_forces.numel() * out_forces.element_size() + 8
 
     if rank != 0:
         if world > 1:

@@ -1,0 +1,575 @@
+// float32 GEMM on the 5th-generation tensor cores with a 3-term TF32 split:
+//
+//   out[row(r), :] = scale * A[row(r), :] @ B          A [M, K] float32, B [K, N] float32
+//
+// Every float32 operand x is split as x = hi + lo with hi = tf32(x) and lo = tf32(x - hi) (both rounded to
+// nearest, so the residual is unbiased), and D = Ahi*Bhi + Alo*Bhi + Ahi*Blo is accumulated in float32 in tensor
+// memory, which brings the result to about 2^-21 relative: float32-grade, unlike a single TF32 pass.
+//
+// Structure (one CTA per SM, persistent over 128-row tiles, warp specialised, 13 warps):
+//   warps 0-7  producers: gather 128 rows x 32 columns (one "K block") of A per pipeline stage with
+//              128-byte row segments, split hi/lo in registers and store both images in the 128-byte
+//              swizzled K-major layout tcgen05 expects; one thread also starts the bulk copy of the
+//              matching pre-packed B block (hi and lo images, already swizzled by the pack kernel).
+//   warp 8     MMA issuer: one elected thread issues tcgen05.mma kind::tf32 (M=128, N<=128, K=8),
+//              4 K-steps x 3 split terms per stage, and commits to the stage's "empty" barrier and,
+//              after the last K block of a tile, to the accumulator's "full" barrier.
+//   warps 9-12 epilogue: tcgen05.ld of the accumulator (each thread one row, 32 columns at a time),
+//              scale, store 128 contiguous bytes per thread, release the accumulator.
+// Accumulators are double buffered in tensor memory (2 x 128 columns), so the epilogue of tile t
+// overlaps the MMAs of tile t+1, and a 3-stage shared-memory ring overlaps loads with MMAs.
+//
+// Row maps: PLAIN (row r of tile t is r + 128 t; used for the radial multilayer perceptron, N may be
+// several 128-column tiles) and LINEAR (rows are the (node, m) pairs of one (element, l) problem of the
+// per-l Linear / ElementalLinear operator, with the weight matrix selected per tile).
+//
+// Every wait on an mbarrier is bounded; on a time-out the role records a code in *status and leaves
+// its loop, the others time out in turn, and the CTA still frees its tensor memory and returns.
+#include "common.cuh"
+
+namespace cmace {
+
+constexpr int GT_STAGES = 3;
+constexpr int GT_TILE_M = 128;
+constexpr int GT_KBLOCK = 32;                       // floats per K block = one 128-byte swizzle row
+constexpr int GT_A_SLAB = GT_TILE_M * 128;          // bytes of one A image (hi or lo) per stage
+constexpr int GT_B_SLAB_MAX = 128 * 128;            // bytes of one B image per stage at N tile = 128
+constexpr int GT_STAGE_BYTES = 2 * GT_A_SLAB + 2 * GT_B_SLAB_MAX;
+constexpr int GT_PRODUCER_WARPS = 8;
+constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
+constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + 4) * 32;
+constexpr int GT_TMEM_COLS = 256;
+constexpr long long GT_TIMEOUT_CYCLES = 4000000000LL;  // about two seconds
+
+enum { GT_MODE_PLAIN = 0, GT_MODE_LINEAR = 1 };
+
+struct GemmArgs {
+  const float *A;
+  const float *packed;          // [nmat][n_tiles][k_blocks][hi|lo][npad rows x 128 B]
+  float *out;
+  const int32_t *node_order;    // LINEAR mode, may be null
+  const int32_t *elem_start;    // LINEAR mode, may be null
+  int32_t *status;              // device int, may be null
+  int64_t M;                    // PLAIN: rows; LINEAR: nodes
+  int K, N;
+  int nelements;
+  int mode;
+  float scale;
+  int n_tiles, k_blocks, npad;  // packing geometry: N tiles of <= 128 columns, npad rows per B image
+  int64_t total_tiles;          // upper bound of the tile index space
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait: false after GT_TIMEOUT_CYCLES
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > GT_TIMEOUT_CYCLES) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte swizzled operand image: rows of 128 bytes, 8-row groups 1024 bytes apart.
+// Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused with swizzle, set to 1),
+// stride byte offset >> 4 [32,46) = 1024 >> 4, version 1 [46,48), layout type 2 = 128-byte swizzle [61,64).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)64 << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::tf32: D float32 (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2), both K-major,
+// N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__device__ __forceinline__ uint32_t umma_idesc_tf32(int M, int N) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+// byte offset of the 16-byte chunk c (0..7) of row r inside a swizzled image
+__device__ __host__ __forceinline__ int sw128_offset(int r, int c) {
+  return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+}
+
+// ---- tile bookkeeping ----------------------------------------------------------------------------
+struct Tile {
+  bool valid;
+  int64_t row0;       // PLAIN: first row; LINEAR: first local row of the (element, l) problem
+  int64_t seg_begin;  // LINEAR: first slot of the element in node_order
+  int64_t seg_rows;   // LINEAR: rows of the problem
+  int l, nl, mat, ntile;
+};
+
+__device__ __forceinline__ Tile locate_tile(const GemmArgs &g, int64_t t) {
+  Tile T;
+  T.valid = false;
+  T.l = 0;
+  T.nl = 1;
+  T.mat = 0;
+  T.seg_begin = 0;
+  T.seg_rows = 0;
+  T.ntile = (int)(t % g.n_tiles);
+  int64_t rt = t / g.n_tiles;
+  if (g.mode == GT_MODE_PLAIN) {
+    T.row0 = rt * GT_TILE_M;
+    T.valid = T.row0 < g.M;
+    T.seg_rows = g.M;
+    return T;
+  }
+  for (int l = 0; l < 4; l++) {
+    const int nl = 2 * l + 1;
+    for (int z = 0; z < g.nelements; z++) {
+      const int64_t b = g.elem_start ? g.elem_start[z] : 0;
+      const int64_t cnt = g.elem_start ? (int64_t)g.elem_start[z + 1] - b : g.M;
+      const int64_t tiles = (cnt * nl + GT_TILE_M - 1) / GT_TILE_M;
+      if (rt < tiles) {
+        T.valid = true;
+        T.row0 = rt * GT_TILE_M;
+        T.seg_begin = b;
+        T.seg_rows = cnt * nl;
+        T.l = l;
+        T.nl = nl;
+        T.mat = z * 4 + l;
+        return T;
+      }
+      rt -= tiles;
+    }
+  }
+  return T;
+}
+
+// global row (in units of rows of A / out) of local row r of a tile, or -1
+__device__ __forceinline__ int64_t global_row(const GemmArgs &g, const Tile &T, int r) {
+  const int64_t lr = T.row0 + r;
+  if (lr >= T.seg_rows) return -1;
+  if (g.mode == GT_MODE_PLAIN) return lr;
+  const int64_t slot = T.seg_begin + lr / T.nl;
+  const int64_t node = g.node_order ? (int64_t)g.node_order[slot] : slot;
+  return node * 16 + T.l * T.l + (lr % T.nl);
+}
+
+__device__ __forceinline__ void report(const GemmArgs &g, int code) {
+  if (g.status) atomicCAS(g.status, 0, code);
+}
+
+__global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmArgs g) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bars[2 * GT_STAGES + 4];
+  __shared__ uint32_t tmem_base_slot;
+
+  // dynamic smem base rounded up to 1024 bytes (the swizzle pattern repeats every 1024 bytes)
+  const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
+  const uint32_t full_bar = smem_u32(&bars[0]);                 // + 8*s
+  const uint32_t empty_bar = smem_u32(&bars[GT_STAGES]);        // + 8*s
+  const uint32_t acc_full = smem_u32(&bars[2 * GT_STAGES]);     // + 8*a
+  const uint32_t acc_empty = smem_u32(&bars[2 * GT_STAGES + 2]);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GT_STAGES; s++) {
+      mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS * 32 + 1);   // producer threads + the expect_tx arrival
+      mbar_init(empty_bar + 8 * s, 1);        // one tcgen05.commit
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(acc_full + 8 * a, 1);         // one tcgen05.commit
+      mbar_init(acc_empty + 8 * a, 128);      // 128 epilogue threads
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == GT_PRODUCER_WARPS) tmem_alloc(smem_u32(&tmem_base_slot), GT_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int k_blocks = g.k_blocks;
+  const uint32_t b_image = (uint32_t)g.npad * 128u;  // bytes of one B image
+
+  if (warp < GT_PRODUCER_WARPS) {
+    // ================================ producers ================================
+    // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  The loads of the
+    // next item are issued into a second register set before the current one is converted and stored,
+    // so two stages of global loads are in flight per thread (HBM latency is about a microsecond).
+    const int p = threadIdx.x;       // 0..255
+    const int chunk = p & 7;         // 16-byte chunk of the 128-byte row segment
+    const int rbase = p >> 3;        // rows rbase + 32 i
+    struct Cursor {
+      int64_t t;
+      Tile T;
+      int kb;
+      bool valid;
+      int64_t grow[GT_ROWS_PER_THREAD];
+    };
+    auto advance = [&](Cursor &c) {
+      if (++c.kb < k_blocks && c.valid) return;
+      c.kb = 0;
+      for (;;) {
+        c.t += gridDim.x;
+        if (c.t >= g.total_tiles) {
+          c.valid = false;
+          return;
+        }
+        c.T = locate_tile(g, c.t);
+        if (c.T.valid) break;
+      }
+      c.valid = true;
+#pragma unroll
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) c.grow[i] = global_row(g, c.T, rbase + 32 * i);
+    };
+    auto issue = [&](const Cursor &c, float4 (&v)[GT_ROWS_PER_THREAD]) {
+      const int k0 = c.kb * GT_KBLOCK + chunk * 4;
+#pragma unroll
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c.grow[i] >= 0 && k0 < g.K) v[i] = __ldg(reinterpret_cast<const float4 *>(g.A + c.grow[i] * g.K + k0));
+      }
+    };
+    int stage = 0;
+    uint32_t phase = 0;
+    // returns false on a timed-out wait
+    auto commit = [&](const Cursor &c, const float4 (&v)[GT_ROWS_PER_THREAD]) -> bool {
+      if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1)) {
+        report(g, 1);
+        return false;
+      }
+      const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+      if (p == 0) {
+        const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
+                                    ((int64_t)(c.T.mat * g.n_tiles + c.T.ntile) * k_blocks + c.kb) *
+                                        (2 * (int64_t)b_image);
+        mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
+        bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
+      }
+#pragma unroll
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
+        const int r = rbase + 32 * i;
+        float4 hi, lo;
+        hi.x = to_tf32(v[i].x); lo.x = to_tf32(v[i].x - hi.x);
+        hi.y = to_tf32(v[i].y); lo.y = to_tf32(v[i].y - hi.y);
+        hi.z = to_tf32(v[i].z); lo.z = to_tf32(v[i].z - hi.z);
+        hi.w = to_tf32(v[i].w); lo.w = to_tf32(v[i].w - hi.w);
+        const uint32_t off = (uint32_t)sw128_offset(r, chunk);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(hi.x), "f"(hi.y), "f"(hi.z),
+                     "f"(hi.w)
+                     : "memory");
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + GT_A_SLAB + off), "f"(lo.x), "f"(lo.y),
+                     "f"(lo.z), "f"(lo.w)
+                     : "memory");
+      }
+      fence_proxy_async();
+      mbar_arrive(full_bar + 8 * stage);
+      if (++stage == GT_STAGES) {
+        stage = 0;
+        phase ^= 1;
+      }
+      return true;
+    };
+
+    Cursor ca;
+    ca.t = (int64_t)blockIdx.x - gridDim.x;
+    ca.kb = k_blocks;  // forces advance() to step to the first tile
+    ca.valid = false;
+    advance(ca);
+    float4 va[GT_ROWS_PER_THREAD], vb[GT_ROWS_PER_THREAD];
+    if (ca.valid) issue(ca, va);
+    while (ca.valid) {
+      Cursor cb = ca;
+      advance(cb);
+      if (cb.valid) issue(cb, vb);
+      if (!commit(ca, va)) break;
+      if (!cb.valid) break;
+      ca = cb;
+      advance(ca);
+      if (ca.valid) issue(ca, va);
+      if (!commit(cb, vb)) break;
+    }
+  } else if (warp == GT_PRODUCER_WARPS) {
+    // ================================ MMA issuer ================================
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    int acc = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
+      const Tile T = locate_tile(g, t);
+      if (!T.valid) continue;
+      int ncols = g.N - T.ntile * 128;
+      ncols = ncols > 128 ? 128 : ncols;
+      const int nmma = (ncols + 15) & ~15;
+      const uint32_t idesc = umma_idesc_tf32(GT_TILE_M, nmma);
+      if (!mbar_wait(acc_empty + 8 * acc, acc_phase[acc] ^ 1)) {
+        report(g, 2);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * 128;
+      for (int kb = 0; kb < k_blocks; kb++) {
+        if (!mbar_wait(full_bar + 8 * stage, phase)) {
+          report(g, 3);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+          const uint32_t sB = sA + 2 * GT_A_SLAB;
+          int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
+          ksteps = ksteps > 4 ? 4 : ksteps;
+          for (int j = 0; j < ksteps; j++) {
+            const uint64_t a_hi = umma_desc_sw128(sA + j * 32);
+            const uint64_t a_lo = umma_desc_sw128(sA + GT_A_SLAB + j * 32);
+            const uint64_t b_hi = umma_desc_sw128(sB + j * 32);
+            const uint64_t b_lo = umma_desc_sw128(sB + b_image + j * 32);
+            umma_tf32(d_tmem, a_lo, b_hi, idesc, (kb | j) != 0);
+            umma_tf32(d_tmem, a_hi, b_lo, idesc, 1);
+            umma_tf32(d_tmem, a_hi, b_hi, idesc, 1);
+          }
+          umma_commit(empty_bar + 8 * stage);
+          if (kb == k_blocks - 1) umma_commit(acc_full + 8 * acc);
+        }
+        __syncwarp();
+        if (++stage == GT_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      acc_phase[acc] ^= 1;
+      acc ^= 1;
+    }
+  } else {
+    // ================================ epilogue ================================
+    const int q = warp & 3;                 // tensor-memory lane quarter this warp may read
+    const int r = q * 32 + lane;            // row of the tile
+    uint32_t acc_phase[2] = {0, 0};
+    int acc = 0;
+    for (int64_t t = blockIdx.x; t < g.total_tiles; t += gridDim.x) {
+      const Tile T = locate_tile(g, t);
+      if (!T.valid) continue;
+      const int64_t grow = global_row(g, T, r);
+      const int n0 = T.ntile * 128;
+      int ncols = g.N - n0;
+      ncols = ncols > 128 ? 128 : ncols;
+      if (!mbar_wait(acc_full + 8 * acc, acc_phase[acc])) {
+        report(g, 4);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * 128 + ((uint32_t)(q * 32) << 16);
+      for (int c0 = 0; c0 < ncols; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c0, v);
+        if (grow >= 0) {
+          float *dst = g.out + grow * g.N + n0 + c0;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            if (c0 + i < ncols) {
+              float4 o;
+              o.x = __uint_as_float(v[i]) * g.scale;
+              o.y = __uint_as_float(v[i + 1]) * g.scale;
+              o.z = __uint_as_float(v[i + 2]) * g.scale;
+              o.w = __uint_as_float(v[i + 3]) * g.scale;
+              *reinterpret_cast<float4 *>(dst + i) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty + 8 * acc);
+      acc_phase[acc] ^= 1;
+      acc ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == GT_PRODUCER_WARPS) tmem_dealloc(tmem_base, GT_TMEM_COLS);
+}
+
+// ---- weight packing ---------------------------------------------------------------------------------
+// Bt [nmat, N, K] (K contiguous, i.e. the transpose of each B) -> per matrix, per N tile, per K block:
+// hi image then lo image, each npad rows x 128 bytes in the swizzled layout, zero padded.
+__global__ void pack_weights_kernel(const float *__restrict__ Bt, int nmat, int N, int K, int n_tiles, int k_blocks,
+                                    int npad, float *__restrict__ packed) {
+  const int64_t total = (int64_t)nmat * n_tiles * k_blocks * npad * 8;  // one thread per 16-byte chunk
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = (int)(i % 8);
+  const int r = (int)((i / 8) % npad);
+  const int kb = (int)((i / (8 * (int64_t)npad)) % k_blocks);
+  const int nt = (int)((i / (8 * (int64_t)npad * k_blocks)) % n_tiles);
+  const int m = (int)(i / (8 * (int64_t)npad * k_blocks * n_tiles));
+  const int n = nt * 128 + r;
+  float hi[4], lo[4];
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    const int k = kb * GT_KBLOCK + c * 4 + u;
+    const float x = (n < N && r < 128 && k < K) ? Bt[((int64_t)m * N + n) * K + k] : 0.f;
+    hi[u] = to_tf32(x);
+    lo[u] = to_tf32(x - hi[u]);
+  }
+  const int64_t image = (int64_t)npad * 32;  // floats per image
+  float *base = packed + (((int64_t)(m * n_tiles + nt) * k_blocks + kb) * 2) * image;
+  const int off = sw128_offset(r, c) / 4;
+  *reinterpret_cast<float4 *>(base + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+  *reinterpret_cast<float4 *>(base + image + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+}
+
+struct PackGeom {
+  int n_tiles, k_blocks, npad;
+  int64_t floats_per_matrix;
+};
+static PackGeom pack_geom(int N, int K) {
+  PackGeom p;
+  p.n_tiles = (N + 127) / 128;
+  p.k_blocks = (K + GT_KBLOCK - 1) / GT_KBLOCK;
+  const int widest = N > 128 ? 128 : N;
+  p.npad = (widest + 15) & ~15;
+  p.floats_per_matrix = (int64_t)p.n_tiles * p.k_blocks * 2 * p.npad * 32;
+  return p;
+}
+
+static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (num_sms <= 0) num_sms = 148;
+  }
+  const size_t smem = (size_t)GT_STAGES * GT_STAGE_BYTES + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm3x_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  int64_t blocks = g.total_tiles < num_sms ? g.total_tiles : num_sms;
+  if (blocks < 1) return CMACE_OK;
+  gemm3x_tf32_kernel<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g);
+  return check_launch(what);
+}
+
+}  // namespace cmace
+
+using namespace cmace;
+
+extern "C" {
+
+int64_t cmace_gemm_packed_floats(int nmat, int N, int K) {
+  if (nmat < 1 || N < 1 || K < 1) return 0;
+  return (int64_t)nmat * pack_geom(N, K).floats_per_matrix;
+}
+
+int cmace_gemm_pack_weights_f32(const float *Bt, int nmat, int N, int K, float *packed, cmace_stream_t stream) {
+  if (!Bt || !packed || nmat < 1 || N < 1 || K < 1) return fail(CMACE_ERR_ARG, "cmace_gemm_pack_weights: bad argument");
+  if (!aligned16(packed)) return fail(CMACE_ERR_ARG, "cmace_gemm_pack_weights: packed must be 16-byte aligned");
+  const PackGeom p = pack_geom(N, K);
+  const int64_t total = (int64_t)nmat * p.n_tiles * p.k_blocks * p.npad * 8;
+  pack_weights_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(Bt, nmat, N, K, p.n_tiles,
+                                                                                        p.k_blocks, p.npad, packed);
+  return check_launch("cmace_gemm_pack_weights");
+}
+
+int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale, float *out,
+                     int32_t *status, cmace_stream_t stream) {
+  if (M < 0 || K < 1 || N < 1) return fail(CMACE_ERR_ARG, "cmace_gemm3x: bad size");
+  if (K % 4 != 0 || N % 4 != 0) return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm3x: K and N must be multiples of 4");
+  if (M == 0) return CMACE_OK;
+  if (!A || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_gemm3x: null pointer");
+  if (!aligned16(A) || !aligned16(packed) || !aligned16(out))
+    return fail(CMACE_ERR_ARG, "cmace_gemm3x: pointers must be 16-byte aligned");
+  const PackGeom p = pack_geom(N, K);
+  GemmArgs g{};
+  g.A = A; g.packed = packed; g.out = out; g.status = status;
+  g.M = M; g.K = K; g.N = N; g.nelements = 1; g.mode = GT_MODE_PLAIN; g.scale = (float)scale;
+  g.n_tiles = p.n_tiles; g.k_blocks = p.k_blocks; g.npad = p.npad;
+  g.total_tiles = ((M + GT_TILE_M - 1) / GT_TILE_M) * p.n_tiles;
+  return gemm_launch(g, "cmace_gemm3x", (cudaStream_t)stream);
+}
+
+int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node_order, const int32_t *elem_start,
+                        int nelements, int64_t nnodes, int K, int Nout, double scale, float *out, int32_t *status,
+                        cmace_stream_t stream) {
+  if (nnodes < 0 || K < 1 || Nout < 1 || nelements < 1) return fail(CMACE_ERR_ARG, "cmace_linear_tc: bad size");
+  if (K % 4 != 0 || Nout % 4 != 0 || Nout > 128)
+    return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: K, Nout multiples of 4 and Nout <= 128");
+  if (nnodes == 0) return CMACE_OK;
+  if (!X || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_linear_tc: null pointer");
+  if ((nelements > 1) != (node_order != nullptr) || (node_order != nullptr) != (elem_start != nullptr))
+    return fail(CMACE_ERR_ARG, "cmace_linear_tc: node_order and elem_start go together with nelements > 1");
+  if (!aligned16(X) || !aligned16(packed) || !aligned16(out))
+    return fail(CMACE_ERR_ARG, "cmace_linear_tc: pointers must be 16-byte aligned");
+  const PackGeom p = pack_geom(Nout, K);
+  GemmArgs g{};
+  g.A = X; g.packed = packed; g.out = out; g.status = status;
+  g.node_order = node_order; g.elem_start = elem_start;
+  g.M = nnodes; g.K = K; g.N = Nout; g.nelements = nelements; g.mode = GT_MODE_LINEAR; g.scale = (float)scale;
+  g.n_tiles = p.n_tiles; g.k_blocks = p.k_blocks; g.npad = p.npad;
+  g.total_tiles = (nnodes * 16 + GT_TILE_M - 1) / GT_TILE_M + 4 * (int64_t)nelements;
+  return gemm_launch(g, "cmace_linear_tc", (cudaStream_t)stream);
+}
+}

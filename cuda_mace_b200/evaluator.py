@@ -74,4 +74,5 @@ class EnergyForceEvaluator:
             out_forces = torch.empty(forces.shape, dtype=forces.dtype, pin_memory=torch.cuda.is_available())
         out_forces.copy_(forces, non_blocking=True)
         e = float(energy.cpu())  # synchronises
+        ops.check_status()
         return e, out_forces

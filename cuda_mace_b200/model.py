@@ -53,7 +53,9 @@ class InvariantMACE(torch.nn.Module):
             L = torch.nn.Module()
             L.register_buffer("W_up", (P["W_up"] / math.sqrt(C)).to(**dd))
             for i, W in enumerate(P["W_radial"]):
-                L.register_buffer(f"W_radial{i}", (W / math.sqrt(W.shape[0])).to(**dd))
+                Wn = (W / math.sqrt(W.shape[0])).to(**dd)
+                L.register_buffer(f"W_radial{i}", Wn)
+                L.register_buffer(f"W_radial{i}_T", Wn.t().contiguous())
             L.n_radial = len(P["W_radial"])
             L.linear = ops.Linear(P["W_lin"].to(**dd), scale=1.0 / float(P["avg_num_neighbors"]))
             if t == 0:
@@ -89,7 +91,11 @@ class InvariantMACE(torch.nn.Module):
             return L.spline(lengths)
         h = bessel
         for i in range(L.n_radial):
-            h = h @ getattr(L, f"W_radial{i}")
+            W = getattr(L, f"W_radial{i}")
+            if ops.tensor_core_ok(h.dtype, W.shape[0], W.shape[1]):
+                h = ops.matmul3x(h, W, getattr(L, f"W_radial{i}_T"))
+            else:
+                h = h @ W
             if i + 1 < L.n_radial:
                 h = _silu_n(h)
         return h

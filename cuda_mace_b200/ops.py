@@ -74,6 +74,80 @@ class _RefCache:
 
 
 # --------------------------------------------------------------------------------------
+# float32 tensor-core GEMM (tcgen05, 3-term TF32 split)
+# --------------------------------------------------------------------------------------
+_status = {}          # device index -> int32[1] written by kernels whose bounded waits time out
+_packed_cache = _RefCache(32)
+USE_TENSOR_CORES = True   # float32 Linear / ElementalLinear / matmul3x go through tcgen05 when shapes allow
+
+
+def _status_tensor(device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_status():
+    """Raises if any tensor-core kernel reported a timed-out wait since the last check (synchronises)."""
+    for idx, t in _status.items():
+        code = int(t.item())
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(f"cuda_mace_b200: a tensor-core kernel on cuda:{idx} gave up waiting (code {code})")
+
+
+def _pack(Bt):
+    """Packs Bt [nmat, N, K] (or [N, K]) float32, K contiguous, into the tensor-core weight image (cached)."""
+    key = _RefCache.key(Bt)
+    hit = _packed_cache.get(key)
+    if hit is not None:
+        return hit
+    B3 = Bt.reshape(-1, Bt.shape[-2], Bt.shape[-1]).contiguous()
+    nmat, N, K = B3.shape
+    n = _abi.call("cmace_gemm_packed_floats", nmat, N, K)
+    packed = torch.empty(int(n), dtype=torch.float32, device=Bt.device)
+    _abi.call("cmace_gemm_pack_weights_f32", _ptr(B3), nmat, N, K, _ptr(packed), _stream())
+    return _packed_cache.put(key, (Bt,), packed)
+
+
+def _gemm3x(A, Bt, scale=1.0):
+    """A [M,K] @ B with Bt = B^T [N,K]; float32 in, float32 out."""
+    A = A.contiguous()
+    M, K = A.shape
+    N = Bt.shape[0]
+    out = torch.empty(M, N, dtype=torch.float32, device=A.device)
+    _abi.call("cmace_gemm3x_f32", _ptr(A), _ptr(_pack(Bt)), M, K, N, float(scale), _ptr(out),
+              _ptr(_status_tensor(A.device)), _stream())
+    return out
+
+
+class _Matmul3xFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, A, W, W_T):
+        ctx.save_for_backward(W)
+        return _gemm3x(A, W_T)
+
+    @staticmethod
+    def backward(ctx, G):
+        (W,) = ctx.saved_tensors
+        return _gemm3x(G, W), None, None
+
+
+def matmul3x(A, W, W_T=None):
+    """A [M,K] @ W [K,N] for a constant float32 weight W (no weight gradient), on the tensor cores with
+    float32-grade accuracy.  W_T = W^T contiguous may be passed to avoid re-creating it."""
+    _check_cuda(A, W)
+    if W_T is None:
+        W_T = W.t().contiguous()
+    return _Matmul3xFunction.apply(A, W, W_T)
+
+
+def tensor_core_ok(dtype, K, N):
+    return USE_TENSOR_CORES and dtype == torch.float32 and K % 4 == 0 and N % 4 == 0
+
+
+# --------------------------------------------------------------------------------------
 # edge topology
 # --------------------------------------------------------------------------------------
 class EdgeTopology:
@@ -185,7 +259,9 @@ class InvariantMessagePassingTP(torch.nn.Module):
 # --------------------------------------------------------------------------------------
 # Linear / ElementalLinear
 # --------------------------------------------------------------------------------------
-def _linear_call(X, W, node_order, elem_start, nelements, scale):
+def _linear_call(X, W, W_other, node_order, elem_start, nelements, scale):
+    """out = scale * X @ W[z, l] per row; W_other is the transposed copy of W (the tensor-core path
+    packs it, since it wants B^T with K contiguous)."""
     X = X.contiguous()
     N, K = X.shape[0], X.shape[2]
     Nout = W.shape[-1]
@@ -194,6 +270,10 @@ def _linear_call(X, W, node_order, elem_start, nelements, scale):
     if W.dtype != X.dtype:
         raise TypeError("X and W must have the same dtype")
     out = torch.empty(N, 16, Nout, dtype=X.dtype, device=X.device)
+    if tensor_core_ok(X.dtype, K, Nout) and Nout <= 128:
+        _abi.call("cmace_linear_tc_f32", _ptr(X), _ptr(_pack(W_other)), _ptr(node_order), _ptr(elem_start),
+                  nelements, N, K, Nout, float(scale), _ptr(out), _ptr(_status_tensor(X.device)), _stream())
+        return out
     _abi.call("cmace_linear_" + _suffix(X), _ptr(X), _ptr(W.contiguous()), _ptr(node_order), _ptr(elem_start),
               nelements, N, K, Nout, float(scale), _ptr(out), _stream())
     return out
@@ -202,16 +282,16 @@ def _linear_call(X, W, node_order, elem_start, nelements, scale):
 class _LinearFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, X, W, W_T, node_order, elem_start, nelements):
-        ctx.save_for_backward(W_T)
+        ctx.save_for_backward(W, W_T)
         scale = 1.0 / math.sqrt(X.shape[2])  # the path weight of linear_impl.cu:33
         ctx.grouping = (node_order, elem_start, nelements, scale)
-        return _linear_call(X, W, node_order, elem_start, nelements, scale)
+        return _linear_call(X, W, W_T, node_order, elem_start, nelements, scale)
 
     @staticmethod
     def backward(ctx, G):
-        (W_T,) = ctx.saved_tensors
+        W, W_T = ctx.saved_tensors
         node_order, elem_start, nelements, scale = ctx.grouping
-        return _linear_call(G, W_T, node_order, elem_start, nelements, scale), None, None, None, None, None
+        return _linear_call(G, W_T, W, node_order, elem_start, nelements, scale), None, None, None, None, None
 
 
 def linear_forward(X, W, W_T):

@@ -147,6 +147,24 @@ int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order
                      const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
                      double scale, double *out, cmace_stream_t stream);
 
+/* ---- float32 tensor-core path (tcgen05, kind::tf32 with a 3-term hi/lo split, TMEM accumulator) -----
+ * The reference runs Linear / ElementalLinear on wmma TF32 with the same 3-term error compensation
+ * (cuda/src/linear_impl.cu:85-101).  Weights are packed once into the shared-memory image the tensor
+ * core reads: Bt [nmat, N, K] is the TRANSPOSE of each [K, N] weight matrix (K contiguous), i.e. W_T for
+ * the forward of Linear and W for its backward.  packed needs cmace_gemm_packed_floats(nmat, N, K) floats.
+ * cmace_linear_tc_f32 has the contract of cmace_linear_f32 (Nout <= 128); cmace_gemm3x_f32 is the plain
+ * out[M,N] = scale * A[M,K] @ B used for the radial multilayer perceptron (which upstream MACE evaluates
+ * with torch and the reference replaces by its spline table, models/InvariantMACE.py:226-240).
+ * status: optional device int32, set non-zero if a bounded wait inside the kernel timed out. */
+int64_t cmace_gemm_packed_floats(int nmat, int N, int K);
+int cmace_gemm_pack_weights_f32(const float *Bt, int nmat, int N, int K, float *packed,
+                                cmace_stream_t stream);
+int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale,
+                     float *out, int32_t *status, cmace_stream_t stream);
+int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node_order,
+                        const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
+                        double scale, float *out, int32_t *status, cmace_stream_t stream);
+
 /* ---- symmetric contraction (correlation 3, invariant output) ------------------------------
  * Replace jit_symmetric_contraction_forward / _backward
  * (jit_wrappers/src/symmetric_contraction_wrapper.cpp:15-205, kernels

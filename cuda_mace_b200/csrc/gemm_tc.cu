@@ -25,21 +25,31 @@
 //
 // Every wait on an mbarrier is bounded; on a time-out the role records a code in *status and leaves
 // its loop, the others time out in turn, and the CTA still frees its tensor memory and returns.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cmace {
 
-constexpr int GT_STAGES = 3;
+constexpr int GT_MAX_STAGES = 8;
 constexpr int GT_TILE_M = 128;
 constexpr int GT_KBLOCK = 32;                       // floats per K block = one 128-byte swizzle row
 constexpr int GT_A_SLAB = GT_TILE_M * 128;          // bytes of one A image (hi or lo) per stage
 constexpr int GT_B_SLAB_MAX = 128 * 128;            // bytes of one B image per stage at N tile = 128
-constexpr int GT_STAGE_BYTES = 2 * GT_A_SLAB + 2 * GT_B_SLAB_MAX;
 constexpr int GT_PRODUCER_WARPS = 8;
 constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
 constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + 4) * 32;
+constexpr int GT_SMEM_BUDGET = 227 * 1024;           // dynamic shared memory a CTA may opt in to
 constexpr int GT_TMEM_COLS = 256;
+constexpr int GT_PREFETCH = 2;                      // K blocks of global loads in flight per producer thread
+constexpr int GT_EP_STRIDE = 36;                    // floats per row of the epilogue transpose buffer (padded)
+constexpr int GT_EP_BYTES = 4 * 32 * GT_EP_STRIDE * 4;
 constexpr long long GT_TIMEOUT_CYCLES = 4000000000LL;  // about two seconds
+#ifdef CMACE_GEMM_DEBUG
+#define GT_DBG(g, bit) (((g).debug & (bit)) != 0)
+#else
+#define GT_DBG(g, bit) false
+#endif
 
 enum { GT_MODE_PLAIN = 0, GT_MODE_LINEAR = 1 };
 
@@ -57,6 +67,8 @@ struct GemmArgs {
   float scale;
   int n_tiles, k_blocks, npad;  // packing geometry: N tiles of <= 128 columns, npad rows per B image
   int64_t total_tiles;          // upper bound of the tile index space
+  int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
+  int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -73,6 +85,15 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#ifdef CMACE_GEMM_TESTWAIT
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -80,6 +101,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 // bounded wait: false after GT_TIMEOUT_CYCLES
@@ -210,9 +232,11 @@ __device__ __forceinline__ int64_t global_row(const GemmArgs &g, const Tile &T, 
   const int64_t lr = T.row0 + r;
   if (lr >= T.seg_rows) return -1;
   if (g.mode == GT_MODE_PLAIN) return lr;
-  const int64_t slot = T.seg_begin + lr / T.nl;
+  // rows of one (element, l) problem fit 32 bits (checked on the host): cheap division
+  const uint32_t lr32 = (uint32_t)lr, q = lr32 / (uint32_t)T.nl;
+  const int64_t slot = T.seg_begin + q;
   const int64_t node = g.node_order ? (int64_t)g.node_order[slot] : slot;
-  return node * 16 + T.l * T.l + (lr % T.nl);
+  return node * 16 + T.l * T.l + (int)(lr32 - q * (uint32_t)T.nl);
 }
 
 __device__ __forceinline__ void report(const GemmArgs &g, int code) {
@@ -221,26 +245,28 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 
 __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmArgs g) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[2 * GT_STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * GT_MAX_STAGES + 4];
   __shared__ uint32_t tmem_base_slot;
 
   // dynamic smem base rounded up to 1024 bytes (the swizzle pattern repeats every 1024 bytes)
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
   const uint32_t full_bar = smem_u32(&bars[0]);                 // + 8*s
-  const uint32_t empty_bar = smem_u32(&bars[GT_STAGES]);        // + 8*s
-  const uint32_t acc_full = smem_u32(&bars[2 * GT_STAGES]);     // + 8*a
-  const uint32_t acc_empty = smem_u32(&bars[2 * GT_STAGES + 2]);
+  const uint32_t empty_bar = smem_u32(&bars[GT_MAX_STAGES]);        // + 8*s
+  const uint32_t acc_full = smem_u32(&bars[2 * GT_MAX_STAGES]);     // + 8*a
+  const uint32_t acc_empty = smem_u32(&bars[2 * GT_MAX_STAGES + 2]);
+  const int GT_STAGES = g.stages;
+  const uint32_t GT_STAGE_BYTES = (uint32_t)g.stage_bytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GT_STAGES; s++) {
-      mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS * 32 + 1);   // producer threads + the expect_tx arrival
+      mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS + 1);   // one arrival per producer warp + the expect_tx arrival
       mbar_init(empty_bar + 8 * s, 1);        // one tcgen05.commit
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(acc_full + 8 * a, 1);         // one tcgen05.commit
-      mbar_init(acc_empty + 8 * a, 128);      // 128 epilogue threads
+      mbar_init(acc_empty + 8 * a, 4);        // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -255,59 +281,71 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
 
   if (warp < GT_PRODUCER_WARPS) {
     // ================================ producers ================================
-    // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  The loads of the
-    // next item are issued into a second register set before the current one is converted and stored,
-    // so two stages of global loads are in flight per thread (HBM latency is about a microsecond).
+    // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
+    // GT_PREFETCH items ahead of the conversion in a register ring, so that enough bytes are in flight
+    // per SM to cover HBM latency (about a microsecond) independently of the shared-memory ring depth.
     const int p = threadIdx.x;       // 0..255
     const int chunk = p & 7;         // 16-byte chunk of the 128-byte row segment
     const int rbase = p >> 3;        // rows rbase + 32 i
-    struct Cursor {
+    // head: the next (tile, K block) item whose loads have not been issued yet
+    struct Head {
       int64_t t;
       Tile T;
       int kb;
       bool valid;
       int64_t grow[GT_ROWS_PER_THREAD];
-    };
-    auto advance = [&](Cursor &c) {
-      if (++c.kb < k_blocks && c.valid) return;
-      c.kb = 0;
+    } head;
+    auto advance = [&]() {
+      if (++head.kb < k_blocks && head.valid) return;
+      head.kb = 0;
       for (;;) {
-        c.t += gridDim.x;
-        if (c.t >= g.total_tiles) {
-          c.valid = false;
+        head.t += gridDim.x;
+        if (head.t >= g.total_tiles) {
+          head.valid = false;
           return;
         }
-        c.T = locate_tile(g, c.t);
-        if (c.T.valid) break;
+        head.T = locate_tile(g, head.t);
+        if (head.T.valid) break;
       }
-      c.valid = true;
+      head.valid = true;
 #pragma unroll
-      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) c.grow[i] = global_row(g, c.T, rbase + 32 * i);
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row(g, head.T, rbase + 32 * i);
     };
-    auto issue = [&](const Cursor &c, float4 (&v)[GT_ROWS_PER_THREAD]) {
-      const int k0 = c.kb * GT_KBLOCK + chunk * 4;
+    // an item in flight only has to remember where its B block lives (-1: no item)
+    auto issue = [&](float4 (&v)[GT_ROWS_PER_THREAD]) -> int64_t {
+      if (!head.valid) return -1;
+      const int k0 = head.kb * GT_KBLOCK + chunk * 4;
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c.grow[i] >= 0 && k0 < g.K) v[i] = __ldg(reinterpret_cast<const float4 *>(g.A + c.grow[i] * g.K + k0));
+        if (head.grow[i] >= 0 && k0 < g.K && !GT_DBG(g, 1))
+          v[i] = __ldg(reinterpret_cast<const float4 *>(g.A + head.grow[i] * g.K + k0));
       }
+      const int64_t bblock = (int64_t)(head.T.mat * g.n_tiles + head.T.ntile) * k_blocks + head.kb;
+      advance();
+      return bblock;
     };
     int stage = 0;
     uint32_t phase = 0;
     // returns false on a timed-out wait
-    auto commit = [&](const Cursor &c, const float4 (&v)[GT_ROWS_PER_THREAD]) -> bool {
-      if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1)) {
+    auto commit = [&](int64_t bblock, const float4 (&v)[GT_ROWS_PER_THREAD]) -> bool {
+      // lane 0 polls the barrier for the warp
+      uint32_t got = 1;
+      if (lane == 0) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
         report(g, 1);
         return false;
       }
       const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-      if (p == 0) {
-        const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
-                                    ((int64_t)(c.T.mat * g.n_tiles + c.T.ntile) * k_blocks + c.kb) *
-                                        (2 * (int64_t)b_image);
+      if (p == 0 && GT_DBG(g, 8)) mbar_arrive(full_bar + 8 * stage);
+      if (p == 0 && !GT_DBG(g, 8)) {
+        const unsigned char *bsrc =
+            reinterpret_cast<const unsigned char *>(g.packed) + bblock * (2 * (int64_t)b_image);
         mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
         bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
       }
+      if (!GT_DBG(g, 16))
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
         const int r = rbase + 32 * i;
@@ -325,7 +363,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
                      : "memory");
       }
       fence_proxy_async();
-      mbar_arrive(full_bar + 8 * stage);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar + 8 * stage);
       if (++stage == GT_STAGES) {
         stage = 0;
         phase ^= 1;
@@ -333,23 +372,24 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       return true;
     };
 
-    Cursor ca;
-    ca.t = (int64_t)blockIdx.x - gridDim.x;
-    ca.kb = k_blocks;  // forces advance() to step to the first tile
-    ca.valid = false;
-    advance(ca);
-    float4 va[GT_ROWS_PER_THREAD], vb[GT_ROWS_PER_THREAD];
-    if (ca.valid) issue(ca, va);
-    while (ca.valid) {
-      Cursor cb = ca;
-      advance(cb);
-      if (cb.valid) issue(cb, vb);
-      if (!commit(ca, va)) break;
-      if (!cb.valid) break;
-      ca = cb;
-      advance(ca);
-      if (ca.valid) issue(ca, va);
-      if (!commit(cb, vb)) break;
+    head.t = (int64_t)blockIdx.x - gridDim.x;
+    head.kb = k_blocks;  // forces advance() to step to the first tile
+    head.valid = false;
+    advance();
+    // register ring: GT_PREFETCH items of global loads in flight per thread
+    float4 buf[GT_PREFETCH][GT_ROWS_PER_THREAD];
+    int64_t inflight[GT_PREFETCH];
+#pragma unroll
+    for (int d = 0; d < GT_PREFETCH; d++) inflight[d] = issue(buf[d]);
+    for (bool run = true; run;) {
+#pragma unroll
+      for (int d = 0; d < GT_PREFETCH; d++) {
+        if (inflight[d] < 0 || !commit(inflight[d], buf[d])) {
+          run = false;
+          break;
+        }
+        inflight[d] = issue(buf[d]);
+      }
     }
   } else if (warp == GT_PRODUCER_WARPS) {
     // ================================ MMA issuer ================================
@@ -365,35 +405,45 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       ncols = ncols > 128 ? 128 : ncols;
       const int nmma = (ncols + 15) & ~15;
       const uint32_t idesc = umma_idesc_tf32(GT_TILE_M, nmma);
-      if (!mbar_wait(acc_empty + 8 * acc, acc_phase[acc] ^ 1)) {
+      uint32_t got = 1;
+      if (lane == 0) got = mbar_wait(acc_empty + 8 * acc, acc_phase[acc] ^ 1) ? 1u : 0u;
+      if (!__shfl_sync(0xffffffffu, got, 0)) {
         report(g, 2);
         break;
       }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * 128;
       for (int kb = 0; kb < k_blocks; kb++) {
-        if (!mbar_wait(full_bar + 8 * stage, phase)) {
+        got = 1;
+        if (lane == 0 && !GT_DBG(g, 1024)) got = mbar_wait(full_bar + 8 * stage, phase) ? 1u : 0u;
+        if (!__shfl_sync(0xffffffffu, got, 0)) {
           report(g, 3);
           ok = false;
           break;
         }
-        tc_fence_after();
+        if (!GT_DBG(g, 512)) tc_fence_after();
         if (lane == 0) {
+          // descriptors of K step j differ from those of step 0 by j * 32 bytes = 2 address units
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-          const uint32_t sB = sA + 2 * GT_A_SLAB;
+          const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
+          const uint64_t b_hi0 = umma_desc_sw128(sA + 2 * GT_A_SLAB);
+          const uint64_t b_lo0 = umma_desc_sw128(sA + 2 * GT_A_SLAB + b_image);
           int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
           ksteps = ksteps > 4 ? 4 : ksteps;
+          if (GT_DBG(g, 2)) ksteps = 0;
           for (int j = 0; j < ksteps; j++) {
-            const uint64_t a_hi = umma_desc_sw128(sA + j * 32);
-            const uint64_t a_lo = umma_desc_sw128(sA + GT_A_SLAB + j * 32);
-            const uint64_t b_hi = umma_desc_sw128(sB + j * 32);
-            const uint64_t b_lo = umma_desc_sw128(sB + b_image + j * 32);
-            umma_tf32(d_tmem, a_lo, b_hi, idesc, (kb | j) != 0);
-            umma_tf32(d_tmem, a_hi, b_lo, idesc, 1);
-            umma_tf32(d_tmem, a_hi, b_hi, idesc, 1);
+            const uint64_t dj = (uint64_t)(2 * j);
+            umma_tf32(d_tmem, a_lo0 + dj, b_hi0 + dj, idesc, (kb | j) != 0);
+            umma_tf32(d_tmem, a_hi0 + dj, b_lo0 + dj, idesc, 1);
+            umma_tf32(d_tmem, a_hi0 + dj, b_hi0 + dj, idesc, 1);
           }
-          umma_commit(empty_bar + 8 * stage);
-          if (kb == k_blocks - 1) umma_commit(acc_full + 8 * acc);
+          if (GT_DBG(g, 128)) {
+            mbar_arrive(empty_bar + 8 * stage);
+            if (kb == k_blocks - 1) mbar_arrive(acc_full + 8 * acc);
+          } else {
+            umma_commit(empty_bar + 8 * stage);
+            if (kb == k_blocks - 1) umma_commit(acc_full + 8 * acc);
+          }
         }
         __syncwarp();
         if (++stage == GT_STAGES) {
@@ -407,6 +457,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
   } else {
     // ================================ epilogue ================================
     const int q = warp & 3;                 // tensor-memory lane quarter this warp may read
+    float *ep_buf = reinterpret_cast<float *>(smem + (smem_base - smem_u32(smem)) + GT_STAGES * GT_STAGE_BYTES) +
+                    q * 32 * GT_EP_STRIDE;
     const int r = q * 32 + lane;            // row of the tile
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
@@ -417,32 +469,42 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       const int n0 = T.ntile * 128;
       int ncols = g.N - n0;
       ncols = ncols > 128 ? 128 : ncols;
-      if (!mbar_wait(acc_full + 8 * acc, acc_phase[acc])) {
+      uint32_t got = 1;
+      if (lane == 0) got = mbar_wait(acc_full + 8 * acc, acc_phase[acc]) ? 1u : 0u;
+      if (!__shfl_sync(0xffffffffu, got, 0)) {
         report(g, 4);
         break;
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * 128 + ((uint32_t)(q * 32) << 16);
+      // rows of this warp (global index per lane), to be read by the lanes that store them
       for (int c0 = 0; c0 < ncols; c0 += 32) {
         uint32_t v[32];
+        if (GT_DBG(g, 64)) continue;
         tmem_ld32(taddr + c0, v);
-        if (grow >= 0) {
-          float *dst = g.out + grow * g.N + n0 + c0;
+        if (GT_DBG(g, 32)) continue;
+        // lane = row: write the row's 32 values, then read back 4 rows x 128 bytes per instruction
+        float *mine = ep_buf + lane * GT_EP_STRIDE;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            if (c0 + i < ncols) {
-              float4 o;
-              o.x = __uint_as_float(v[i]) * g.scale;
-              o.y = __uint_as_float(v[i + 1]) * g.scale;
-              o.z = __uint_as_float(v[i + 2]) * g.scale;
-              o.w = __uint_as_float(v[i + 3]) * g.scale;
-              *reinterpret_cast<float4 *>(dst + i) = o;
-            }
-          }
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4 *>(mine + i) =
+              make_float4(__uint_as_float(v[i]) * g.scale, __uint_as_float(v[i + 1]) * g.scale,
+                          __uint_as_float(v[i + 2]) * g.scale, __uint_as_float(v[i + 3]) * g.scale);
+        __syncwarp();
+        const int c4 = (lane & 7) * 4;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+          const int rr = it * 4 + (lane >> 3);
+          const int64_t gr = __shfl_sync(0xffffffffu, grow, rr);
+          const float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + c4);
+          if (gr >= 0 && c0 + c4 < ncols && !GT_DBG(g, 4))
+            *reinterpret_cast<float4 *>(g.out + gr * g.N + n0 + c0 + c4) = o;
         }
+        __syncwarp();
       }
       tc_fence_before();
-      mbar_arrive(acc_empty + 8 * acc);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
       acc_phase[acc] ^= 1;
       acc ^= 1;
     }
@@ -504,7 +566,16 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (num_sms <= 0) num_sms = 148;
   }
-  const size_t smem = (size_t)GT_STAGES * GT_STAGE_BYTES + 1024;
+#ifdef CMACE_GEMM_DEBUG
+  g.debug = getenv("CMACE_GEMM_DEBUG") ? atoi(getenv("CMACE_GEMM_DEBUG")) : 0;
+#endif
+  g.stage_bytes = 2 * GT_A_SLAB + 2 * g.npad * 128;
+  g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024) / g.stage_bytes;
+  if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
+#ifdef CMACE_GEMM_DEBUG
+  if (getenv("CMACE_GEMM_STAGES") && atoi(getenv("CMACE_GEMM_STAGES")) < g.stages) g.stages = atoi(getenv("CMACE_GEMM_STAGES"));
+#endif
+  const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
   cudaError_t e = cudaFuncSetAttribute(gemm3x_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   int64_t blocks = g.total_tiles < num_sms ? g.total_tiles : num_sms;
@@ -555,6 +626,7 @@ int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node
                         int nelements, int64_t nnodes, int K, int Nout, double scale, float *out, int32_t *status,
                         cmace_stream_t stream) {
   if (nnodes < 0 || K < 1 || Nout < 1 || nelements < 1) return fail(CMACE_ERR_ARG, "cmace_linear_tc: bad size");
+  if (nnodes > 0x7fffffffLL / 16) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: too many nodes");
   if (K % 4 != 0 || Nout % 4 != 0 || Nout > 128)
     return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: K, Nout multiples of 4 and Nout <= 128");
   if (nnodes == 0) return CMACE_OK;

@@ -50,6 +50,7 @@ SIGNATURES = {
     "cmace_symcon_plan_destroy": [_P],
     "cmace_symcon_plan_nterms": [_P],
     "cmace_symcon_plan_nclasses": [_P],
+    "cmace_symcon_plan_is_canonical": [_P],
     "cmace_symcon_fwd_f32": [_P, _P, _P, _P, _P, _P, _I, _L, _I, _P, _P],
     "cmace_symcon_fwd_f64": [_P, _P, _P, _P, _P, _P, _I, _L, _I, _P, _P],
     "cmace_symcon_bwd_f32": [_P, _P, _P, _P, _P, _P, _P, _I, _L, _I, _P, _P],
@@ -64,7 +65,8 @@ _RESTYPES = {
 # functions whose integer result is a value, not a status
 _VALUE_FUNCS = {"cmace_abi_version", "cmace_sender_order_workspace_bytes", "cmace_imp_bwd_scratch_elems",
                 "cmace_gemm_packed_floats",
-                "cmace_symcon_plan_destroy", "cmace_symcon_plan_nterms", "cmace_symcon_plan_nclasses"}
+                "cmace_symcon_plan_destroy", "cmace_symcon_plan_nterms", "cmace_symcon_plan_nclasses",
+                "cmace_symcon_plan_is_canonical"}
 
 _lib = None
 

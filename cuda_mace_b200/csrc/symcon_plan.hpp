@@ -12,6 +12,8 @@
 #include <string>
 #include <vector>
 
+#include "symcon_canonical.inc"
+
 namespace cmace {
 
 struct SymconProgram {
@@ -21,13 +23,40 @@ struct SymconProgram {
   std::vector<double> scale3, scale2;     // [w3], [w2] form_p = scale_p * form_class
   std::vector<int32_t> packed3, packed2;  // j | k << 8 | class << 16   /   j | class << 16
   std::vector<double> coef3, coef2;
+  // When the forms equal the build-time canonical ones up to a scale per class, the generated
+  // straight-line kernel can be used: form_p = canon_scale_p * canonical_form[canon_class_p].
+  bool canonical = false;
+  std::vector<int32_t> canon_class3, canon_class2;
+  std::vector<double> canon_scale3, canon_scale2;
 };
+
 
 struct Mono {
   int a, b, c;
   bool operator<(const Mono &o) const { return a != o.a ? a < o.a : (b != o.b ? b < o.b : c < o.c); }
 };
 typedef std::map<Mono, double> Poly;
+
+// Finds the build-time canonical class a form is proportional to (form = sigma * canonical); -1 if none.
+template <int W>
+inline int match_canonical(const Poly &form, const int (*monos)[W], const double *coefs, const int *starts,
+                           int nclass, double &sigma) {
+  for (int q = 0; q < nclass; q++) {
+    if ((int)form.size() != starts[q + 1] - starts[q]) continue;
+    bool ok = true;
+    double s = 0.0;
+    for (int t = starts[q]; t < starts[q + 1] && ok; t++) {
+      const Mono m{monos[t][0], monos[t][1], W == 3 ? monos[t][W - 1] : 0};
+      auto it = form.find(m);
+      if (it == form.end()) { ok = false; break; }
+      const double ratio = it->second / coefs[t];
+      if (s == 0.0) s = ratio;
+      if (std::fabs(ratio - s) > 1e-5 * std::fabs(s)) ok = false;
+    }
+    if (ok) { sigma = s; return q; }
+  }
+  return -1;
+}
 
 // Groups proportional polynomials: cls[p] = class id, scale[p] with poly_p = scale[p] * poly_rep.
 inline void classify(const std::vector<Poly> &polys, std::vector<int> &cls, std::vector<double> &scale,
@@ -142,6 +171,29 @@ inline bool build_symcon_program(int maxnz, const int16_t *u3_num, const int32_t
   prog.seg2[16] = (int)prog.packed2.size();
   for (int p = 0; p < w3; p++) { prog.class3.push_back(cls3[p] < 0 ? 0 : cls3[p]); prog.scale3.push_back(cls3[p] < 0 ? 0.0 : sc3[p]); }
   for (int p = 0; p < w2; p++) { prog.class2.push_back(cls2[p] < 0 ? 0 : cls2[p]); prog.scale2.push_back(cls2[p] < 0 ? 0.0 : sc2[p]); }
+
+  // canonical matching
+  prog.canonical = true;
+  std::vector<int> cq3(reps3.size()), cq2(reps2.size());
+  std::vector<double> sg3(reps3.size()), sg2(reps2.size());
+  for (size_t q = 0; q < reps3.size() && prog.canonical; q++) {
+    cq3[q] = match_canonical<3>(poly3[reps3[q]], canon::kMono3, canon::kCoef3, canon::kClassStart3, canon::NCLASS3, sg3[q]);
+    if (cq3[q] < 0) prog.canonical = false;
+  }
+  for (size_t q = 0; q < reps2.size() && prog.canonical; q++) {
+    cq2[q] = match_canonical<2>(poly2[reps2[q]], canon::kMono2, canon::kCoef2, canon::kClassStart2, canon::NCLASS2, sg2[q]);
+    if (cq2[q] < 0) prog.canonical = false;
+  }
+  if (prog.canonical) {
+    for (int p = 0; p < w3; p++) {
+      prog.canon_class3.push_back(cls3[p] < 0 ? 0 : cq3[cls3[p]]);
+      prog.canon_scale3.push_back(cls3[p] < 0 ? 0.0 : sc3[p] * sg3[cls3[p]]);
+    }
+    for (int p = 0; p < w2; p++) {
+      prog.canon_class2.push_back(cls2[p] < 0 ? 0 : cq2[cls2[p]]);
+      prog.canon_scale2.push_back(cls2[p] < 0 ? 0.0 : sc2[p] * sg2[cls2[p]]);
+    }
+  }
   return true;
 }
 
@@ -168,6 +220,19 @@ inline double eval_symcon_program(const SymconProgram &pg, const double *x, cons
     acc += x[i] * (d1 + 0.5 * d2 + d3 / 3.0);
   }
   return acc;
+}
+
+// Same result through the generated straight-line code (requires pg.canonical).
+inline double eval_symcon_canonical(const SymconProgram &pg, const double *x, const double *W3, const double *W2,
+                                    double w1, double *grad) {
+  double w3[canon::NCLASS3] = {0}, w2[canon::NCLASS2] = {0}, xx[16], g[16], value;
+  for (size_t p = 0; p < pg.canon_class3.size(); p++) w3[pg.canon_class3[p]] += pg.canon_scale3[p] * W3[p];
+  for (size_t p = 0; p < pg.canon_class2.size(); p++) w2[pg.canon_class2[p]] += pg.canon_scale2[p] * W2[p];
+  for (int i = 0; i < 16; i++) xx[i] = x[i];
+  canon::eval<double>(xx, w3, w2, w1, g, value);
+  if (grad)
+    for (int i = 0; i < 16; i++) grad[i] = g[i];
+  return value;
 }
 
 }  // namespace cmace

@@ -16,6 +16,7 @@
 // the effective weights sit in shared memory (conflict-free, lane-major), the program is read
 // with warp-uniform addresses.  No atomics; every output element has one writer.
 #include <cmath>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -31,6 +32,10 @@ struct cmace_symcon_plan {
   double *d_f64 = nullptr;     // [scale3 (w3)] [scale2 (w2)] [coef3] [coef2]
   float *d_f32 = nullptr;      // same layout in float
   int ints_total = 0, reals_total = 0;
+  // canonical fast path: per path, class of the generated program and scale (device copies follow the
+  // generic arrays: ints [.. | canon_class3 (w3) | canon_class2 (w2)], reals [.. | canon_scale3 | canon_scale2])
+  bool canonical = false;
+  int canon_int_off = 0, canon_real_off = 0;
 };
 
 namespace cmace {
@@ -128,6 +133,70 @@ __global__ void __launch_bounds__(SC_WARPS * 32)
   }
 }
 
+// ---- generated straight-line path -----------------------------------------------------------
+// Used when the caller's tables are the canonical l_max=3 couplings (up to a scale per path).  One thread
+// per (node, channel): the node's 16 components, the 12 effective class weights and the 16 gradient
+// components stay in registers; the effective weights of every element are combined once per CTA into
+// shared memory (each thread its own channel column), then nodes are streamed: 16 coalesced loads in,
+// 1 (forward) or 16 (backward) coalesced stores out.  HBM-bound: s*17*N*C bytes forward, s*33*N*C backward.
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(128)
+    symcon_canon_kernel(const int32_t *__restrict__ cclass3, const int32_t *__restrict__ cclass2,
+                        const T *__restrict__ cscale3, const T *__restrict__ cscale2, int w3, int w2, int w1,
+                        const T *__restrict__ X, const int32_t *__restrict__ atom_types, const T *__restrict__ W3,
+                        const T *__restrict__ W2, const T *__restrict__ W1, const T *__restrict__ gout,
+                        int nelements, int64_t nnodes, int C, T *__restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T *weff = reinterpret_cast<T *>(smem_raw);  // [nelements][13][blockDim.x]
+  constexpr int NW = canon::NCLASS3 + canon::NCLASS2 + 1;
+  const int CH = blockDim.x;
+  const int c = blockIdx.y * CH + threadIdx.x;
+  for (int z = 0; z < nelements; z++) {
+    T acc[NW];
+#pragma unroll
+    for (int q = 0; q < NW; q++) acc[q] = T(0);
+    for (int p = 0; p < w3; p++) {
+      const T v = cscale3[p] * W3[((int64_t)z * w3 + p) * C + c];
+      const int q = cclass3[p];
+#pragma unroll
+      for (int u = 0; u < canon::NCLASS3; u++) acc[u] += (u == q) ? v : T(0);
+    }
+    for (int p = 0; p < w2; p++) {
+      const T v = cscale2[p] * W2[((int64_t)z * w2 + p) * C + c];
+      const int q = cclass2[p];
+#pragma unroll
+      for (int u = 0; u < canon::NCLASS2; u++) acc[canon::NCLASS3 + u] += (u == q) ? v : T(0);
+    }
+    acc[NW - 1] = W1[(int64_t)z * w1 * C + c];
+#pragma unroll
+    for (int q = 0; q < NW; q++) weff[(z * NW + q) * CH + threadIdx.x] = acc[q];
+  }
+  // each thread reads back only what it wrote: no barrier needed
+
+  for (int64_t node = blockIdx.x; node < nnodes; node += gridDim.x) {
+    const int z = atom_types[node];
+    T x[16], g[16], w3r[canon::NCLASS3], w2r[canon::NCLASS2], value;
+    const T *xrow = X + node * 16 * C + c;
+#pragma unroll
+    for (int i = 0; i < 16; i++) x[i] = __ldcs(xrow + (int64_t)i * C);
+    const T *wz = weff + (int64_t)z * NW * CH + threadIdx.x;
+#pragma unroll
+    for (int q = 0; q < canon::NCLASS3; q++) w3r[q] = wz[q * CH];
+#pragma unroll
+    for (int q = 0; q < canon::NCLASS2; q++) w2r[q] = wz[(canon::NCLASS3 + q) * CH];
+    const T w1r = wz[(NW - 1) * CH];
+    canon::eval<T>(x, w3r, w2r, w1r, g, value);
+    if (BWD) {
+      const T go = gout[node * C + c];
+      T *orow = out + node * 16 * C + c;
+#pragma unroll
+      for (int i = 0; i < 16; i++) __stcs(orow + (int64_t)i * C, go * g[i]);
+    } else {
+      out[node * C + c] = value;
+    }
+  }
+}
+
 }  // namespace cmace
 
 using namespace cmace;
@@ -162,6 +231,15 @@ int cmace_symcon_plan_create(int maxnz, const int16_t *u3_num, const int32_t *u3
   reals.insert(reals.end(), prog.scale2.begin(), prog.scale2.end());
   reals.insert(reals.end(), prog.coef3.begin(), prog.coef3.end());
   reals.insert(reals.end(), prog.coef2.begin(), prog.coef2.end());
+  plan->canonical = prog.canonical;
+  plan->canon_int_off = (int)ints.size();
+  plan->canon_real_off = (int)reals.size();
+  if (prog.canonical) {
+    ints.insert(ints.end(), prog.canon_class3.begin(), prog.canon_class3.end());
+    ints.insert(ints.end(), prog.canon_class2.begin(), prog.canon_class2.end());
+    reals.insert(reals.end(), prog.canon_scale3.begin(), prog.canon_scale3.end());
+    reals.insert(reals.end(), prog.canon_scale2.begin(), prog.canon_scale2.end());
+  }
   std::vector<float> reals32(reals.begin(), reals.end());
   plan->ints_total = (int)ints.size();
   plan->reals_total = (int)reals.size();
@@ -190,9 +268,16 @@ void cmace_symcon_plan_destroy(cmace_symcon_plan *plan) {
 
 int cmace_symcon_plan_nterms(const cmace_symcon_plan *plan) { return plan ? plan->nterms3 + plan->nterms2 : 0; }
 int cmace_symcon_plan_nclasses(const cmace_symcon_plan *plan) { return plan ? plan->nclass3 + plan->nclass2 : 0; }
+int cmace_symcon_plan_is_canonical(const cmace_symcon_plan *plan) { return plan && plan->canonical ? 1 : 0; }
 }
 
 namespace cmace {
+
+// CMACE_SYMCON_GENERIC=1 in the environment forces the table-driven kernel (tests compare both)
+static bool force_generic() {
+  const char *e = getenv("CMACE_SYMCON_GENERIC");
+  return e != nullptr && e[0] == '1';
+}
 
 template <typename T, bool BWD>
 static int symcon_launch(const cmace_symcon_plan *plan, const T *X, const int32_t *atom_types, const T *W3,
@@ -203,6 +288,30 @@ static int symcon_launch(const cmace_symcon_plan *plan, const T *X, const int32_
   if (C <= 0 || C % 32 != 0) return fail(CMACE_ERR_UNSUPPORTED, "%s: channels must be a multiple of 32", what);
   if (nnodes == 0) return CMACE_OK;
   if (!X || !atom_types || !W3 || !W2 || !W1 || !out || (BWD && !gout)) return fail(CMACE_ERR_ARG, "%s: null pointer", what);
+  const T *reals = sizeof(T) == 8 ? reinterpret_cast<const T *>(plan->d_f64) : reinterpret_cast<const T *>(plan->d_f32);
+  if (plan->canonical && !force_generic()) {
+    // channel chunk per CTA: the whole row when C <= 128, else 128-wide chunks
+    const int CH = C <= 128 ? C : 128;
+    constexpr int NW = canon::NCLASS3 + canon::NCLASS2 + 1;
+    const size_t smem = sizeof(T) * (size_t)nelements * NW * CH;
+    if (C % CH == 0 && smem <= 160 * 1024) {
+      auto kern = symcon_canon_kernel<T, BWD>;
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+      }
+      int per_sm = (int)((200 * 1024) / (smem + 1024));
+      per_sm = per_sm < 1 ? 1 : (per_sm > 12 ? 12 : per_sm);
+      int64_t blocks = (int64_t)148 * per_sm;
+      if (blocks > nnodes) blocks = nnodes;
+      dim3 grid((unsigned)blocks, (unsigned)(C / CH));
+      const int32_t *ci = plan->d_ints + plan->canon_int_off;
+      const T *cr = reals + plan->canon_real_off;
+      kern<<<grid, CH, smem, (cudaStream_t)stream>>>(ci, ci + plan->w3, cr, cr + plan->w3, plan->w3, plan->w2, plan->w1, X,
+                                                     atom_types, W3, W2, W1, gout, nelements, nnodes, C, out);
+      return check_launch(what);
+    }
+  }
   PlanView pv;
   const int32_t *ip = plan->d_ints;
   pv.seg3 = ip; ip += 17;

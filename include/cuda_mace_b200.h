@@ -188,6 +188,9 @@ int cmace_symcon_plan_create(int u3_max_nonzero, const int16_t *u3_num_nonzero /
 void cmace_symcon_plan_destroy(cmace_symcon_plan *plan);
 int cmace_symcon_plan_nterms(const cmace_symcon_plan *plan);
 int cmace_symcon_plan_nclasses(const cmace_symcon_plan *plan);
+/* 1 when the tables were recognised as the canonical l_max = 3 couplings (up to one scale per path) and the
+ * build-time generated register kernel is used instead of the table-driven one. */
+int cmace_symcon_plan_is_canonical(const cmace_symcon_plan *plan);
 int cmace_symcon_fwd_f32(const cmace_symcon_plan *plan, const float *X, const int32_t *atom_types,
                          const float *W3, const float *W2, const float *W1, int nelements,
                          int64_t nnodes, int channels, float *out, cmace_stream_t stream);

@@ -84,24 +84,50 @@ def tables_f64(U):
     return maxnz, n3.numpy(), i3.numpy(), v3d.numpy(), n2.numpy(), i2.numpy(), v2d.numpy()
 
 
-def test_contraction_program_matches_dense_oracle(hc, U):
-    maxnz, n3, i3, v3, n2, i2, v2 = tables_f64(U)
+@pytest.mark.parametrize("canonical", [0, 1])
+@pytest.mark.parametrize("rescale", [False, True])
+def test_contraction_program_matches_dense_oracle(hc, U, canonical, rescale):
+    """Table-driven program (canonical=0) and generated straight-line code (canonical=1) against the dense
+    einsum; `rescale` multiplies every coupling path by its own factor, as a different upstream
+    normalisation of the U tensors would: the plan must still recognise the canonical forms."""
+    U3, U2, U1 = U
+    if rescale:
+        g0 = torch.Generator().manual_seed(9)
+        U3 = U3 * (0.5 + torch.rand(23, generator=g0, dtype=torch.float64)) * torch.where(torch.arange(23) % 3 == 0, -1.0, 1.0)
+        U2 = U2 * (0.5 + torch.rand(4, generator=g0, dtype=torch.float64))
+    Uc = (U3, U2, U1)
+    maxnz, n3, i3, v3, n2, i2, v2 = tables_f64(Uc)
     N, C, Z = 9, 32, 3
     g = torch.Generator().manual_seed(0)
     X = torch.randn(N, 16, C, generator=g, dtype=torch.float64, requires_grad=True)
     at = torch.randint(0, Z, (N,), generator=g, dtype=torch.int32)
     W3, W2, W1 = (torch.randn(Z, n, C, generator=g, dtype=torch.float64) for n in (23, 4, 1))
-    ref = oops.symmetric_contraction(X, at, *U, W3, W2, W1)[:, 0]
+    ref = oops.symmetric_contraction(X, at, *Uc, W3, W2, W1)[:, 0]
     (gref,) = torch.autograd.grad(ref.sum(), X)
-    out, grad, info = np.zeros((N, C)), np.zeros((N, 16, C)), np.zeros(4, np.int32)
+    out, grad, info = np.zeros((N, C)), np.zeros((N, 16, C)), np.zeros(5, np.int32)
     Xn, atn, a, b, c = X.detach().numpy(), at.numpy(), W3.numpy(), W2.numpy(), W1.numpy()
     rc = hc.hc_symcon_f64(maxnz, P(n3), P(i3), P(v3), P(n2), P(i2), P(v2), 23, 4, 1, P(Xn), P(atn), P(a), P(b), P(c),
-                          ctypes.c_int64(N), C, P(out), P(grad), P(info))
+                          ctypes.c_int64(N), C, P(out), P(grad), P(info), canonical)
     assert rc == 0
-    # 23 coupling paths collapse to 8 distinct cubic invariants, 4 quadratic ones
-    assert info[0] == 8 and info[1] == 4
+    # 23 coupling paths collapse to 8 distinct cubic invariants, 4 quadratic ones, all canonical
+    assert info[0] == 8 and info[1] == 4 and info[4] == 1
     assert np.abs(out - ref.detach().numpy()).max() < 1e-12 * np.abs(ref.detach().numpy()).max()
     assert np.abs(grad - gref.numpy()).max() < 1e-12 * np.abs(gref.numpy()).max()
+
+
+def test_non_canonical_tables_are_detected(hc, U):
+    """A coupling tensor with one perturbed entry is no longer proportional to a canonical form."""
+    U3, U2, U1 = (t.clone() for t in U)
+    idx = (U3[..., 5] != 0).nonzero()[0]
+    U3[idx[0], idx[1], idx[2], 5] *= 1.5
+    maxnz, n3, i3, v3, n2, i2, v2 = tables_f64((U3, U2, U1))
+    info = np.zeros(5, np.int32)
+    z = np.zeros((1, 16, 32))
+    w = np.zeros((1, 23, 32))
+    at, out, grad = np.zeros(1, np.int32), np.zeros((1, 32)), np.zeros((1, 16, 32))  # kept alive across the call
+    rc = hc.hc_symcon_f64(maxnz, P(n3), P(i3), P(v3), P(n2), P(i2), P(v2), 23, 4, 1, P(z), P(at),
+                          P(w), P(w), P(w), ctypes.c_int64(1), 32, P(out), P(grad), P(info), 1)
+    assert rc == 0 and info[4] == 0
 
 
 def test_contraction_program_rejects_bad_tables(hc, U):
@@ -109,9 +135,10 @@ def test_contraction_program_rejects_bad_tables(hc, U):
     bad = i3.copy()
     bad[0, 1, 1] |= 0xFF  # path index beyond w3
     z = np.zeros((1, 16, 32))
-    info = np.zeros(4, np.int32)
+    info = np.zeros(5, np.int32)
     at = np.zeros(1, np.int32)
     w = np.zeros((1, 23, 32))
+    out, grad = np.zeros((1, 32)), np.zeros((1, 16, 32))
     rc = hc.hc_symcon_f64(maxnz, P(n3), P(bad), P(v3), P(n2), P(i2), P(v2), 23, 4, 1, P(z), P(at), P(w), P(w), P(w),
-                          ctypes.c_int64(1), 32, P(np.zeros((1, 32))), P(np.zeros((1, 16, 32))), P(info))
+                          ctypes.c_int64(1), 32, P(out), P(grad), P(info), 0)
     assert rc == 1

@@ -314,3 +314,33 @@ def test_tensor_core_and_fma_linear_agree(dev):
             ops.USE_TENSOR_CORES = True
     ops.check_status()
     assert rel_err(outs[0], ref) < 2e-6 and rel_err(outs[1], ref) < 2e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_contraction_generated_and_table_driven_kernels_agree(dtype, dev, U, monkeypatch):
+    """The build-time generated register kernel (selected for the canonical couplings) and the
+    table-driven kernel (any tables) give the same numbers; a rescaled U still takes the fast path."""
+    from cuda_mace_b200 import _abi, ops
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(2)
+    N, C, Z = 300, 128, 4
+    U3, U2, U1 = U
+    U3 = U3 * (0.5 + torch.rand(23, generator=g, dtype=torch.float64))
+    X = torch.randn(N, 16, C, generator=g, dtype=torch.float64).to(dtype)
+    at = torch.randint(0, Z, (N,), generator=g, dtype=torch.int32)
+    W3, W2, W1 = (torch.randn(Z, n, C, generator=g, dtype=torch.float64).to(dtype) / n for n in (23, 4, 1))
+    Xo = X.double().clone().requires_grad_(True)
+    ref = oops.symmetric_contraction_chunked(Xo, at, U3, U2, U1, W3.double(), W2.double(), W1.double())
+    (ref ** 2).sum().backward()
+    results = []
+    for generic in ("0", "1"):
+        monkeypatch.setenv("CMACE_SYMCON_GENERIC", generic)
+        mod = ops.SymmetricContraction(U3, U2, U1, W3, W2, W1).to(dev)
+        Xg = X.to(dev).clone().requires_grad_(True)
+        out = mod(Xg, at.to(dev))
+        assert _abi.call("cmace_symcon_plan_is_canonical", mod._plan.handle) == 1
+        (out ** 2).sum().backward()
+        assert rel_err(out, ref) < TOL[dtype]["out"] and rel_err(Xg.grad, Xo.grad) < TOL[dtype]["grad"]
+        results.append((out.detach(), Xg.grad))
+    assert rel_err(results[0][0], results[1][0]) < TOL[dtype]["out"]

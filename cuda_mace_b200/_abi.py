@@ -38,6 +38,8 @@ SIGNATURES = {
     "cmace_imp_bwd_scratch_elems": [_L, _I, _I],
     "cmace_imp_bwd_edge_f32": [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P, _P, _P, _P, _P],
     "cmace_imp_bwd_edge_f64": [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P, _P, _P, _P, _P],
+    "cmace_imp_bwd_edge_f64_noalloc_max_elems": [],
+    "cmace_imp_bwd_edge_f64_noalloc": [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P, _P, _P, _P],
     "cmace_imp_bwd_node_f32": [_P, _P, _P, _L, _I, _P, _P],
     "cmace_imp_bwd_node_f64": [_P, _P, _P, _L, _I, _P, _P],
     "cmace_linear_f32": [_P, _P, _P, _P, _I, _L, _I, _I, _D, _P, _P],
@@ -60,11 +62,12 @@ _RESTYPES = {
     "cmace_sender_order_workspace_bytes": _L,
     "cmace_imp_bwd_scratch_elems": _L,
     "cmace_gemm_packed_floats": _L,
+    "cmace_imp_bwd_edge_f64_noalloc_max_elems": _L,
     "cmace_symcon_plan_destroy": None,
 }
 # functions whose integer result is a value, not a status
 _VALUE_FUNCS = {"cmace_abi_version", "cmace_sender_order_workspace_bytes", "cmace_imp_bwd_scratch_elems",
-                "cmace_gemm_packed_floats",
+                "cmace_gemm_packed_floats", "cmace_imp_bwd_edge_f64_noalloc_max_elems",
                 "cmace_symcon_plan_destroy", "cmace_symcon_plan_nterms", "cmace_symcon_plan_nclasses",
                 "cmace_symcon_plan_is_canonical"}
 
@@ -75,7 +78,7 @@ _lib = None
 KERNEL_LAUNCHES = {
     "cmace_receiver_csr": 1, "cmace_sender_order": 3, "cmace_group_by_element": 3,
     "cmace_sph_fwd": 1, "cmace_sph_bwd": 1, "cmace_edge_basis_fwd": 1, "cmace_edge_basis_bwd": 1,
-    "cmace_spline_fwd": 1, "cmace_spline_bwd": 1, "cmace_imp_fwd": 1, "cmace_imp_bwd_edge": 1,
+    "cmace_spline_fwd": 1, "cmace_spline_bwd": 1, "cmace_imp_fwd": 1, "cmace_imp_bwd_edge": 1, "cmace_imp_bwd_edge_f64_noalloc": 2,
     "cmace_imp_bwd_node": 1, "cmace_linear": 1, "cmace_symcon_fwd": 1, "cmace_symcon_bwd": 1,
     "cmace_gemm_pack_weights": 1, "cmace_gemm3x": 1, "cmace_linear_tc": 1,
 }

@@ -345,6 +345,38 @@ static int imp_bwd_node(const T *Tin, const int32_t *perm, const int32_t *send_p
   return check_launch("cmace_imp_bwd_node");
 }
 
+// ---- variant without caller scratch -------------------------------------------------------------
+// Some callers cannot hand over scratch memory because they cannot allocate on the device at the point
+// of the call: a plugin running inside another framework's memory pool that is already sized, or a
+// host thread that must not call into an allocator while the device is busy.  For those, the float64
+// edge backward keeps its per-chunk gradY partials in a fixed array in the library image.
+constexpr int64_t kStaticScratchElems = 2 * 1024 * 1024;  // doubles: 16 MiB, e.g. 65 536 edges at C = 128
+static __device__ __align__(256) double g_static_gradY_partial[kStaticScratchElems];
+
+// device address of the array, looked up once per device (index = CUDA device ordinal)
+static double *static_scratch_address(int *err) {
+  static double *addr[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = 1;
+    return nullptr;
+  }
+  if (addr[dev] == nullptr) {
+    // the array's name is a host-side handle, not a device pointer: ask the runtime for the address
+    // on the device that is current now
+    double *p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_gradY_partial);
+    if (e != cudaSuccess || p == nullptr) {
+      *err = 1;
+      return nullptr;
+    }
+    addr[dev] = p;
+  }
+  *err = 0;
+  return addr[dev];
+}
+
 }  // namespace cmace
 
 using namespace cmace;
@@ -381,6 +413,30 @@ int cmace_imp_bwd_edge_f64(const double *X, const double *Y, const double *R, co
   return imp_bwd_edge<double>(X, Y, R, G, sender, row_ptr, nnodes, nedges, channels, gradR, gradY, T,
                               gradY_partial, stream);
 }
+int64_t cmace_imp_bwd_edge_f64_noalloc_max_elems(void) { return kStaticScratchElems; }
+
+int cmace_imp_bwd_edge_f64_noalloc(const double *X, const double *Y, const double *R, const double *G,
+                                   const int32_t *sender, const int32_t *row_ptr, int64_t nnodes, int64_t nedges,
+                                   int channels, double *gradR, double *gradY, double *T, cmace_stream_t stream) {
+  const int64_t need = cmace_imp_bwd_scratch_elems(nedges, channels, 1);
+  if (need > kStaticScratchElems)
+    return fail(CMACE_ERR_UNSUPPORTED,
+                "cmace_imp_bwd_edge_f64_noalloc: %lld scratch elements needed, the built-in array holds %lld "
+                "(reduce the number of edges per call or use cmace_imp_bwd_edge_f64 with your own scratch)",
+                (long long)need, (long long)kStaticScratchElems);
+  int err = 0;
+  double *scratch = need > 0 ? static_scratch_address(&err) : nullptr;
+  if (err) return fail(CMACE_ERR_CUDA, "cmace_imp_bwd_edge_f64_noalloc: cudaGetSymbolAddress failed");
+  if (need > 0) {
+    // the array keeps the previous call's contents; the part this call sums over starts from zero
+    cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)need * sizeof(double), (cudaStream_t)stream);
+    if (e != cudaSuccess)
+      return fail(CMACE_ERR_CUDA, "cmace_imp_bwd_edge_f64_noalloc: %s", cudaGetErrorString(e));
+  }
+  return imp_bwd_edge<double>(X, Y, R, G, sender, row_ptr, nnodes, nedges, channels, gradR, gradY, T, scratch,
+                              stream);
+}
+
 int cmace_imp_bwd_node_f32(const float *T, const int32_t *perm, const int32_t *send_ptr, int64_t nnodes,
                            int channels, float *gradX, cmace_stream_t stream) {
   return imp_bwd_node<float>(T, perm, send_ptr, nnodes, channels, gradX, stream);

@@ -125,6 +125,23 @@ int cmace_imp_bwd_edge_f64(const double *X, const double *Y, const double *R, co
                            const int32_t *sender, const int32_t *row_ptr, int64_t nnodes,
                            int64_t nedges, int channels, double *gradR, double *gradY, double *T,
                            double *gradY_partial, cmace_stream_t stream);
+/* No counterpart in the reference.  Same computation as cmace_imp_bwd_edge_f64 for callers that cannot
+ * allocate device memory where they call from (a plugin inside a framework whose memory pool is fixed, a
+ * thread that must stay out of the allocator): the gradY partials live in a 16 MiB array that is part of
+ * the library image (every GPU that loads the library carries it until exit), so no scratch pointer is
+ * passed and nothing is allocated or freed, by this library or by any other.  Limits and rules:
+ *  - at most cmace_imp_bwd_edge_f64_noalloc_max_elems() = 2 Mi scratch doubles, i.e.
+ *    cmace_imp_bwd_scratch_elems(nedges, channels, 1) must not exceed it (65 536 edges at C = 128);
+ *    larger calls fail with CMACE_ERR_UNSUPPORTED and a message;
+ *  - the first call on each device looks up the array's device address (that device must be current);
+ *    make that first call outside any stream capture;
+ *  - all calls share the one array: calls that overlap on the GPU (different streams, or several host
+ *    threads) race on it; issue them on one stream or serialise them. */
+int64_t cmace_imp_bwd_edge_f64_noalloc_max_elems(void);
+int cmace_imp_bwd_edge_f64_noalloc(const double *X, const double *Y, const double *R, const double *G,
+                                   const int32_t *sender, const int32_t *row_ptr, int64_t nnodes,
+                                   int64_t nedges, int channels, double *gradR, double *gradY, double *T,
+                                   cmace_stream_t stream);
 int cmace_imp_bwd_node_f32(const float *T, const int32_t *perm, const int32_t *send_ptr,
                            int64_t nnodes, int channels, float *gradX, cmace_stream_t stream);
 int cmace_imp_bwd_node_f64(const double *T, const int32_t *perm, const int32_t *send_ptr,

@@ -179,6 +179,10 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the kernels)")
+    # libraries (NCCL's version banner) write to stdout; keep stdout clean for the one JSON line
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     import torch.distributed as dist
 
     from cuda_mace_b200 import _abi, cg, domain, evaluator, model, systems
@@ -292,7 +296,9 @@ def main():
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"], _ = cpu_reference_run(args, 2, 1)
-    print(json.dumps(line))
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
+    print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

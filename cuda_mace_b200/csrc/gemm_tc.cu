@@ -5,6 +5,10 @@
 // Every float32 operand x is split as x = hi + lo with hi = tf32(x) and lo = tf32(x - hi) (both rounded to
 // nearest, so the residual is unbiased), and D = Ahi*Bhi + Alo*Bhi + Ahi*Blo is accumulated in float32 in tensor
 // memory, which brings the result to about 2^-21 relative: float32-grade, unlike a single TF32 pass.
+// Issuing a tcgen05.mma costs about 145 cycles whatever its N (measured), so instructions are the scarce
+// resource: the hi and lo images of B sit back to back and are read as ONE operand of twice the rows, which
+// yields Ahi*Bhi and Ahi*Blo from a single instruction (two column ranges of the accumulator, added in the
+// epilogue); with Alo*Bhi that is two instructions per K step instead of three.
 //
 // Structure (one CTA per SM, persistent over 128-row tiles, warp specialised, 13 warps):
 //   warps 0-7  producers: gather 128 rows x 32 columns (one "K block") of A per pipeline stage with
@@ -16,7 +20,7 @@
 //              after the last K block of a tile, to the accumulator's "full" barrier.
 //   warps 9-12 epilogue: tcgen05.ld of the accumulator (each thread one row, 32 columns at a time),
 //              scale, store 128 contiguous bytes per thread, release the accumulator.
-// Accumulators are double buffered in tensor memory (2 x 128 columns), so the epilogue of tile t
+// Accumulators are double buffered in tensor memory (2 x 256 columns), so the epilogue of tile t
 // overlaps the MMAs of tile t+1, and a 3-stage shared-memory ring overlaps loads with MMAs.
 //
 // Row maps: PLAIN (row r of tile t is r + 128 t; used for the radial multilayer perceptron, N may be
@@ -40,14 +44,18 @@ constexpr int GT_PRODUCER_WARPS = 8;
 constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
 constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + 4) * 32;
 constexpr int GT_SMEM_BUDGET = 227 * 1024;           // dynamic shared memory a CTA may opt in to
-constexpr int GT_TMEM_COLS = 256;
+constexpr int GT_TMEM_COLS = 512;                   // two accumulators of 2 x 128 columns
 constexpr int GT_PREFETCH = 2;                      // K blocks of global loads in flight per producer thread
 constexpr int GT_EP_STRIDE = 36;                    // floats per row of the epilogue transpose buffer (padded)
 constexpr int GT_EP_BYTES = 4 * 32 * GT_EP_STRIDE * 4;
 constexpr long long GT_TIMEOUT_CYCLES = 4000000000LL;  // about two seconds
 #ifdef CMACE_GEMM_DEBUG
 #define GT_DBG(g, bit) (((g).debug & (bit)) != 0)
+#define GT_PROF(g, slot, t0) do { if (((g).debug & 4096) && blockIdx.x == 0 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long *>((g).status) + (slot), (unsigned long long)(clock64() - (t0))); } while (0)
+#define GT_NOW() clock64()
 #else
+#define GT_PROF(g, slot, t0) do { } while (0)
+#define GT_NOW() 0
 #define GT_DBG(g, bit) false
 #endif
 
@@ -139,8 +147,30 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// same with accumulation always on (no predicate set-up between two MMAs)
+__device__ __forceinline__ void umma_tf32_acc(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.u32 p, 1, 1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -197,8 +227,10 @@ __device__ __forceinline__ Tile locate_tile(const GemmArgs &g, int64_t t) {
   T.mat = 0;
   T.seg_begin = 0;
   T.seg_rows = 0;
-  T.ntile = (int)(t % g.n_tiles);
-  int64_t rt = t / g.n_tiles;
+  // tile indices fit 32 bits (checked on the host): cheap division
+  const uint32_t t32 = (uint32_t)t, rt32 = t32 / (uint32_t)g.n_tiles;
+  T.ntile = (int)(t32 - rt32 * (uint32_t)g.n_tiles);
+  int64_t rt = rt32;
   if (g.mode == GT_MODE_PLAIN) {
     T.row0 = rt * GT_TILE_M;
     T.valid = T.row0 < g.M;
@@ -258,6 +290,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
   const uint32_t GT_STAGE_BYTES = (uint32_t)g.stage_bytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t_kernel0 = GT_NOW();
+  (void)t_kernel0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GT_STAGES; s++) {
@@ -331,8 +365,11 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
     auto commit = [&](int64_t bblock, const float4 (&v)[GT_ROWS_PER_THREAD]) -> bool {
       // lane 0 polls the barrier for the warp
       uint32_t got = 1;
+      const long long tw = GT_NOW();
       if (lane == 0) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
+      if (warp == 0) GT_PROF(g, 1, tw);
+      const long long tc = GT_NOW();
       if (!got) {
         report(g, 1);
         return false;
@@ -365,6 +402,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+      if (warp == 0) GT_PROF(g, 2, tc);
       if (++stage == GT_STAGES) {
         stage = 0;
         phase ^= 1;
@@ -404,18 +442,26 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       int ncols = g.N - T.ntile * 128;
       ncols = ncols > 128 ? 128 : ncols;
       const int nmma = (ncols + 15) & ~15;
-      const uint32_t idesc = umma_idesc_tf32(GT_TILE_M, nmma);
+      // B images are npad rows each, hi directly followed by lo: read as one operand of 2 * npad rows,
+      // one MMA gives Ahi*Bhi in columns [0, npad) and Ahi*Blo in columns [npad, 2 npad)
+      const uint32_t idesc2 = umma_idesc_tf32(GT_TILE_M, 2 * g.npad);
+      const uint32_t idesc1 = umma_idesc_tf32(GT_TILE_M, nmma);
       uint32_t got = 1;
+      const long long ta = GT_NOW();
       if (lane == 0) got = mbar_wait(acc_empty + 8 * acc, acc_phase[acc] ^ 1) ? 1u : 0u;
+      GT_PROF(g, 3, ta);
       if (!__shfl_sync(0xffffffffu, got, 0)) {
         report(g, 2);
         break;
       }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * 128;
+      const uint32_t d_tmem = tmem_base + acc * 256;
       for (int kb = 0; kb < k_blocks; kb++) {
         got = 1;
+        const long long tf = GT_NOW();
         if (lane == 0 && !GT_DBG(g, 1024)) got = mbar_wait(full_bar + 8 * stage, phase) ? 1u : 0u;
+        GT_PROF(g, 4, tf);
+        const long long ti = GT_NOW();
         if (!__shfl_sync(0xffffffffu, got, 0)) {
           report(g, 3);
           ok = false;
@@ -427,16 +473,35 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
           const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
           const uint64_t b_hi0 = umma_desc_sw128(sA + 2 * GT_A_SLAB);
-          const uint64_t b_lo0 = umma_desc_sw128(sA + 2 * GT_A_SLAB + b_image);
           int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
           ksteps = ksteps > 4 ? 4 : ksteps;
           if (GT_DBG(g, 2)) ksteps = 0;
-          for (int j = 0; j < ksteps; j++) {
-            const uint64_t dj = (uint64_t)(2 * j);
-            umma_tf32(d_tmem, a_lo0 + dj, b_hi0 + dj, idesc, (kb | j) != 0);
-            umma_tf32(d_tmem, a_hi0 + dj, b_lo0 + dj, idesc, 1);
-            umma_tf32(d_tmem, a_hi0 + dj, b_hi0 + dj, idesc, 1);
+          const long long tm0 = GT_NOW();
+          // the issuing thread shares its scheduler with busy warps, so every instruction between two
+          // MMAs costs issue latency: descriptors are formed first, then the MMAs go back to back
+          uint64_t ah[4], al[4], bh[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            ah[j] = a_hi0 + (uint64_t)(2 * j);
+            al[j] = a_lo0 + (uint64_t)(2 * j);
+            bh[j] = b_hi0 + (uint64_t)(2 * j);
           }
+          if (ksteps == 4) {
+            umma_tf32(d_tmem, ah[0], bh[0], idesc2, kb != 0);
+            umma_tf32_acc(d_tmem, al[0], bh[0], idesc1);
+#pragma unroll
+            for (int j = 1; j < 4; j++) {
+              umma_tf32_acc(d_tmem, ah[j], bh[j], idesc2);
+              umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
+            }
+          } else {
+            for (int j = 0; j < ksteps; j++) {
+              umma_tf32(d_tmem, ah[j], bh[j], idesc2, (kb | j) != 0);
+              umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
+            }
+          }
+          GT_PROF(g, 8, tm0);
+          const long long tm1 = GT_NOW();
           if (GT_DBG(g, 128)) {
             mbar_arrive(empty_bar + 8 * stage);
             if (kb == k_blocks - 1) mbar_arrive(acc_full + 8 * acc);
@@ -444,8 +509,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
             umma_commit(empty_bar + 8 * stage);
             if (kb == k_blocks - 1) umma_commit(acc_full + 8 * acc);
           }
+          GT_PROF(g, 9, tm1);
         }
         __syncwarp();
+        GT_PROF(g, 5, ti);
         if (++stage == GT_STAGES) {
           stage = 0;
           phase ^= 1;
@@ -470,41 +537,53 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       int ncols = g.N - n0;
       ncols = ncols > 128 ? 128 : ncols;
       uint32_t got = 1;
+      const long long te = GT_NOW();
       if (lane == 0) got = mbar_wait(acc_full + 8 * acc, acc_phase[acc]) ? 1u : 0u;
+      if (q == 0) GT_PROF(g, 6, te);
+      const long long tb = GT_NOW();
       if (!__shfl_sync(0xffffffffu, got, 0)) {
         report(g, 4);
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * 128 + ((uint32_t)(q * 32) << 16);
-      // rows of this warp (global index per lane), to be read by the lanes that store them
+      const uint32_t taddr = tmem_base + acc * 256 + ((uint32_t)(q * 32) << 16);
+      // the 4 rows x 128 bytes each store instruction of this lane covers: row pointers, once per tile
+      float *rowptr[8];
+#pragma unroll
+      for (int it = 0; it < 8; it++) {
+        const int64_t gr = __shfl_sync(0xffffffffu, grow, it * 4 + (lane >> 3));
+        rowptr[it] = gr >= 0 ? g.out + gr * g.N + n0 + (lane & 7) * 4 : nullptr;
+      }
       for (int c0 = 0; c0 < ncols; c0 += 32) {
-        uint32_t v[32];
         if (GT_DBG(g, 64)) continue;
-        tmem_ld32(taddr + c0, v);
+        uint32_t v[32], w[32];
+        tmem_ld32_nowait(taddr + c0, v);             // Ahi*Bhi + Alo*Bhi
+        tmem_ld32_nowait(taddr + g.npad + c0, w);    // Ahi*Blo
+        tmem_ld_wait();
         if (GT_DBG(g, 32)) continue;
         // lane = row: write the row's 32 values, then read back 4 rows x 128 bytes per instruction
         float *mine = ep_buf + lane * GT_EP_STRIDE;
 #pragma unroll
         for (int i = 0; i < 32; i += 4)
           *reinterpret_cast<float4 *>(mine + i) =
-              make_float4(__uint_as_float(v[i]) * g.scale, __uint_as_float(v[i + 1]) * g.scale,
-                          __uint_as_float(v[i + 2]) * g.scale, __uint_as_float(v[i + 3]) * g.scale);
+              make_float4((__uint_as_float(v[i]) + __uint_as_float(w[i])) * g.scale,
+                          (__uint_as_float(v[i + 1]) + __uint_as_float(w[i + 1])) * g.scale,
+                          (__uint_as_float(v[i + 2]) + __uint_as_float(w[i + 2])) * g.scale,
+                          (__uint_as_float(v[i + 3]) + __uint_as_float(w[i + 3])) * g.scale);
         __syncwarp();
-        const int c4 = (lane & 7) * 4;
+        const bool col_ok = c0 + (lane & 7) * 4 < ncols;
 #pragma unroll
         for (int it = 0; it < 8; it++) {
           const int rr = it * 4 + (lane >> 3);
-          const int64_t gr = __shfl_sync(0xffffffffu, grow, rr);
-          const float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + c4);
-          if (gr >= 0 && c0 + c4 < ncols && !GT_DBG(g, 4))
-            *reinterpret_cast<float4 *>(g.out + gr * g.N + n0 + c0 + c4) = o;
+          const float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 7) * 4);
+          if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) *reinterpret_cast<float4 *>(rowptr[it] + c0) = o;
         }
         __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
+      if (q == 0) GT_PROF(g, 7, tb);
       acc_phase[acc] ^= 1;
       acc ^= 1;
     }
@@ -512,6 +591,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) GT_PROF(g, 0, t_kernel0);
   if (warp == GT_PRODUCER_WARPS) tmem_dealloc(tmem_base, GT_TMEM_COLS);
 }
 
@@ -578,6 +658,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
   cudaError_t e = cudaFuncSetAttribute(gemm3x_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  if (g.total_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many tiles", what);
   int64_t blocks = g.total_tiles < num_sms ? g.total_tiles : num_sms;
   if (blocks < 1) return CMACE_OK;
   gemm3x_tf32_kernel<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g);

@@ -46,7 +46,7 @@ SIGNATURES = {
     "cmace_linear_f64": [_P, _P, _P, _P, _I, _L, _I, _I, _D, _P, _P],
     "cmace_gemm_packed_floats": [_I, _I, _I],
     "cmace_gemm_pack_weights_f32": [_P, _I, _I, _I, _P, _P],
-    "cmace_gemm3x_f32": [_P, _P, _L, _I, _I, _D, _P, _P, _P],
+    "cmace_gemm3x_f32": [_P, _P, _L, _I, _I, _D, _I, _P, _P, _P, _P],
     "cmace_linear_tc_f32": [_P, _P, _P, _P, _I, _L, _I, _I, _D, _P, _P, _P],
     "cmace_symcon_plan_create": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, ctypes.POINTER(_P)],
     "cmace_symcon_plan_destroy": [_P],

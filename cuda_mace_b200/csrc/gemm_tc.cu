@@ -40,8 +40,9 @@ constexpr int GT_TILE_M = 128;
 constexpr int GT_KBLOCK = 32;                       // floats per K block = one 128-byte swizzle row
 constexpr int GT_A_SLAB = GT_TILE_M * 128;          // bytes of one A image (hi or lo) per stage
 constexpr int GT_B_SLAB_MAX = 128 * 128;            // bytes of one B image per stage at N tile = 128
-constexpr int GT_PRODUCER_WARPS = 8;
+constexpr int GT_PRODUCER_WARPS = 8;                 // 8 measured best (4: 0.47 ms, 8: 0.36 ms, 16: 0.59 ms on the Linear case)
 constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
+constexpr int GT_ROW_STEP = GT_PRODUCER_WARPS * 4;                       // rows between a thread's row segments
 constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + 4) * 32;
 constexpr int GT_SMEM_BUDGET = 227 * 1024;           // dynamic shared memory a CTA may opt in to
 constexpr int GT_TMEM_COLS = 512;                   // two accumulators of 2 x 128 columns
@@ -77,6 +78,8 @@ struct GemmArgs {
   int64_t total_tiles;          // upper bound of the tile index space
   int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
   int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
+  int a_act;                    // 1: apply the normalised SiLU to A while loading it
+  const float *ep_z;            // when set: out = scale * acc * silu_n'(ep_z[row, col]), ep_z laid out like out
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -205,6 +208,18 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(u);
 }
 
+// Second-moment-normalised SiLU of the radial multilayer perceptron, c * x * sigmoid(x), and its derivative.
+constexpr float kSiluNorm = 1.676532470331092f;
+// (exp2 and reciprocal on the special-function unit: about 2 ulp each, far inside the float32 targets)
+__device__ __forceinline__ float sigmoid_fast(float x) {
+  return __fdividef(1.0f, 1.0f + exp2f(-1.4426950408889634f * x));
+}
+__device__ __forceinline__ float silu_n(float x) { return kSiluNorm * x * sigmoid_fast(x); }
+__device__ __forceinline__ float silu_n_grad(float x) {
+  const float s = sigmoid_fast(x);
+  return kSiluNorm * s * fmaf(x, 1.0f - s, 1.0f);
+}
+
 // byte offset of the 16-byte chunk c (0..7) of row r inside a swizzled image
 __device__ __host__ __forceinline__ int sw128_offset(int r, int c) {
   return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
@@ -320,7 +335,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
     // per SM to cover HBM latency (about a microsecond) independently of the shared-memory ring depth.
     const int p = threadIdx.x;       // 0..255
     const int chunk = p & 7;         // 16-byte chunk of the 128-byte row segment
-    const int rbase = p >> 3;        // rows rbase + 32 i
+    const int rbase = p >> 3;        // rows rbase + GT_ROW_STEP * i
     // head: the next (tile, K block) item whose loads have not been issued yet
     struct Head {
       int64_t t;
@@ -343,7 +358,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       }
       head.valid = true;
 #pragma unroll
-      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row(g, head.T, rbase + 32 * i);
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row(g, head.T, rbase + GT_ROW_STEP * i);
     };
     // an item in flight only has to remember where its B block lives (-1: no item)
     auto issue = [&](float4 (&v)[GT_ROWS_PER_THREAD]) -> int64_t {
@@ -385,12 +400,18 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       if (!GT_DBG(g, 16))
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
-        const int r = rbase + 32 * i;
-        float4 hi, lo;
-        hi.x = to_tf32(v[i].x); lo.x = to_tf32(v[i].x - hi.x);
-        hi.y = to_tf32(v[i].y); lo.y = to_tf32(v[i].y - hi.y);
-        hi.z = to_tf32(v[i].z); lo.z = to_tf32(v[i].z - hi.z);
-        hi.w = to_tf32(v[i].w); lo.w = to_tf32(v[i].w - hi.w);
+        const int r = rbase + GT_ROW_STEP * i;
+        float4 a = v[i], hi, lo;
+        if (g.a_act) {
+          a.x = silu_n(a.x);
+          a.y = silu_n(a.y);
+          a.z = silu_n(a.z);
+          a.w = silu_n(a.w);
+        }
+        hi.x = to_tf32(a.x); lo.x = to_tf32(a.x - hi.x);
+        hi.y = to_tf32(a.y); lo.y = to_tf32(a.y - hi.y);
+        hi.z = to_tf32(a.z); lo.z = to_tf32(a.z - hi.z);
+        hi.w = to_tf32(a.w); lo.w = to_tf32(a.w - hi.w);
         const uint32_t off = (uint32_t)sw128_offset(r, chunk);
         asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(hi.x), "f"(hi.y), "f"(hi.z),
                      "f"(hi.w)
@@ -575,8 +596,17 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
 #pragma unroll
         for (int it = 0; it < 8; it++) {
           const int rr = it * 4 + (lane >> 3);
-          const float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 7) * 4);
-          if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) *reinterpret_cast<float4 *>(rowptr[it] + c0) = o;
+          float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 7) * 4);
+          if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) {
+            if (g.ep_z != nullptr) {
+              const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + c0));
+              o.x *= silu_n_grad(z.x);
+              o.y *= silu_n_grad(z.y);
+              o.z *= silu_n_grad(z.z);
+              o.w *= silu_n_grad(z.w);
+            }
+            *reinterpret_cast<float4 *>(rowptr[it] + c0) = o;
+          }
         }
         __syncwarp();
       }
@@ -686,17 +716,18 @@ int cmace_gemm_pack_weights_f32(const float *Bt, int nmat, int N, int K, float *
   return check_launch("cmace_gemm_pack_weights");
 }
 
-int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale, float *out,
-                     int32_t *status, cmace_stream_t stream) {
+int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale, int a_act,
+                     const float *ep_z, float *out, int32_t *status, cmace_stream_t stream) {
   if (M < 0 || K < 1 || N < 1) return fail(CMACE_ERR_ARG, "cmace_gemm3x: bad size");
   if (K % 4 != 0 || N % 4 != 0) return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm3x: K and N must be multiples of 4");
   if (M == 0) return CMACE_OK;
   if (!A || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_gemm3x: null pointer");
-  if (!aligned16(A) || !aligned16(packed) || !aligned16(out))
+  if (!aligned16(A) || !aligned16(packed) || !aligned16(out) || !aligned16(ep_z))
     return fail(CMACE_ERR_ARG, "cmace_gemm3x: pointers must be 16-byte aligned");
   const PackGeom p = pack_geom(N, K);
   GemmArgs g{};
   g.A = A; g.packed = packed; g.out = out; g.status = status;
+  g.a_act = a_act ? 1 : 0; g.ep_z = ep_z;
   g.M = M; g.K = K; g.N = N; g.nelements = 1; g.mode = GT_MODE_PLAIN; g.scale = (float)scale;
   g.n_tiles = p.n_tiles; g.k_blocks = p.k_blocks; g.npad = p.npad;
   g.total_tiles = ((M + GT_TILE_M - 1) / GT_TILE_M) * p.n_tiles;

@@ -89,13 +89,13 @@ class InvariantMACE(torch.nn.Module):
     def _radial_weights(self, L, bessel, lengths):
         if self.radial == "spline":
             return L.spline(lengths)
+        Ws = [getattr(L, f"W_radial{i}") for i in range(L.n_radial)]
+        on_tc = all(ops.tensor_core_ok(bessel.dtype, W.shape[0], W.shape[1]) for W in Ws)
+        if on_tc and ops.FUSED_RADIAL_ACTIVATION:
+            return ops.radial_mlp(bessel, Ws, [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial)])
         h = bessel
-        for i in range(L.n_radial):
-            W = getattr(L, f"W_radial{i}")
-            if ops.tensor_core_ok(h.dtype, W.shape[0], W.shape[1]):
-                h = ops.matmul3x(h, W, getattr(L, f"W_radial{i}_T"))
-            else:
-                h = h @ W
+        for i, W in enumerate(Ws):
+            h = ops.matmul3x(h, W, getattr(L, f"W_radial{i}_T")) if on_tc else h @ W
             if i + 1 < L.n_radial:
                 h = _silu_n(h)
         return h

@@ -172,12 +172,16 @@ int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order
  * cmace_linear_tc_f32 has the contract of cmace_linear_f32 (Nout <= 128); cmace_gemm3x_f32 is the plain
  * out[M,N] = scale * A[M,K] @ B used for the radial multilayer perceptron (which upstream MACE evaluates
  * with torch and the reference replaces by its spline table, models/InvariantMACE.py:226-240).
+ * a_act = 1 applies the perceptron's activation (second-moment normalised SiLU) to A while it is loaded;
+ * ep_z != NULL multiplies the result elementwise by that activation's derivative at ep_z [M,N]; with
+ * these two switches the whole perceptron, forward and backward, is a chain of GEMM calls without any
+ * separate elementwise pass.
  * status: optional device int32, set non-zero if a bounded wait inside the kernel timed out. */
 int64_t cmace_gemm_packed_floats(int nmat, int N, int K);
 int cmace_gemm_pack_weights_f32(const float *Bt, int nmat, int N, int K, float *packed,
                                 cmace_stream_t stream);
 int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale,
-                     float *out, int32_t *status, cmace_stream_t stream);
+                     int a_act, const float *ep_z, float *out, int32_t *status, cmace_stream_t stream);
 int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node_order,
                         const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
                         double scale, float *out, int32_t *status, cmace_stream_t stream);

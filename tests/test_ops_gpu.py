@@ -344,3 +344,32 @@ def test_contraction_generated_and_table_driven_kernels_agree(dtype, dev, U, mon
         assert rel_err(out, ref) < TOL[dtype]["out"] and rel_err(Xg.grad, Xo.grad) < TOL[dtype]["grad"]
         results.append((out.detach(), Xg.grad))
     assert rel_err(results[0][0], results[1][0]) < TOL[dtype]["out"]
+
+
+def test_fused_radial_mlp_matches_oracle(dev):
+    """The GEMM chain with the activation folded into loads and epilogues against the oracle's perceptron,
+    value and gradient with respect to the Bessel features."""
+    import math
+
+    from cuda_mace_b200 import ops
+    from oracle import model as omodel
+
+    g = torch.Generator().manual_seed(12)
+    E = 3000
+    dims = [8, 64, 64, 64, 512]
+    Ws = [torch.randn(dims[i], dims[i + 1], generator=g, dtype=torch.float64) for i in range(4)]
+    b = torch.randn(E, 8, generator=g, dtype=torch.float64) * 0.7
+    bo = b.float().double().clone().requires_grad_(True)
+    ref = omodel.radial_mlp(bo, [W.float().double() for W in Ws])
+    gr = torch.randn(E, 512, generator=g, dtype=torch.float64).float()
+    (ref * gr.double()).sum().backward()
+    Wn = [(W / math.sqrt(W.shape[0])).float().to(dev) for W in Ws]
+    # the oracle divides by sqrt(fan_in) in float64; fold the same factor into float32 weights for the kernel
+    ref2 = omodel.radial_mlp(bo.detach(), [w.double().cpu() * math.sqrt(w.shape[0]) for w in Wn])
+    bg = b.float().to(dev).requires_grad_(True)
+    out = ops.radial_mlp(bg, Wn, [w.t().contiguous() for w in Wn])
+    ops.check_status()
+    assert rel_err(out, ref2) < 5e-6
+    out.backward(gr.to(dev))
+    ops.check_status()
+    assert rel_err(bg.grad, bo.grad) < 2e-5

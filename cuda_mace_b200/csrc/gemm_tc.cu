@@ -234,6 +234,7 @@ struct Tile {
   int l, nl, mat, ntile;
 };
 
+template <int MODE>
 __device__ __forceinline__ Tile locate_tile(const GemmArgs &g, int64_t t) {
   Tile T;
   T.valid = false;
@@ -246,7 +247,7 @@ __device__ __forceinline__ Tile locate_tile(const GemmArgs &g, int64_t t) {
   const uint32_t t32 = (uint32_t)t, rt32 = t32 / (uint32_t)g.n_tiles;
   T.ntile = (int)(t32 - rt32 * (uint32_t)g.n_tiles);
   int64_t rt = rt32;
-  if (g.mode == GT_MODE_PLAIN) {
+  if (MODE == GT_MODE_PLAIN) {
     T.row0 = rt * GT_TILE_M;
     T.valid = T.row0 < g.M;
     T.seg_rows = g.M;
@@ -275,10 +276,11 @@ __device__ __forceinline__ Tile locate_tile(const GemmArgs &g, int64_t t) {
 }
 
 // global row (in units of rows of A / out) of local row r of a tile, or -1
+template <int MODE>
 __device__ __forceinline__ int64_t global_row(const GemmArgs &g, const Tile &T, int r) {
   const int64_t lr = T.row0 + r;
   if (lr >= T.seg_rows) return -1;
-  if (g.mode == GT_MODE_PLAIN) return lr;
+  if (MODE == GT_MODE_PLAIN) return lr;
   // rows of one (element, l) problem fit 32 bits (checked on the host): cheap division
   const uint32_t lr32 = (uint32_t)lr, q = lr32 / (uint32_t)T.nl;
   const int64_t slot = T.seg_begin + q;
@@ -292,7 +294,7 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 
 // ACT: the activation switches (a_act, ep_z) are compiled in only for the variant that uses them, the plain
 // variant measured 14 % faster without the extra code in its producer and epilogue loops
-template <bool ACT>
+template <bool ACT, int MODE>
 __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmArgs g) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[2 * GT_MAX_STAGES + 4];
@@ -356,12 +358,12 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
           head.valid = false;
           return;
         }
-        head.T = locate_tile(g, head.t);
+        head.T = locate_tile<MODE>(g, head.t);
         if (head.T.valid) break;
       }
       head.valid = true;
 #pragma unroll
-      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row(g, head.T, rbase + GT_ROW_STEP * i);
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row<MODE>(g, head.T, rbase + GT_ROW_STEP * i);
     };
     // an item in flight only has to remember where its B block lives (-1: no item)
     auto issue = [&](float4 (&v)[GT_ROWS_PER_THREAD]) -> int64_t {
@@ -461,7 +463,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
     int acc = 0;
     bool ok = true;
     for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
-      const Tile T = locate_tile(g, t);
+      const Tile T = locate_tile<MODE>(g, t);
       if (!T.valid) continue;
       int ncols = g.N - T.ntile * 128;
       ncols = ncols > 128 ? 128 : ncols;
@@ -554,9 +556,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
     for (int64_t t = blockIdx.x; t < g.total_tiles; t += gridDim.x) {
-      const Tile T = locate_tile(g, t);
+      const Tile T = locate_tile<MODE>(g, t);
       if (!T.valid) continue;
-      const int64_t grow = global_row(g, T, r);
+      const int64_t grow = global_row<MODE>(g, T, r);
       const int n0 = T.ntile * 128;
       int ncols = g.N - n0;
       ncols = ncols > 128 ? 128 : ncols;
@@ -690,7 +692,8 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
 #endif
   const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
   const bool act = g.a_act != 0 || g.ep_z != nullptr;
-  auto kern = act ? gemm3x_tf32_kernel<true> : gemm3x_tf32_kernel<false>;
+  auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
+                                       : (act ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN> : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   if (g.total_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many tiles", what);

@@ -141,19 +141,26 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
   for (int64_t e = e0; e < e1; e += 2) {
     const int64_t eb = (e + 1 < e1) ? e + 1 : e;
     const T yv = __ldg(Y + (int64_t)ylm * nedges + (yedge ? eb : e));
+    // loads of both edges of the pair are issued before either is consumed
+    const int64_t s2[2] = {sender[e], sender[eb]};
+    T xx[2][VEC], rr[2][4][VEC];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      load_vec<T, VEC>(xx[h], X + s2[h] * C + c0);
+#pragma unroll
+      for (int l = 0; l < 4; l++) load_vec_stream<T, VEC>(rr[h][l], R + ((h ? eb : e) * 4 + l) * C + c0);
+    }
 #pragma unroll
     for (int h = 0; h < 2; h++) {
       const int64_t ee = h ? eb : e;
       if (h && e + 1 >= e1) break;  // warp-uniform
-      const int64_t s = sender[ee];
-      T x[VEC], r[4][VEC], u[4][VEC], p[16];
-      load_vec<T, VEC>(x, X + s * C + c0);
+      T(&x)[VEC] = xx[h];
+      T(&r)[4][VEC] = rr[h];
+      T u[4][VEC], p[16];
 #pragma unroll
-      for (int l = 0; l < 4; l++) {
-        load_vec_stream<T, VEC>(r[l], R + (ee * 4 + l) * C + c0);
+      for (int l = 0; l < 4; l++)
 #pragma unroll
         for (int v = 0; v < VEC; v++) u[l][v] = T(0);
-      }
 #pragma unroll
       for (int m = 0; m < 16; m++) {
         const T y = __shfl_sync(0xffffffffu, yv, 16 * h + m);

@@ -109,12 +109,16 @@ class ClockSampler:
 
 def algorithmic_bytes(name, s, N, Ns, E, C, Z):
     """Bytes each kernel has to move when every tensor is read or written once (indices 4 B)."""
+    if name.startswith("cmace_gemm3x_f32["):  # tagged with its shape: A [E,K] in, [E,N] out, weights
+        k, n = (int(x.split("=")[1]) for x in name[name.index("[") + 1:-1].split(","))
+        return 4 * (E * k + E * n + k * n)
     base = name[:-4]
     return {
         "cmace_imp_fwd": s * (4 * E * C + 16 * E + Ns * C + 16 * N * C) + 8 * E,
         "cmace_imp_bwd_edge": s * (2 * 4 * E * C + 2 * 16 * E + Ns * C + 16 * N * C) + 8 * E,
         "cmace_imp_bwd_node": s * (E * C + Ns * C) + 4 * E,
         "cmace_linear": s * (16 * N * C * 2 + 4 * Z * C * C),
+        "cmace_linear_tc": s * (16 * N * C * 2 + 4 * Z * C * C),
         "cmace_symcon_fwd": s * (16 * N * C + N * C),
         "cmace_symcon_bwd": s * (16 * N * C * 2 + N * C),
         "cmace_edge_basis_fwd": s * E * (3 + 16 + 8),

@@ -107,8 +107,9 @@ def load():
     return lib
 
 
-def call(name, *args):
-    """Calls a status-returning entry point; raises RuntimeError with the library's message."""
+def call(name, *args, tag=None):
+    """Calls a status-returning entry point; raises RuntimeError with the library's message.
+    `tag` only labels the call in the optional kernel timing (e.g. the GEMM shape)."""
     global launch_count
     lib = load()
     if name in _VALUE_FUNCS:
@@ -122,7 +123,7 @@ def call(name, *args):
         ev0.record()
         rc = getattr(lib, name)(*args)
         ev1.record()
-        _timing.append((name, ev0, ev1))
+        _timing.append((name if tag is None else f"{name}[{tag}]", ev0, ev1))
     else:
         rc = getattr(lib, name)(*args)
     launch_count += n_launch

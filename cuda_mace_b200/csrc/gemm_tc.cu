@@ -78,8 +78,8 @@ struct GemmArgs {
   int64_t total_tiles;          // upper bound of the tile index space
   int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
   int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
-  int a_act;                    // 1: apply the normalised SiLU to A while loading it
-  const float *ep_z;            // when set: out = scale * acc * silu_n'(ep_z[row, col]), ep_z laid out like out
+  int a_act;                    // 1: apply SiLU to A while loading it
+  const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -208,16 +208,16 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(u);
 }
 
-// Second-moment-normalised SiLU of the radial multilayer perceptron, c * x * sigmoid(x), and its derivative.
-constexpr float kSiluNorm = 1.676532470331092f;
+// SiLU of the radial multilayer perceptron, x * sigmoid(x), and its derivative (the second-moment
+// normalisation constant of e3nn's activation is folded into the next layer's weights by the caller).
 // (exp2 and reciprocal on the special-function unit: about 2 ulp each, far inside the float32 targets)
 __device__ __forceinline__ float sigmoid_fast(float x) {
   return __fdividef(1.0f, 1.0f + exp2f(-1.4426950408889634f * x));
 }
-__device__ __forceinline__ float silu_n(float x) { return kSiluNorm * x * sigmoid_fast(x); }
+__device__ __forceinline__ float silu_n(float x) { return x * sigmoid_fast(x); }
 __device__ __forceinline__ float silu_n_grad(float x) {
   const float s = sigmoid_fast(x);
-  return kSiluNorm * s * fmaf(x, 1.0f - s, 1.0f);
+  return s * fmaf(x, 1.0f - s, 1.0f);
 }
 
 // byte offset of the 16-byte chunk c (0..7) of row r inside a swizzled image

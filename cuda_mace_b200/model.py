@@ -53,7 +53,9 @@ class InvariantMACE(torch.nn.Module):
             L = torch.nn.Module()
             L.register_buffer("W_up", (P["W_up"] / math.sqrt(C)).to(**dd))
             for i, W in enumerate(P["W_radial"]):
-                Wn = (W / math.sqrt(W.shape[0])).to(**dd)
+                # 1/sqrt(fan_in) of e3nn's FullyConnectedNet; the second-moment constant of the activation
+                # that feeds layers 1.. is folded in as well, so the activation itself is a plain SiLU
+                Wn = (W / math.sqrt(W.shape[0]) * (SILU_2MOM if i > 0 else 1.0)).to(**dd)
                 L.register_buffer(f"W_radial{i}", Wn)
                 L.register_buffer(f"W_radial{i}_T", Wn.t().contiguous())
             L.n_radial = len(P["W_radial"])
@@ -97,7 +99,7 @@ class InvariantMACE(torch.nn.Module):
         for i, W in enumerate(Ws):
             h = ops.matmul3x(h, W, getattr(L, f"W_radial{i}_T")) if on_tc else h @ W
             if i + 1 < L.n_radial:
-                h = _silu_n(h)
+                h = torch.nn.functional.silu(h)
         return h
 
     def node_energies(self, positions, species, edge_index, shifts, topology=None, exchange=None, n_owned=None):

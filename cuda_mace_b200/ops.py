@@ -116,7 +116,7 @@ def _pack(Bt):
 
 
 def _gemm3x(A, Bt, scale=1.0, act_a=False, ep_z=None):
-    """act(A) [M,K] @ B with Bt = B^T [N,K], optionally times silu_n'(ep_z) elementwise; float32."""
+    """act(A) [M,K] @ B with Bt = B^T [N,K], optionally times silu'(ep_z) elementwise; float32."""
     A = A.contiguous()
     M, K = A.shape
     N = Bt.shape[0]
@@ -126,7 +126,7 @@ def _gemm3x(A, Bt, scale=1.0, act_a=False, ep_z=None):
             raise RuntimeError("ep_z must have the output's shape")
     out = torch.empty(M, N, dtype=torch.float32, device=A.device)
     _abi.call("cmace_gemm3x_f32", _ptr(A), _ptr(_pack(Bt)), M, K, N, float(scale), 1 if act_a else 0, _ptr(ep_z),
-              _ptr(out), _ptr(_status_tensor(A.device)), _stream())
+              _ptr(out), _ptr(_status_tensor(A.device)), _stream(), tag=f"K={K},N={N}")
     return out
 
 
@@ -160,9 +160,10 @@ class _RadialMLPFunction(torch.autograd.Function):
 
 
 def radial_mlp(bessel, weights, weights_t):
-    """Radial multilayer perceptron on the tensor cores (float32): h <- silu_n(h) @ W_i with no
+    """Radial multilayer perceptron on the tensor cores (float32): h <- silu(h) @ W_i with no
     activation before the first and after the last layer.  weights[i] [in,out] already carry the
-    1/sqrt(fan_in) of e3nn's FullyConnectedNet; weights_t[i] are their contiguous transposes."""
+    1/sqrt(fan_in) of e3nn's FullyConnectedNet and, from the second layer on, the second-moment
+    constant of its normalised SiLU; weights_t[i] are their contiguous transposes."""
     _check_cuda(bessel)
     return _RadialMLPFunction.apply(bessel, len(weights), *weights, *weights_t)
 

@@ -172,7 +172,8 @@ int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order
  * cmace_linear_tc_f32 has the contract of cmace_linear_f32 (Nout <= 128); cmace_gemm3x_f32 is the plain
  * out[M,N] = scale * A[M,K] @ B used for the radial multilayer perceptron (which upstream MACE evaluates
  * with torch and the reference replaces by its spline table, models/InvariantMACE.py:226-240).
- * a_act = 1 applies the perceptron's activation (second-moment normalised SiLU) to A while it is loaded;
+ * a_act = 1 applies the perceptron's activation (SiLU; e3nn's second-moment constant is folded into the next
+ * layer's weights) to A while it is loaded;
  * ep_z != NULL multiplies the result elementwise by that activation's derivative at ep_z [M,N]; with
  * these two switches the whole perceptron, forward and backward, is a chain of GEMM calls without any
  * separate elementwise pass.

@@ -363,9 +363,10 @@ def test_fused_radial_mlp_matches_oracle(dev):
     ref = omodel.radial_mlp(bo, [W.float().double() for W in Ws])
     gr = torch.randn(E, 512, generator=g, dtype=torch.float64).float()
     (ref * gr.double()).sum().backward()
-    Wn = [(W / math.sqrt(W.shape[0])).float().to(dev) for W in Ws]
-    # the oracle divides by sqrt(fan_in) in float64; fold the same factor into float32 weights for the kernel
-    ref2 = omodel.radial_mlp(bo.detach(), [w.double().cpu() * math.sqrt(w.shape[0]) for w in Wn])
+    # kernel weights: 1/sqrt(fan_in) folded in, and the activation's normalisation constant from layer 1 on
+    Wn = [(W / math.sqrt(W.shape[0]) * (omodel.SILU_2MOM if i > 0 else 1.0)).float().to(dev) for i, W in enumerate(Ws)]
+    ref2 = omodel.radial_mlp(bo.detach(), [w.double().cpu() * math.sqrt(w.shape[0]) / (omodel.SILU_2MOM if i > 0 else 1.0)
+                                           for i, w in enumerate(Wn)])
     bg = b.float().to(dev).requires_grad_(True)
     out = ops.radial_mlp(bg, Wn, [w.t().contiguous() for w in Wn])
     ops.check_status()

@@ -10,11 +10,14 @@
 // yields Ahi*Bhi and Ahi*Blo from a single instruction (two column ranges of the accumulator, added in the
 // epilogue); with Alo*Bhi that is two instructions per K step instead of three.
 //
-// Structure (one CTA per SM, persistent over 128-row tiles, warp specialised, 13 warps):
-//   warps 0-7  producers: gather 128 rows x 32 columns (one "K block") of A per pipeline stage with
-//              128-byte row segments, split hi/lo in registers and store both images in the 128-byte
-//              swizzled K-major layout tcgen05 expects; one thread also starts the bulk copy of the
-//              matching pre-packed B block (hi and lo images, already swizzled by the pack kernel).
+// Structure (one CTA per SM, persistent over 128-row tiles, warp specialised, 14 warps):
+//   warp 13    loader (PLAIN row map): one TMA tile load (128 rows x 32 columns) of A per pipeline item into
+//              a raw ring in shared memory; nothing waits in registers for HBM.
+//   warps 0-7  converters (PLAIN): read the raw tile from shared memory, split hi/lo and store both images
+//              in the 128-byte swizzled K-major layout tcgen05 expects; one thread also starts the bulk copy
+//              of the matching pre-packed B block (hi and lo images, already swizzled by the pack kernel).
+//              With the LINEAR row map (gathered rows) the same warps load the row segments into registers
+//              themselves, two items ahead, and convert from there.
 //   warp 8     MMA issuer: one elected thread issues tcgen05.mma kind::tf32 (M=128, N<=128, K=8),
 //              4 K-steps x 3 split terms per stage, and commits to the stage's "empty" barrier and,
 //              after the last K block of a tile, to the accumulator's "full" barrier.
@@ -29,7 +32,10 @@
 //
 // Every wait on an mbarrier is bounded; on a time-out the role records a code in *status and leaves
 // its loop, the others time out in turn, and the CTA still frees its tensor memory and returns.
+#include <cuda.h>
+
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -43,8 +49,10 @@ constexpr int GT_B_SLAB_MAX = 128 * 128;            // bytes of one B image per 
 constexpr int GT_PRODUCER_WARPS = 8;                 // 8 measured best (4: 0.47 ms, 8: 0.36 ms, 16: 0.59 ms on the Linear case)
 constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
 constexpr int GT_ROW_STEP = GT_PRODUCER_WARPS * 4;                       // rows between a thread's row segments
-constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + 4) * 32;
-constexpr int GT_SMEM_BUDGET = 227 * 1024;           // dynamic shared memory a CTA may opt in to
+constexpr int GT_LOADER_WARP = GT_PRODUCER_WARPS + 5;    // warp that issues the row copies into the raw ring
+constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + 4 + 1) * 32;
+constexpr int GT_MAX_RAW = 6;                          // raw ring depth upper bound
+constexpr int GT_SMEM_BUDGET = 227 * 1024 - 2048;    // dynamic shared memory (the static barriers count against the same 227 KB)
 constexpr int GT_TMEM_COLS = 512;                   // two accumulators of 2 x 128 columns
 constexpr int GT_PREFETCH = 2;                      // K blocks of global loads in flight per producer thread
 constexpr int GT_EP_STRIDE = 36;                    // floats per row of the epilogue transpose buffer (padded)
@@ -77,6 +85,7 @@ struct GemmArgs {
   int n_tiles, k_blocks, npad;  // packing geometry: N tiles of <= 128 columns, npad rows per B image
   int64_t total_tiles;          // upper bound of the tile index space
   int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
+  int raw_stages;               // depth of the raw A ring (16 KB each) the loader warp fills with bulk copies
   int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
   int a_act;                    // 1: apply SiLU to A while loading it
   const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
@@ -128,6 +137,12 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -295,9 +310,10 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 // ACT: the activation switches (a_act, ep_z) are compiled in only for the variant that uses them, the plain
 // variant measured 14 % faster without the extra code in its producer and epilogue loops
 template <bool ACT, int MODE>
-__global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmArgs g) {
+__global__ void __launch_bounds__(GT_THREADS, 1)
+    gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[2 * GT_MAX_STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * GT_MAX_STAGES + 4 + 2 * GT_MAX_RAW];
   __shared__ uint32_t tmem_base_slot;
 
   // dynamic smem base rounded up to 1024 bytes (the swizzle pattern repeats every 1024 bytes)
@@ -306,6 +322,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
   const uint32_t empty_bar = smem_u32(&bars[GT_MAX_STAGES]);        // + 8*s
   const uint32_t acc_full = smem_u32(&bars[2 * GT_MAX_STAGES]);     // + 8*a
   const uint32_t acc_empty = smem_u32(&bars[2 * GT_MAX_STAGES + 2]);
+  const uint32_t raw_full = smem_u32(&bars[2 * GT_MAX_STAGES + 4]);            // + 8*r
+  const uint32_t raw_empty = smem_u32(&bars[2 * GT_MAX_STAGES + 4 + GT_MAX_RAW]);  // + 8*r
   const int GT_STAGES = g.stages;
   const uint32_t GT_STAGE_BYTES = (uint32_t)g.stage_bytes;
 
@@ -317,6 +335,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
     for (int s = 0; s < GT_STAGES; s++) {
       mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS + 1);   // one arrival per producer warp + the expect_tx arrival
       mbar_init(empty_bar + 8 * s, 1);        // one tcgen05.commit
+    }
+    for (int r = 0; r < g.raw_stages; r++) {
+      mbar_init(raw_full + 8 * r, 1);         // the loader's expect_tx arrival (+ the copies' bytes)
+      mbar_init(raw_empty + 8 * r, GT_PRODUCER_WARPS);  // one arrival per converter warp
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(acc_full + 8 * a, 1);         // one tcgen05.commit
@@ -333,7 +355,91 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
   const int k_blocks = g.k_blocks;
   const uint32_t b_image = (uint32_t)g.npad * 128u;  // bytes of one B image
 
-  if (warp < GT_PRODUCER_WARPS) {
+  // raw ring (16 KB per stage, rows of 128 bytes, not swizzled) sits behind the image stages and the
+  // epilogue buffers
+  const uint32_t raw_base = smem_base + GT_STAGES * GT_STAGE_BYTES + GT_EP_BYTES;
+
+  if (MODE == GT_MODE_PLAIN && warp < GT_PRODUCER_WARPS) {
+    // ================================ converters ================================
+    // Per (tile, K block) item: wait for the loader's rows in the raw ring, split every float into its
+    // hi and lo tf32 parts and write both swizzled operand images of the next free image stage.  The
+    // loop is deliberately tiny (shared-memory loads at fixed offsets, 12 ALU operations and two stores
+    // per 16 bytes): these warps are bound by instruction issue, not by memory.
+    const int p = threadIdx.x;       // 0..255
+    const int chunk = p & 7;         // 16-byte chunk of the 128-byte row segment
+    const int rbase = p >> 3;        // rows rbase + GT_ROW_STEP * i
+    uint32_t soff[GT_ROWS_PER_THREAD];  // the raw tile arrives in the same swizzled layout as the images
+#pragma unroll
+    for (int i = 0; i < GT_ROWS_PER_THREAD; i++) soff[i] = (uint32_t)sw128_offset(rbase + GT_ROW_STEP * i, chunk);
+    int stage = 0, raw = 0;
+    uint32_t phase = 0, raw_phase = 0;
+    for (int64_t t = blockIdx.x; t < g.total_tiles; t += gridDim.x) {
+      const Tile T = locate_tile<MODE>(g, t);
+      if (!T.valid) continue;
+      const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
+                                  ((int64_t)(T.mat * g.n_tiles + T.ntile) * k_blocks) * (2 * (int64_t)b_image);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks; kb++) {
+        uint32_t got = 1;
+        if (lane == 0) {
+          got = mbar_wait(raw_full + 8 * raw, raw_phase) ? 1u : 0u;
+          if (got) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          report(g, 1);
+          ok = false;
+          break;
+        }
+        const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+        const uint32_t sR = raw_base + raw * GT_A_SLAB;
+        if (p == 0) {
+          mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
+          bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
+                        full_bar + 8 * stage);
+        }
+#pragma unroll
+        for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
+          float4 a, hi, lo;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
+                       : "r"(sR + soff[i])
+                       : "memory");
+          if (ACT && g.a_act) {
+            a.x = silu_n(a.x);
+            a.y = silu_n(a.y);
+            a.z = silu_n(a.z);
+            a.w = silu_n(a.w);
+          }
+          hi.x = to_tf32(a.x); lo.x = to_tf32(a.x - hi.x);
+          hi.y = to_tf32(a.y); lo.y = to_tf32(a.y - hi.y);
+          hi.z = to_tf32(a.z); lo.z = to_tf32(a.z - hi.z);
+          hi.w = to_tf32(a.w); lo.w = to_tf32(a.w - hi.w);
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + soff[i]), "f"(hi.x), "f"(hi.y),
+                       "f"(hi.z), "f"(hi.w)
+                       : "memory");
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + GT_A_SLAB + soff[i]), "f"(lo.x),
+                       "f"(lo.y), "f"(lo.z), "f"(lo.w)
+                       : "memory");
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(full_bar + 8 * stage);
+          mbar_arrive(raw_empty + 8 * raw);
+        }
+        if (++stage == GT_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+        if (++raw == g.raw_stages) {
+          raw = 0;
+          raw_phase ^= 1;
+        }
+      }
+      if (!ok) break;
+    }
+  } else if (MODE != GT_MODE_PLAIN && warp < GT_PRODUCER_WARPS) {
     // ================================ producers ================================
     // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
     // GT_PREFETCH items ahead of the conversion in a register ring, so that enough bytes are in flight
@@ -453,6 +559,33 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm3x_tf32_kernel(const GemmAr
           break;
         }
         inflight[d] = issue(buf[d]);
+      }
+    }
+  } else if (warp == GT_LOADER_WARP) {
+    // ================================ loader ================================
+    // PLAIN row map only: one TMA tile load (128 rows x 32 columns, 128-byte swizzle, zero fill outside
+    // the matrix) per pipeline item into the raw ring; a single instruction moves 16 KB and completes on
+    // the stage's barrier, so no register or thread waits on HBM and the ring depth sets the bytes in flight.
+    if (MODE == GT_MODE_PLAIN && lane == 0) {
+      int raw = 0;
+      uint32_t raw_phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
+        const Tile T = locate_tile<MODE>(g, t);
+        if (!T.valid) continue;
+        for (int kb = 0; kb < k_blocks; kb++) {
+          if (!mbar_wait(raw_empty + 8 * raw, raw_phase ^ 1)) {
+            report(g, 5);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(raw_full + 8 * raw, GT_A_SLAB);
+          tma_load_2d(raw_base + raw * GT_A_SLAB, &tmap, kb * GT_KBLOCK, (int)T.row0, raw_full + 8 * raw);
+          if (++raw == g.raw_stages) {
+            raw = 0;
+            raw_phase ^= 1;
+          }
+        }
       }
     }
   } else if (warp == GT_PRODUCER_WARPS) {
@@ -673,6 +806,22 @@ static PackGeom pack_geom(int N, int K) {
   return p;
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time dependency on libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
 static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -685,12 +834,37 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   g.debug = getenv("CMACE_GEMM_DEBUG") ? atoi(getenv("CMACE_GEMM_DEBUG")) : 0;
 #endif
   g.stage_bytes = 2 * GT_A_SLAB + 2 * g.npad * 128;
-  g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024) / g.stage_bytes;
-  if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
+  if (g.mode == GT_MODE_PLAIN) {
+    // leave room for at least three raw stages (16 KB each) next to the image stages
+    g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024 - 3 * GT_A_SLAB) / g.stage_bytes;
+    if (g.stages > 4) g.stages = 4;
+    if (g.stages < 1) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
+    g.raw_stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024 - g.stages * g.stage_bytes) / GT_A_SLAB;
+    if (g.raw_stages > GT_MAX_RAW) g.raw_stages = GT_MAX_RAW;
+  } else {
+    g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024) / g.stage_bytes;
+    if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
+    g.raw_stages = 0;
+  }
 #ifdef CMACE_GEMM_DEBUG
   if (getenv("CMACE_GEMM_STAGES") && atoi(getenv("CMACE_GEMM_STAGES")) < g.stages) g.stages = atoi(getenv("CMACE_GEMM_STAGES"));
 #endif
-  const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
+  const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + (size_t)g.raw_stages * GT_A_SLAB + 1024;
+  CUtensorMap tmap;
+  memset(&tmap, 0, sizeof(tmap));
+  if (g.mode == GT_MODE_PLAIN) {
+    // A [M, K] row-major float32: innermost dimension K, tiles of 32 columns x 128 rows, 128-byte swizzle
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available", what);
+    const cuuint64_t dims[2] = {(cuuint64_t)g.K, (cuuint64_t)g.M};
+    const cuuint64_t strides[1] = {(cuuint64_t)g.K * 4};
+    const cuuint32_t box[2] = {GT_KBLOCK, GT_TILE_M};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(g.A), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (%d)", what, (int)r);
+  }
   const bool act = g.a_act != 0 || g.ep_z != nullptr;
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
                                        : (act ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN> : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>);
@@ -699,7 +873,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (g.total_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many tiles", what);
   int64_t blocks = g.total_tiles < num_sms ? g.total_tiles : num_sms;
   if (blocks < 1) return CMACE_OK;
-  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g);
+  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g, tmap);
   return check_launch(what);
 }
 
@@ -727,7 +901,8 @@ int cmace_gemm_pack_weights_f32(const float *Bt, int nmat, int N, int K, float *
 int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale, int a_act,
                      const float *ep_z, float *out, int32_t *status, cmace_stream_t stream) {
   if (M < 0 || K < 1 || N < 1) return fail(CMACE_ERR_ARG, "cmace_gemm3x: bad size");
-  if (K % 4 != 0 || N % 4 != 0) return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm3x: K and N must be multiples of 4");
+  if (K % 8 != 0 || N % 4 != 0)
+    return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm3x: K must be a multiple of 8 and N a multiple of 4");
   if (M == 0) return CMACE_OK;
   if (!A || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_gemm3x: null pointer");
   if (!aligned16(A) || !aligned16(packed) || !aligned16(out) || !aligned16(ep_z))
@@ -747,8 +922,8 @@ int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node
                         cmace_stream_t stream) {
   if (nnodes < 0 || K < 1 || Nout < 1 || nelements < 1) return fail(CMACE_ERR_ARG, "cmace_linear_tc: bad size");
   if (nnodes > 0x7fffffffLL / 16) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: too many nodes");
-  if (K % 4 != 0 || Nout % 4 != 0 || Nout > 128)
-    return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: K, Nout multiples of 4 and Nout <= 128");
+  if (K % 8 != 0 || Nout % 4 != 0 || Nout > 128)
+    return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: K multiple of 8, Nout multiple of 4 and Nout <= 128");
   if (nnodes == 0) return CMACE_OK;
   if (!X || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_linear_tc: null pointer");
   if ((nelements > 1) != (node_order != nullptr) || (node_order != nullptr) != (elem_start != nullptr))

@@ -190,7 +190,7 @@ def matmul3x(A, W, W_T=None):
 
 
 def tensor_core_ok(dtype, K, N):
-    return USE_TENSOR_CORES and dtype == torch.float32 and K % 4 == 0 and N % 4 == 0
+    return USE_TENSOR_CORES and dtype == torch.float32 and K % 8 == 0 and N % 4 == 0
 
 
 # --------------------------------------------------------------------------------------

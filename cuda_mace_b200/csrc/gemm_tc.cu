@@ -10,19 +10,22 @@
 // yields Ahi*Bhi and Ahi*Blo from a single instruction (two column ranges of the accumulator, added in the
 // epilogue); with Alo*Bhi that is two instructions per K step instead of three.
 //
-// Structure (one CTA per SM, persistent over 128-row tiles, warp specialised, 14 warps):
-//   warp 13    loader (PLAIN row map): one TMA tile load (128 rows x 32 columns) of A per pipeline item into
-//              a raw ring in shared memory; nothing waits in registers for HBM.
-//   warps 0-7  converters (PLAIN): read the raw tile from shared memory, split hi/lo and store both images
-//              in the 128-byte swizzled K-major layout tcgen05 expects; one thread also starts the bulk copy
-//              of the matching pre-packed B block (hi and lo images, already swizzled by the pack kernel).
+// Structure (one CTA per SM, persistent over 128-row tiles, warp specialised, 18 warps):
+//   warp 17    loader (PLAIN row map): per pipeline item one TMA tile load (128 rows x 32 columns of A,
+//              128-byte swizzle) straight into the stage's hi image (the tensor core ignores the low 13
+//              mantissa bits of a float32, so raw data is the hi operand) and one bulk copy of the matching
+//              pre-packed B block (hi and lo images, swizzled by the pack kernel).  Nothing waits in
+//              registers for HBM.
+//   warps 0-7  converters (PLAIN): read the raw tile back from shared memory and store the residual image
+//              lo = tf32(a - trunc(a)) next to it.
 //              With the LINEAR row map (gathered rows) the same warps load the row segments into registers
 //              themselves, two items ahead, and convert from there.
 //   warp 8     MMA issuer: one elected thread issues tcgen05.mma kind::tf32 (M=128, N<=128, K=8),
 //              4 K-steps x 3 split terms per stage, and commits to the stage's "empty" barrier and,
 //              after the last K block of a tile, to the accumulator's "full" barrier.
-//   warps 9-12 epilogue: tcgen05.ld of the accumulator (each thread one row, 32 columns at a time),
-//              scale, store 128 contiguous bytes per thread, release the accumulator.
+//   warps 9-16 epilogue: tcgen05.ld of the accumulator (each thread one row, 16 columns at a time), add the
+//              two column ranges, scale, transpose through shared memory, store 64-byte row pieces,
+//              release the accumulator.
 // Accumulators are double buffered in tensor memory (2 x 256 columns), so the epilogue of tile t
 // overlaps the MMAs of tile t+1, and a 3-stage shared-memory ring overlaps loads with MMAs.
 //
@@ -49,14 +52,14 @@ constexpr int GT_B_SLAB_MAX = 128 * 128;            // bytes of one B image per 
 constexpr int GT_PRODUCER_WARPS = 8;                 // 8 measured best (4: 0.47 ms, 8: 0.36 ms, 16: 0.59 ms on the Linear case)
 constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
 constexpr int GT_ROW_STEP = GT_PRODUCER_WARPS * 4;                       // rows between a thread's row segments
-constexpr int GT_LOADER_WARP = GT_PRODUCER_WARPS + 5;    // warp that issues the row copies into the raw ring
-constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + 4 + 1) * 32;
-constexpr int GT_MAX_RAW = 6;                          // raw ring depth upper bound
+constexpr int GT_EPILOGUE_WARPS = 8;
+constexpr int GT_LOADER_WARP = GT_PRODUCER_WARPS + 1 + GT_EPILOGUE_WARPS;  // warp that starts the asynchronous copies
+constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + GT_EPILOGUE_WARPS + 1) * 32;
 constexpr int GT_SMEM_BUDGET = 227 * 1024 - 2048;    // dynamic shared memory (the static barriers count against the same 227 KB)
 constexpr int GT_TMEM_COLS = 512;                   // two accumulators of 2 x 128 columns
 constexpr int GT_PREFETCH = 2;                      // K blocks of global loads in flight per producer thread
-constexpr int GT_EP_STRIDE = 36;                    // floats per row of the epilogue transpose buffer (padded)
-constexpr int GT_EP_BYTES = 4 * 32 * GT_EP_STRIDE * 4;
+constexpr int GT_EP_STRIDE = 20;                    // floats per row of an epilogue transpose buffer (16 + padding)
+constexpr int GT_EP_BYTES = 8 * 32 * GT_EP_STRIDE * 4;  // one buffer per epilogue warp, 20 KB in all
 constexpr long long GT_TIMEOUT_CYCLES = 4000000000LL;  // about two seconds
 #ifdef CMACE_GEMM_DEBUG
 #define GT_DBG(g, bit) (((g).debug & (bit)) != 0)
@@ -85,7 +88,7 @@ struct GemmArgs {
   int n_tiles, k_blocks, npad;  // packing geometry: N tiles of <= 128 columns, npad rows per B image
   int64_t total_tiles;          // upper bound of the tile index space
   int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
-  int raw_stages;               // depth of the raw A ring (16 KB each) the loader warp fills with bulk copies
+  int raw_stages;               // unused
   int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
   int a_act;                    // 1: apply SiLU to A while loading it
   const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
@@ -187,6 +190,15 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -313,7 +325,7 @@ template <bool ACT, int MODE>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[2 * GT_MAX_STAGES + 4 + 2 * GT_MAX_RAW];
+  __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 4];
   __shared__ uint32_t tmem_base_slot;
 
   // dynamic smem base rounded up to 1024 bytes (the swizzle pattern repeats every 1024 bytes)
@@ -322,8 +334,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   const uint32_t empty_bar = smem_u32(&bars[GT_MAX_STAGES]);        // + 8*s
   const uint32_t acc_full = smem_u32(&bars[2 * GT_MAX_STAGES]);     // + 8*a
   const uint32_t acc_empty = smem_u32(&bars[2 * GT_MAX_STAGES + 2]);
-  const uint32_t raw_full = smem_u32(&bars[2 * GT_MAX_STAGES + 4]);            // + 8*r
-  const uint32_t raw_empty = smem_u32(&bars[2 * GT_MAX_STAGES + 4 + GT_MAX_RAW]);  // + 8*r
+  const uint32_t tma_full = smem_u32(&bars[2 * GT_MAX_STAGES + 4]);   // + 8*s, PLAIN: A tile and B block landed
   const int GT_STAGES = g.stages;
   const uint32_t GT_STAGE_BYTES = (uint32_t)g.stage_bytes;
 
@@ -333,16 +344,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GT_STAGES; s++) {
-      mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS + 1);   // one arrival per producer warp + the expect_tx arrival
+      // LINEAR: one arrival per producer warp + the expect_tx arrival of the B copy; PLAIN: converters only
+      mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS + (MODE == GT_MODE_PLAIN ? 0 : 1));
+      mbar_init(tma_full + 8 * s, 1);         // the loader's expect_tx arrival (+ the copies' bytes)
       mbar_init(empty_bar + 8 * s, 1);        // one tcgen05.commit
-    }
-    for (int r = 0; r < g.raw_stages; r++) {
-      mbar_init(raw_full + 8 * r, 1);         // the loader's expect_tx arrival (+ the copies' bytes)
-      mbar_init(raw_empty + 8 * r, GT_PRODUCER_WARPS);  // one arrival per converter warp
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(acc_full + 8 * a, 1);         // one tcgen05.commit
-      mbar_init(acc_empty + 8 * a, 4);        // one arrival per epilogue warp
+      mbar_init(acc_empty + 8 * a, GT_EPILOGUE_WARPS);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -355,89 +364,71 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   const int k_blocks = g.k_blocks;
   const uint32_t b_image = (uint32_t)g.npad * 128u;  // bytes of one B image
 
-  // raw ring (16 KB per stage, rows of 128 bytes, not swizzled) sits behind the image stages and the
-  // epilogue buffers
-  const uint32_t raw_base = smem_base + GT_STAGES * GT_STAGE_BYTES + GT_EP_BYTES;
-
   if (MODE == GT_MODE_PLAIN && warp < GT_PRODUCER_WARPS) {
     // ================================ converters ================================
-    // Per (tile, K block) item: wait for the loader's rows in the raw ring, split every float into its
-    // hi and lo tf32 parts and write both swizzled operand images of the next free image stage.  The
-    // loop is deliberately tiny (shared-memory loads at fixed offsets, 12 ALU operations and two stores
-    // per 16 bytes): these warps are bound by instruction issue, not by memory.
+    // The loader's TMA puts the raw float32 tile straight into the stage's "hi" image: kind::tf32 reads
+    // the top 19 bits of each float32 and ignores the low 13 mantissa bits (checked on the hardware), so
+    // the raw tile IS the hi operand, hi = trunc_tf32(a).  These warps only add the residual image
+    // lo = tf32(a - hi): one shared-memory load, three ALU operations per float and one store per 16 bytes.
+    // They are bound by instruction issue, hence the tiny loop.
     const int p = threadIdx.x;       // 0..255
     const int chunk = p & 7;         // 16-byte chunk of the 128-byte row segment
     const int rbase = p >> 3;        // rows rbase + GT_ROW_STEP * i
-    uint32_t soff[GT_ROWS_PER_THREAD];  // the raw tile arrives in the same swizzled layout as the images
+    uint32_t soff[GT_ROWS_PER_THREAD];
 #pragma unroll
     for (int i = 0; i < GT_ROWS_PER_THREAD; i++) soff[i] = (uint32_t)sw128_offset(rbase + GT_ROW_STEP * i, chunk);
-    int stage = 0, raw = 0;
-    uint32_t phase = 0, raw_phase = 0;
-    for (int64_t t = blockIdx.x; t < g.total_tiles; t += gridDim.x) {
-      const Tile T = locate_tile<MODE>(g, t);
-      if (!T.valid) continue;
-      const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
-                                  ((int64_t)(T.mat * g.n_tiles + T.ntile) * k_blocks) * (2 * (int64_t)b_image);
-      bool ok = true;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
+      if (!locate_tile<MODE>(g, t).valid) continue;
       for (int kb = 0; kb < k_blocks; kb++) {
         uint32_t got = 1;
-        if (lane == 0) {
-          got = mbar_wait(raw_full + 8 * raw, raw_phase) ? 1u : 0u;
-          if (got) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
-        }
+        const long long tw = GT_NOW();
+        if (lane == 0) got = mbar_wait(tma_full + 8 * stage, phase) ? 1u : 0u;
         got = __shfl_sync(0xffffffffu, got, 0);
+        if (warp == 0) GT_PROF(g, 1, tw);
+        const long long tc = GT_NOW();
         if (!got) {
           report(g, 1);
           ok = false;
           break;
         }
         const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-        const uint32_t sR = raw_base + raw * GT_A_SLAB;
-        if (p == 0) {
-          mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
-          bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
-                        full_bar + 8 * stage);
-        }
 #pragma unroll
         for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
-          float4 a, hi, lo;
+          float4 a, lo;
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                        : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
-                       : "r"(sR + soff[i])
+                       : "r"(sA + soff[i])
                        : "memory");
           if (ACT && g.a_act) {
+            // the activated values replace the raw ones in the hi image
             a.x = silu_n(a.x);
             a.y = silu_n(a.y);
             a.z = silu_n(a.z);
             a.w = silu_n(a.w);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + soff[i]), "f"(a.x), "f"(a.y), "f"(a.z),
+                         "f"(a.w)
+                         : "memory");
           }
-          hi.x = to_tf32(a.x); lo.x = to_tf32(a.x - hi.x);
-          hi.y = to_tf32(a.y); lo.y = to_tf32(a.y - hi.y);
-          hi.z = to_tf32(a.z); lo.z = to_tf32(a.z - hi.z);
-          hi.w = to_tf32(a.w); lo.w = to_tf32(a.w - hi.w);
-          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + soff[i]), "f"(hi.x), "f"(hi.y),
-                       "f"(hi.z), "f"(hi.w)
-                       : "memory");
+          lo.x = to_tf32(a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u));
+          lo.y = to_tf32(a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u));
+          lo.z = to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u));
+          lo.w = to_tf32(a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u));
           asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + GT_A_SLAB + soff[i]), "f"(lo.x),
                        "f"(lo.y), "f"(lo.z), "f"(lo.w)
                        : "memory");
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(full_bar + 8 * stage);
-          mbar_arrive(raw_empty + 8 * raw);
-        }
+        if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+        if (warp == 0) GT_PROF(g, 2, tc);
         if (++stage == GT_STAGES) {
           stage = 0;
           phase ^= 1;
         }
-        if (++raw == g.raw_stages) {
-          raw = 0;
-          raw_phase ^= 1;
-        }
       }
-      if (!ok) break;
     }
   } else if (MODE != GT_MODE_PLAIN && warp < GT_PRODUCER_WARPS) {
     // ================================ producers ================================
@@ -563,27 +554,35 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     }
   } else if (warp == GT_LOADER_WARP) {
     // ================================ loader ================================
-    // PLAIN row map only: one TMA tile load (128 rows x 32 columns, 128-byte swizzle, zero fill outside
-    // the matrix) per pipeline item into the raw ring; a single instruction moves 16 KB and completes on
-    // the stage's barrier, so no register or thread waits on HBM and the ring depth sets the bytes in flight.
+    // PLAIN row map only.  Per pipeline item one thread starts two asynchronous copies that complete on the
+    // stage's barrier: the TMA tile load of A (128 rows x 32 columns, 128-byte swizzle, zeros outside the
+    // matrix) into the hi image, and the bulk copy of the matching pre-packed B block.  Nothing waits in
+    // registers for HBM; the ring depth sets the bytes in flight.
     if (MODE == GT_MODE_PLAIN && lane == 0) {
-      int raw = 0;
-      uint32_t raw_phase = 0;
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
       for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
         const Tile T = locate_tile<MODE>(g, t);
         if (!T.valid) continue;
+        const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
+                                    ((int64_t)(T.mat * g.n_tiles + T.ntile) * k_blocks) * (2 * (int64_t)b_image);
         for (int kb = 0; kb < k_blocks; kb++) {
-          if (!mbar_wait(raw_empty + 8 * raw, raw_phase ^ 1)) {
+          const long long tl = GT_NOW();
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1)) {
             report(g, 5);
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(raw_full + 8 * raw, GT_A_SLAB);
-          tma_load_2d(raw_base + raw * GT_A_SLAB, &tmap, kb * GT_KBLOCK, (int)T.row0, raw_full + 8 * raw);
-          if (++raw == g.raw_stages) {
-            raw = 0;
-            raw_phase ^= 1;
+          GT_PROF(g, 10, tl);
+          const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+          mbar_arrive_expect_tx(tma_full + 8 * stage, GT_A_SLAB + 2 * b_image);
+          tma_load_2d(sA, &tmap, kb * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
+          bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
+                        tma_full + 8 * stage);
+          if (++stage == GT_STAGES) {
+            stage = 0;
+            phase ^= 1;
           }
         }
       }
@@ -682,9 +681,13 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     }
   } else {
     // ================================ epilogue ================================
-    const int q = warp & 3;                 // tensor-memory lane quarter this warp may read
+    // Eight warps: two per tensor-memory lane quarter (a warp may only read lanes 32*(warp%4)..+31), the two
+    // taking alternate 32-column chunks of the tile.  Each chunk goes through a per-warp transpose buffer
+    // in two 16-column halves so that the global stores are 64-byte row pieces, 8 rows per instruction.
+    const int q = warp & 3;                          // tensor-memory lane quarter this warp may read
+    const int half = (warp - (GT_PRODUCER_WARPS + 1)) >> 2;  // which alternate chunks this warp takes
     float *ep_buf = reinterpret_cast<float *>(smem + (smem_base - smem_u32(smem)) + GT_STAGES * GT_STAGE_BYTES) +
-                    q * 32 * GT_EP_STRIDE;
+                    (warp - (GT_PRODUCER_WARPS + 1)) * 32 * GT_EP_STRIDE;
     const int r = q * 32 + lane;            // row of the tile
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
@@ -698,7 +701,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       uint32_t got = 1;
       const long long te = GT_NOW();
       if (lane == 0) got = mbar_wait(acc_full + 8 * acc, acc_phase[acc]) ? 1u : 0u;
-      if (q == 0) GT_PROF(g, 6, te);
+      if (q == 0 && half == 0) GT_PROF(g, 6, te);
       const long long tb = GT_NOW();
       if (!__shfl_sync(0xffffffffu, got, 0)) {
         report(g, 4);
@@ -706,52 +709,55 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * 256 + ((uint32_t)(q * 32) << 16);
-      // the 4 rows x 128 bytes each store instruction of this lane covers: row pointers, once per tile
-      float *rowptr[8];
+      // rows each store instruction of this lane covers (8 rows x 64 bytes): row pointers, once per tile
+      float *rowptr[4];
 #pragma unroll
-      for (int it = 0; it < 8; it++) {
-        const int64_t gr = __shfl_sync(0xffffffffu, grow, it * 4 + (lane >> 3));
-        rowptr[it] = gr >= 0 ? g.out + gr * g.N + n0 + (lane & 7) * 4 : nullptr;
+      for (int it = 0; it < 4; it++) {
+        const int64_t gr = __shfl_sync(0xffffffffu, grow, it * 8 + (lane >> 2));
+        rowptr[it] = gr >= 0 ? g.out + gr * g.N + n0 + (lane & 3) * 4 : nullptr;
       }
-      for (int c0 = 0; c0 < ncols; c0 += 32) {
-        if (GT_DBG(g, 64)) continue;
-        uint32_t v[32], w[32];
-        tmem_ld32_nowait(taddr + c0, v);             // Ahi*Bhi + Alo*Bhi
-        tmem_ld32_nowait(taddr + g.npad + c0, w);    // Ahi*Blo
-        tmem_ld_wait();
-        if (GT_DBG(g, 32)) continue;
-        // lane = row: write the row's 32 values, then read back 4 rows x 128 bytes per instruction
-        float *mine = ep_buf + lane * GT_EP_STRIDE;
+      for (int c0 = half * 32; c0 < ncols; c0 += 64) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          *reinterpret_cast<float4 *>(mine + i) =
-              make_float4((__uint_as_float(v[i]) + __uint_as_float(w[i])) * g.scale,
-                          (__uint_as_float(v[i + 1]) + __uint_as_float(w[i + 1])) * g.scale,
-                          (__uint_as_float(v[i + 2]) + __uint_as_float(w[i + 2])) * g.scale,
-                          (__uint_as_float(v[i + 3]) + __uint_as_float(w[i + 3])) * g.scale);
-        __syncwarp();
-        const bool col_ok = c0 + (lane & 7) * 4 < ncols;
+        for (int h16 = 0; h16 < 32; h16 += 16) {
+          const int cc = c0 + h16;
+          if (cc >= ncols) break;  // warp-uniform
+          uint32_t v[16], w[16];
+          tmem_ld16_nowait(taddr + cc, v);             // Ahi*Bhi + Alo*Bhi
+          tmem_ld16_nowait(taddr + g.npad + cc, w);    // Ahi*Blo
+          tmem_ld_wait();
+          // lane = row: write the row's 16 values, then read back 8 rows x 64 bytes per instruction
+          float *mine = ep_buf + lane * GT_EP_STRIDE;
 #pragma unroll
-        for (int it = 0; it < 8; it++) {
-          const int rr = it * 4 + (lane >> 3);
-          float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 7) * 4);
-          if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) {
-            if (ACT && g.ep_z != nullptr) {
-              const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + c0));
-              o.x *= silu_n_grad(z.x);
-              o.y *= silu_n_grad(z.y);
-              o.z *= silu_n_grad(z.z);
-              o.w *= silu_n_grad(z.w);
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<float4 *>(mine + i) =
+                make_float4((__uint_as_float(v[i]) + __uint_as_float(w[i])) * g.scale,
+                            (__uint_as_float(v[i + 1]) + __uint_as_float(w[i + 1])) * g.scale,
+                            (__uint_as_float(v[i + 2]) + __uint_as_float(w[i + 2])) * g.scale,
+                            (__uint_as_float(v[i + 3]) + __uint_as_float(w[i + 3])) * g.scale);
+          __syncwarp();
+          const bool col_ok = cc + (lane & 3) * 4 < ncols;
+#pragma unroll
+          for (int it = 0; it < 4; it++) {
+            const int rr = it * 8 + (lane >> 2);
+            float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 3) * 4);
+            if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) {
+              if (ACT && g.ep_z != nullptr) {
+                const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + cc));
+                o.x *= silu_n_grad(z.x);
+                o.y *= silu_n_grad(z.y);
+                o.z *= silu_n_grad(z.z);
+                o.w *= silu_n_grad(z.w);
+              }
+              *reinterpret_cast<float4 *>(rowptr[it] + cc) = o;
             }
-            *reinterpret_cast<float4 *>(rowptr[it] + c0) = o;
           }
+          __syncwarp();
         }
-        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
-      if (q == 0) GT_PROF(g, 7, tb);
+      if (q == 0 && half == 0) GT_PROF(g, 7, tb);
       acc_phase[acc] ^= 1;
       acc ^= 1;
     }
@@ -834,22 +840,11 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   g.debug = getenv("CMACE_GEMM_DEBUG") ? atoi(getenv("CMACE_GEMM_DEBUG")) : 0;
 #endif
   g.stage_bytes = 2 * GT_A_SLAB + 2 * g.npad * 128;
-  if (g.mode == GT_MODE_PLAIN) {
-    // leave room for at least three raw stages (16 KB each) next to the image stages
-    g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024 - 3 * GT_A_SLAB) / g.stage_bytes;
-    if (g.stages > 4) g.stages = 4;
-    if (g.stages < 1) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
-    g.raw_stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024 - g.stages * g.stage_bytes) / GT_A_SLAB;
-    if (g.raw_stages > GT_MAX_RAW) g.raw_stages = GT_MAX_RAW;
-  } else {
-    g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024) / g.stage_bytes;
-    if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
-    g.raw_stages = 0;
-  }
-#ifdef CMACE_GEMM_DEBUG
-  if (getenv("CMACE_GEMM_STAGES") && atoi(getenv("CMACE_GEMM_STAGES")) < g.stages) g.stages = atoi(getenv("CMACE_GEMM_STAGES"));
-#endif
-  const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + (size_t)g.raw_stages * GT_A_SLAB + 1024;
+  g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024) / g.stage_bytes;
+  if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
+  if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
+  g.raw_stages = 0;
+  const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   if (g.mode == GT_MODE_PLAIN) {

@@ -5,8 +5,8 @@
 // Every float32 operand x is split as x = hi + lo with hi = tf32(x) and lo = tf32(x - hi) (both rounded to
 // nearest, so the residual is unbiased), and D = Ahi*Bhi + Alo*Bhi + Ahi*Blo is accumulated in float32 in tensor
 // memory, which brings the result to about 2^-21 relative: float32-grade, unlike a single TF32 pass.
-// Issuing a tcgen05.mma costs about 145 cycles whatever its N (measured), so instructions are the scarce
-// resource: the hi and lo images of B sit back to back and are read as ONE operand of twice the rows, which
+// A tcgen05.mma of M=128, K=8 takes 48 cycles at N=64 and 64 cycles at N=128 (measured), so narrow
+// instructions waste the pipe: the hi and lo images of B sit back to back and are read as ONE operand of twice the rows, which
 // yields Ahi*Bhi and Ahi*Blo from a single instruction (two column ranges of the accumulator, added in the
 // epilogue); with Alo*Bhi that is two instructions per K step instead of three.
 //

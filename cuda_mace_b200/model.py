@@ -96,6 +96,10 @@ class InvariantMACE(torch.nn.Module):
         if on_tc and ops.FUSED_RADIAL_ACTIVATION:
             return ops.radial_mlp(bessel, Ws, [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial)])
         h = bessel
+        if on_tc and ops.radial_hidden_ok(bessel.dtype, Ws[:-1]):
+            # all hidden layers and their activations in one kernel, then the last, linear layer
+            h = ops.radial_hidden(bessel, Ws[:-1], [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial - 1)])
+            return ops.matmul3x(h, Ws[-1], getattr(L, f"W_radial{L.n_radial - 1}_T"))
         for i, W in enumerate(Ws):
             h = ops.matmul3x(h, W, getattr(L, f"W_radial{i}_T")) if on_tc else h @ W
             if i + 1 < L.n_radial:

@@ -168,6 +168,58 @@ def radial_mlp(bessel, weights, weights_t):
     return _RadialMLPFunction.apply(bessel, len(weights), *weights, *weights_t)
 
 
+class _RadialHiddenFunction(torch.autograd.Function):
+    """basis [E,nb] -> silu(silu(silu(basis W1) W2) W3) [E,64] in one kernel; the forward keeps the activation
+    derivatives (tiled), the backward is the mirrored chain of three products."""
+
+    @staticmethod
+    def forward(ctx, basis, W1, W2, W3, W1T, W2T, W3T):
+        basis = basis.contiguous()
+        E, nb = basis.shape
+        h3 = torch.empty(E, 64, dtype=torch.float32, device=basis.device)
+        saved = None
+        if basis.requires_grad:
+            n = _abi.call("cmace_radial_hidden_saved_floats", E)
+            saved = torch.empty(max(int(n), 4), dtype=torch.float32, device=basis.device)
+        _abi.call("cmace_radial_hidden_fwd_f32", _ptr(basis), nb, _ptr(_pack(W1T)), _ptr(_pack(W2T)), _ptr(_pack(W3T)),
+                  E, _ptr(h3), _ptr(saved), _ptr(_status_tensor(basis.device)), _stream())
+        ctx.saved = saved
+        ctx.weights = (W1, W2, W3)
+        ctx.nb = nb
+        return h3
+
+    @staticmethod
+    def backward(ctx, g):
+        if ctx.saved is None:
+            raise RuntimeError("radial_hidden: the forward ran without a gradient request")
+        g = g.contiguous()
+        E = g.shape[0]
+        W1, W2, W3 = ctx.weights
+        gb = torch.empty(E, ctx.nb, dtype=torch.float32, device=g.device)
+        _abi.call("cmace_radial_hidden_bwd_f32", _ptr(g), _ptr(ctx.saved), _ptr(_pack(W3)), _ptr(_pack(W2)),
+                  _ptr(_pack(W1)), ctx.nb, E, _ptr(gb), _ptr(_status_tensor(g.device)), _stream())
+        return gb, None, None, None, None, None, None
+
+
+def radial_hidden_ok(dtype, weights):
+    """True when the one-kernel version of the perceptron's hidden layers applies: float32, three hidden layers
+    of width 64 and a basis of 8, 16, 24 or 32 functions."""
+    if not USE_TENSOR_CORES or dtype != torch.float32 or len(weights) != 3:
+        return False
+    nb = weights[0].shape[0]
+    return (nb in (8, 16, 24, 32) and tuple(weights[0].shape) == (nb, 64)
+            and tuple(weights[1].shape) == (64, 64) and tuple(weights[2].shape) == (64, 64))
+
+
+def radial_hidden(basis, weights, weights_t):
+    """Hidden layers of the radial perceptron: silu(... silu(basis @ W1) ...) for three constant float32 weight
+    matrices [nb,64], [64,64], [64,64] (no weight gradients); weights_t are their contiguous transposes."""
+    _check_cuda(basis)
+    if not radial_hidden_ok(basis.dtype, weights):
+        raise RuntimeError("radial_hidden needs float32, a basis of 8/16/24/32 functions and three layers of width 64")
+    return _RadialHiddenFunction.apply(basis, *weights, *weights_t)
+
+
 class _Matmul3xFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, A, W, W_T):

@@ -187,6 +187,23 @@ int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node
                         const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
                         double scale, float *out, int32_t *status, cmace_stream_t stream);
 
+/* ---- hidden layers of the radial multilayer perceptron in one kernel (float32) ---------------------
+ * basis [E, nb] -> h3 = silu(silu(silu(basis W1) W2) W3) [E, 64], nb in {8, 16, 24, 32}, hidden width 64: the
+ * network upstream MACE evaluates with torch (e3nn FullyConnectedNet) and the reference tabulates into its
+ * spline (models/InvariantMACE.py:226-240), without its last, linear layer.  The activations stay in shared /
+ * tensor memory between the layers.  Weights are packed with cmace_gemm_pack_weights_f32 (nmat = 1):
+ * forward packed_wK from Bt = W_K^T [64, in]; backward packed_wKt from Bt = W_K [in, 64].  The normalisation
+ * constants (1/sqrt(fan_in), second moment of the activation) are folded into the weights by the caller.
+ * saved: cmace_radial_hidden_saved_floats(E) floats written by the forward (activation derivatives, tiled) and
+ * read by the backward; NULL in the forward when no backward follows. */
+int64_t cmace_radial_hidden_saved_floats(int64_t nedges);
+int cmace_radial_hidden_fwd_f32(const float *basis, int nb, const float *packed_w1, const float *packed_w2,
+                                const float *packed_w3, int64_t nedges, float *h3, float *saved,
+                                int32_t *status, cmace_stream_t stream);
+int cmace_radial_hidden_bwd_f32(const float *grad_h3, const float *saved, const float *packed_w3t,
+                                const float *packed_w2t, const float *packed_w1t, int nb, int64_t nedges,
+                                float *grad_basis, int32_t *status, cmace_stream_t stream);
+
 /* ---- symmetric contraction (correlation 3, invariant output) ------------------------------
  * Replace jit_symmetric_contraction_forward / _backward
  * (jit_wrappers/src/symmetric_contraction_wrapper.cpp:15-205, kernels

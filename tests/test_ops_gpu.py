@@ -374,3 +374,36 @@ def test_fused_radial_mlp_matches_oracle(dev):
     out.backward(gr.to(dev))
     ops.check_status()
     assert rel_err(bg.grad, bo.grad) < 2e-5
+
+
+@pytest.mark.parametrize("E,nb", [(3000, 8), (128, 8), (517, 16), (1, 32), (70000, 8)])
+def test_hidden_radial_layers_in_one_kernel(E, nb, dev):
+    """Three hidden layers with their activations on chip against the oracle's perceptron without its last
+    layer: value and gradient with respect to the basis, ragged last tile included."""
+    import math
+
+    from cuda_mace_b200 import ops
+    from oracle import model as omodel
+
+    g = torch.Generator().manual_seed(13 + E)
+    dims = [nb, 64, 64, 64]
+    Ws = [torch.randn(dims[i], dims[i + 1], generator=g, dtype=torch.float64).float().double() for i in range(3)]
+    b = (torch.randn(E, nb, generator=g, dtype=torch.float64) * 0.7).float().double()
+    bo = b.clone().requires_grad_(True)
+    # oracle: layers with the activation after every one of them (the perceptron's hidden part)
+    h = bo
+    for W in Ws:
+        h = omodel.silu_n(h @ W / math.sqrt(W.shape[0]))
+    gr = torch.randn(E, 64, generator=g, dtype=torch.float64).float()
+    (h * gr.double()).sum().backward()
+    # kernel weights carry 1/sqrt(fan_in) and, from the second layer on, the activation's constant; the
+    # kernel's output lacks the constant of the last activation
+    Wn = [(W / math.sqrt(W.shape[0]) * (omodel.SILU_2MOM if i > 0 else 1.0)).float().to(dev) for i, W in enumerate(Ws)]
+    bg = b.float().to(dev).requires_grad_(True)
+    out = ops.radial_hidden(bg, Wn, [w.t().contiguous() for w in Wn])
+    ops.check_status()
+    assert out.shape == (E, 64)
+    assert rel_err(out * omodel.SILU_2MOM, h) < 5e-6
+    out.backward(gr.to(dev) * omodel.SILU_2MOM)
+    ops.check_status()
+    assert rel_err(bg.grad, bo.grad) < 2e-5

@@ -51,6 +51,7 @@ SIGNATURES = {
     "cmace_radial_hidden_saved_floats": [_L],
     "cmace_radial_hidden_fwd_f32": [_P, _I, _P, _P, _P, _L, _P, _P, _P, _P],
     "cmace_radial_hidden_bwd_f32": [_P, _P, _P, _P, _P, _I, _L, _P, _P, _P],
+    "cmace_imp_radial_fused_fwd_f32": [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _P, _P, _P, _P],
     "cmace_symcon_plan_create": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, ctypes.POINTER(_P)],
     "cmace_symcon_plan_destroy": [_P],
     "cmace_symcon_plan_nterms": [_P],
@@ -86,7 +87,7 @@ KERNEL_LAUNCHES = {
     "cmace_spline_fwd": 1, "cmace_spline_bwd": 1, "cmace_imp_fwd": 1, "cmace_imp_bwd_edge": 1, "cmace_imp_bwd_edge_f64_noalloc": 2,
     "cmace_imp_bwd_node": 1, "cmace_linear": 1, "cmace_symcon_fwd": 1, "cmace_symcon_bwd": 1,
     "cmace_gemm_pack_weights": 1, "cmace_gemm3x": 1, "cmace_linear_tc": 1,
-    "cmace_radial_hidden_fwd": 1, "cmace_radial_hidden_bwd": 1,
+    "cmace_radial_hidden_fwd": 1, "cmace_radial_hidden_bwd": 1, "cmace_imp_radial_fused_fwd": 1,
 }
 launch_count = 0       # kernels launched through this binding since import
 _timing = None         # list of (name, start_event, end_event) while timing is on

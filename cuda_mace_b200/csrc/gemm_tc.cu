@@ -670,6 +670,23 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Tensor map of a row-major float32 matrix [rows, K] for tile loads of 128 rows x 32 columns with the 128-byte
+// swizzle (zeros outside the matrix): the layout of one K block of a tensor-core operand image.
+int encode_rows_tensor_map(CUtensorMap *tmap, const float *A, int64_t rows, int K, const char *what) {
+  memset(tmap, 0, sizeof(*tmap));
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available", what);
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 4};
+  const cuuint32_t box[2] = {GT_KBLOCK, GT_TILE_M};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(A), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (%d)", what, (int)r);
+  return CMACE_OK;
+}
+
 static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -690,17 +707,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   if (g.mode == GT_MODE_PLAIN) {
-    // A [M, K] row-major float32: innermost dimension K, tiles of 32 columns x 128 rows, 128-byte swizzle
-    EncodeTiledFn enc = encode_tiled_fn();
-    if (enc == nullptr) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available", what);
-    const cuuint64_t dims[2] = {(cuuint64_t)g.K, (cuuint64_t)g.M};
-    const cuuint64_t strides[1] = {(cuuint64_t)g.K * 4};
-    const cuuint32_t box[2] = {GT_KBLOCK, GT_TILE_M};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(g.A), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (%d)", what, (int)r);
+    if (int rc = encode_rows_tensor_map(&tmap, g.A, g.M, g.K, what)) return rc;
   }
   const bool act = g.a_act != 0 || g.ep_z != nullptr;
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>

@@ -97,13 +97,6 @@ __device__ __forceinline__ void silu_both(float z, float &a, float &d) {
   d = s * fmaf(z, 1.0f - s, 1.0f);
 }
 
-// lane 0 polls for the warp; returns false on a time-out
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lane) {
-  uint32_t got = 1;
-  if (lane == 0) got = mbar_wait(bar, parity) ? 1u : 0u;
-  return __shfl_sync(0xffffffffu, got, 0) != 0;
-}
-
 template <bool BACKWARD>
 __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const RadialArgs g) {
   extern __shared__ __align__(1024) unsigned char smem[];

@@ -168,4 +168,14 @@ __device__ __host__ __forceinline__ int sw128_offset(int r, int c) {
   return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
 }
 
+// lane 0 polls for the warp; returns false on a time-out
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lane) {
+  uint32_t got = 1;
+  if (lane == 0) got = mbar_wait(bar, parity) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, got, 0) != 0;
+}
+
+// host side (gemm_tc.cu): tensor map for 128-row x 32-column tile loads of a row-major float32 matrix [rows, K]
+int encode_rows_tensor_map(CUtensorMap *tmap, const float *A, int64_t rows, int K, const char *what);
+
 }  // namespace cmace

@@ -106,6 +106,20 @@ class InvariantMACE(torch.nn.Module):
                 h = torch.nn.functional.silu(h)
         return h
 
+    def _messages(self, L, up, Y, bessel, lengths, send, recv, n_owned, topology):
+        """Radial weights and message passing of one interaction; in float32 with the standard perceptron the
+        hidden layers run in one kernel and the last layer inside the message-passing kernel."""
+        C = self.channels
+        Ws = [getattr(L, f"W_radial{i}") for i in range(L.n_radial)]
+        if (self.radial == "exact" and ops.radial_hidden_ok(up.dtype, Ws[:-1])
+                and ops.FUSED_RADIAL_MESSAGE_PASSING and ops.fused_radial_ok(up.dtype, C, Ws[-1].shape[0])
+                and all(ops.tensor_core_ok(up.dtype, W.shape[0], W.shape[1]) for W in Ws)):
+            hidden = ops.radial_hidden(bessel, Ws[:-1], [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial - 1)])
+            return ops.fused_radial_message_passing(up, Y, hidden, Ws[-1], getattr(L, f"W_radial{L.n_radial - 1}_T"),
+                                                    topology)
+        R = self._radial_weights(L, bessel, lengths).view(-1, 4, C)
+        return self.tp(up, Y, R, send, recv, n_owned, topology=topology)
+
     def node_energies(self, positions, species, edge_index, shifts, topology=None, exchange=None, n_owned=None):
         """Interaction energy per receiving node [n_owned] (float64); differentiable with respect to
         positions.
@@ -133,7 +147,6 @@ class InvariantMACE(torch.nn.Module):
         h = self.embedding.index_select(0, species.long())
         es = []
         for t, L in enumerate(self.layers):
-            R = self._radial_weights(L, bessel, lengths).view(-1, 4, C)
             sc = None
             if t == 1:
                 # FullyConnectedTensorProduct(h, one_hot): sc[n] = h[n] @ W_sc[z_n]
@@ -141,7 +154,7 @@ class InvariantMACE(torch.nn.Module):
                 if exchange is not None:
                     h = exchange(h)
             up = h @ L.W_up
-            m = self.tp(up, Y, R, send, recv, n_owned, topology=topology)
+            m = self._messages(L, up, Y, bessel, lengths, send, recv, n_owned, topology)
             m = L.linear(m)
             if t == 0:
                 m = L.skip(m, species_owned)

@@ -83,6 +83,10 @@ USE_TENSOR_CORES = True   # float32 Linear / ElementalLinear / matmul3x go throu
 # but lengthens the producer and epilogue warps, which bound that kernel: measured 41.3 ms per step with
 # it against 39.9 ms without on the 64 000-atom benchmark, so it is off by default.
 FUSED_RADIAL_ACTIVATION = False
+# Last radial layer formed inside the message-passing forward (R is written once and never read back there).
+# Measured at 64 000 atoms (E = 3.33 M, C = 128): 3.75 ms against 2.25 + 1.23 ms for the GEMM followed by the
+# plain forward, so the model does not use it by default; fused_radial_message_passing() always does.
+FUSED_RADIAL_MESSAGE_PASSING = False
 
 
 def _status_tensor(device):
@@ -337,6 +341,82 @@ class _IMPFunction(torch.autograd.Function):
             _abi.call("cmace_imp_bwd_node_" + _suffix(X), _ptr(T), _ptr(perm), _ptr(send_ptr), topo.nsenders, C,
                       _ptr(gradX), _stream())
         return gradX, gradY, gradR, None
+
+
+def _pack_fused_radial(W_T, C):
+    """Weight image of the fused kernel: one 128-row block per group of 32 channels, rows ordered (l, channel),
+    from W_T [4C, K] (the transpose of the last radial layer W [K, 4C])."""
+    key = _RefCache.key(W_T) + ("fused", C)
+    hit = _packed_cache.get(key)
+    if hit is not None:
+        return hit
+    K = W_T.shape[1]
+    nq = C // 32
+    Bt = W_T.reshape(4, nq, 32, K).permute(1, 0, 2, 3).reshape(nq, 128, K).contiguous()
+    return _packed_cache.put(key, (W_T,), _pack(Bt))
+
+
+def fused_radial_ok(dtype, C, K):
+    """True when the kernel with the last radial layer inside applies (shapes and dtype)."""
+    return USE_TENSOR_CORES and dtype == torch.float32 and C in (32, 64, 96, 128) and K in (32, 64)
+
+
+class _FusedRadialIMPFunction(torch.autograd.Function):
+    """Message passing whose radial weights R = H @ W are formed on the tensor cores inside the scatter
+    kernel.  The forward also writes R when a backward will follow; the backward is the unfused one
+    (edge pass, sender pass, then grad H = grad R @ W^T)."""
+
+    @staticmethod
+    def forward(ctx, X, Y, H, W, W_T, topo):
+        X, Y, H = X.contiguous(), Y.contiguous(), H.contiguous()
+        N, C, E, K = topo.nnodes, X.shape[1], topo.nedges, H.shape[1]
+        if X.shape[0] != topo.nsenders or Y.shape != (16, E) or H.shape[0] != E or W.shape != (K, 4 * C):
+            raise RuntimeError(f"shape mismatch: X {tuple(X.shape)}, Y {tuple(Y.shape)}, H {tuple(H.shape)}, "
+                               f"W {tuple(W.shape)} for {N} nodes and {E} edges")
+        need_grad = any(ctx.needs_input_grad[:3])
+        out = torch.empty(N, 16, C, dtype=torch.float32, device=X.device)
+        R = torch.empty(E, 4, C, dtype=torch.float32, device=X.device) if need_grad else None
+        _abi.call("cmace_imp_radial_fused_fwd_f32", _ptr(X), _ptr(Y), _ptr(H), _ptr(_pack_fused_radial(W_T, C)),
+                  _ptr(topo.sender), _ptr(topo.receiver), N, E, C, K, _ptr(out), _ptr(R),
+                  _ptr(_status_tensor(X.device)), _stream())
+        ctx.save_for_backward(X, Y, W)
+        ctx.R = R
+        ctx.topo = topo
+        return out
+
+    @staticmethod
+    def backward(ctx, G):
+        X, Y, W = ctx.saved_tensors
+        topo, R = ctx.topo, ctx.R
+        G = G.contiguous()
+        N, C, E = topo.nnodes, X.shape[1], topo.nedges
+        need_x = ctx.needs_input_grad[0]
+        gradR = torch.empty_like(R)
+        gradY = torch.empty_like(Y)
+        T = torch.empty(E, C, dtype=X.dtype, device=X.device) if need_x else None
+        nscratch = _abi.call("cmace_imp_bwd_scratch_elems", E, C, 0)
+        scratch = torch.empty(nscratch, dtype=X.dtype, device=X.device) if nscratch > 0 else None
+        _abi.call("cmace_imp_bwd_edge_f32", _ptr(X), _ptr(Y), _ptr(R), _ptr(G), _ptr(topo.sender), _ptr(topo.row_ptr),
+                  N, E, C, _ptr(gradR), _ptr(gradY), _ptr(T), _ptr(scratch), _stream())
+        ctx.R = None
+        gradX = None
+        if need_x:
+            perm, send_ptr = topo.sender_order()
+            gradX = torch.empty(topo.nsenders, C, dtype=X.dtype, device=X.device)
+            _abi.call("cmace_imp_bwd_node_f32", _ptr(T), _ptr(perm), _ptr(send_ptr), topo.nsenders, C, _ptr(gradX),
+                      _stream())
+        gradH = _gemm3x(gradR.view(E, 4 * C), W) if ctx.needs_input_grad[2] else None
+        return gradX, gradY, gradH, None, None, None
+
+
+def fused_radial_message_passing(X, Y, H, W, W_T, topology):
+    """out[i,lm,c] = sum_e X[sender(e),c] Y[lm,e] (H @ W)[e, l(lm)*C + c]: InvariantMessagePassingTP applied to
+    the radial weights H @ W without a separate pass for that product.  X [Ns,C], Y [16,E], H [E,K] (K = 32 or
+    64), W [K,4C] constant float32 (no weight gradient), W_T its contiguous transpose."""
+    _check_cuda(X, Y, H, W, W_T)
+    if not fused_radial_ok(X.dtype, X.shape[1], H.shape[1]):
+        raise RuntimeError("fused_radial_message_passing needs float32, 32/64/96/128 channels and K = 32 or 64")
+    return _FusedRadialIMPFunction.apply(X, Y, H, W, W_T, topology)
 
 
 class InvariantMessagePassingTP(torch.nn.Module):

@@ -204,6 +204,20 @@ int cmace_radial_hidden_bwd_f32(const float *grad_h3, const float *saved, const 
                                 const float *packed_w2t, const float *packed_w1t, int nb, int64_t nedges,
                                 float *grad_basis, int32_t *status, cmace_stream_t stream);
 
+/* ---- message passing with the last radial layer formed on the fly (float32) --------------------------
+ * out[i,lm,c] = sum_e X[sender(e),c] * Y[lm,e] * R[e,l,c] with R = H @ W, H [E,K] (K = 32 or 64) the last hidden
+ * activations of the radial perceptron and W [K,4C] its last layer: cmace_imp_fwd_f32 applied to the product
+ * without a separate pass that writes and re-reads R [E,4,C] (no counterpart in the reference, which reads R from
+ * its spline kernel's output, models/InvariantMACE.py:101-113).  C in {32,64,96,128}.
+ * packed_w: cmace_gemm_pack_weights_f32 of Bt [C/32, 128, K] with Bt[q, l*32 + j, :] = W[:, l*C + q*32 + j].
+ * sender, receiver: the edge list sorted by receiver (the receiver list itself, not the CSR).
+ * R: optional output [E,4,C] for a later backward pass (cmace_imp_bwd_edge_f32), or NULL.
+ * out is zero-filled by the call; partial sums are combined with float atomics. */
+int cmace_imp_radial_fused_fwd_f32(const float *X, const float *Y, const float *H, const float *packed_w,
+                                   const int32_t *sender, const int32_t *receiver, int64_t nnodes,
+                                   int64_t nedges, int nchannels, int K, float *out, float *R,
+                                   int32_t *status, cmace_stream_t stream);
+
 /* ---- symmetric contraction (correlation 3, invariant output) ------------------------------
  * Replace jit_symmetric_contraction_forward / _backward
  * (jit_wrappers/src/symmetric_contraction_wrapper.cpp:15-205, kernels

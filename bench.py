@@ -121,6 +121,10 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
         "cmace_linear_tc": s * (16 * N * C * 2 + 4 * Z * C * C),
         "cmace_symcon_fwd": s * (16 * N * C + N * C),
         "cmace_symcon_bwd": s * (16 * N * C * 2 + N * C),
+        # hidden radial layers: basis in, h3 out, three saved derivative arrays (written forward, read backward)
+        "cmace_radial_hidden_fwd": 4 * E * (8 + 64 + 3 * 64),
+        "cmace_radial_hidden_bwd": 4 * E * (64 + 3 * 64 + 8),
+        "cmace_imp_radial_fused_fwd": 4 * (E * 64 + 16 * E + Ns * C + 16 * N * C + 4 * E * C) + 8 * E,
         "cmace_edge_basis_fwd": s * E * (3 + 16 + 8),
         "cmace_edge_basis_bwd": s * E * (3 + 16 + 8 + 3),
     }.get(base)

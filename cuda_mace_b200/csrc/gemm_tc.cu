@@ -88,7 +88,7 @@ struct GemmArgs {
   int n_tiles, k_blocks, npad;  // packing geometry: N tiles of <= 128 columns, npad rows per B image
   int64_t total_tiles;          // upper bound of the tile index space
   int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
-  int raw_stages;               // unused
+  int b_resident;               // PLAIN: bytes of this CTA's B images kept in shared memory for the whole kernel, or 0
   int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
   int a_act;                    // 1: apply SiLU to A while loading it
   const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
@@ -117,6 +117,12 @@ __device__ __forceinline__ Tile locate_tile(const GemmArgs &g, int64_t t) {
   T.ntile = (int)(t32 - rt32 * (uint32_t)g.n_tiles);
   int64_t rt = rt32;
   if (MODE == GT_MODE_PLAIN) {
+    if (g.b_resident) {
+      // a CTA keeps one column tile of B: iteration j of CTA b works on row tile b / n_tiles + j * (CTAs per column tile)
+      const uint32_t j = t32 / gridDim.x;
+      T.ntile = (int)(blockIdx.x % (uint32_t)g.n_tiles);
+      rt = blockIdx.x / (uint32_t)g.n_tiles + (int64_t)j * (gridDim.x / (uint32_t)g.n_tiles);
+    }
     T.row0 = rt * GT_TILE_M;
     T.valid = T.row0 < g.M;
     T.seg_rows = g.M;
@@ -167,16 +173,18 @@ template <bool ACT, int MODE>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 5];
   __shared__ uint32_t tmem_base_slot;
 
   // dynamic smem base rounded up to 1024 bytes (the swizzle pattern repeats every 1024 bytes)
-  const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
+  const uint32_t smem_first = (smem_u32(smem) + 1023u) & ~1023u;
+  const uint32_t smem_base = smem_first + (uint32_t)g.b_resident;   // the ring starts behind the resident B images
   const uint32_t full_bar = smem_u32(&bars[0]);                 // + 8*s
   const uint32_t empty_bar = smem_u32(&bars[GT_MAX_STAGES]);        // + 8*s
   const uint32_t acc_full = smem_u32(&bars[2 * GT_MAX_STAGES]);     // + 8*a
   const uint32_t acc_empty = smem_u32(&bars[2 * GT_MAX_STAGES + 2]);
   const uint32_t tma_full = smem_u32(&bars[2 * GT_MAX_STAGES + 4]);   // + 8*s, PLAIN: A tile and B block landed
+  const uint32_t b_full = smem_u32(&bars[3 * GT_MAX_STAGES + 4]);     // PLAIN with resident B: images landed
   const int GT_STAGES = g.stages;
   const uint32_t GT_STAGE_BYTES = (uint32_t)g.stage_bytes;
 
@@ -195,6 +203,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       mbar_init(acc_full + 8 * a, 1);         // one tcgen05.commit
       mbar_init(acc_empty + 8 * a, GT_EPILOGUE_WARPS);  // one arrival per epilogue warp
     }
+    mbar_init(b_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == GT_PRODUCER_WARPS) tmem_alloc(smem_u32(&tmem_base_slot), GT_TMEM_COLS);
@@ -404,6 +413,15 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (g.b_resident) {
+        const unsigned char *src = reinterpret_cast<const unsigned char *>(g.packed) +
+                                   ((int64_t)(blockIdx.x % (uint32_t)g.n_tiles) * k_blocks) * (2 * (int64_t)b_image);
+        mbar_arrive_expect_tx(b_full, (uint32_t)g.b_resident);
+        for (uint32_t off = 0; off < (uint32_t)g.b_resident; off += 8192u) {
+          const uint32_t n = (uint32_t)g.b_resident - off < 8192u ? (uint32_t)g.b_resident - off : 8192u;
+          bulk_copy_g2s(smem_first + off, src + off, n, b_full);
+        }
+      }
       for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
         const Tile T = locate_tile<MODE>(g, t);
         if (!T.valid) continue;
@@ -418,10 +436,11 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           }
           GT_PROF(g, 10, tl);
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-          mbar_arrive_expect_tx(tma_full + 8 * stage, GT_A_SLAB + 2 * b_image);
+          mbar_arrive_expect_tx(tma_full + 8 * stage, g.b_resident ? (uint32_t)GT_A_SLAB : GT_A_SLAB + 2 * b_image);
           tma_load_2d(sA, &tmap, kb * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
-          bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
-                        tma_full + 8 * stage);
+          if (!g.b_resident)
+            bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
+                          tma_full + 8 * stage);
           if (++stage == GT_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -436,6 +455,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
     bool ok = true;
+    if (MODE == GT_MODE_PLAIN && g.b_resident) {
+      uint32_t got = 1;
+      if (lane == 0) got = mbar_wait(b_full, 0) ? 1u : 0u;
+      if (!__shfl_sync(0xffffffffu, got, 0)) {
+        report(g, 6);
+        ok = false;
+      }
+    }
     for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
       const Tile T = locate_tile<MODE>(g, t);
       if (!T.valid) continue;
@@ -472,7 +499,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           // descriptors of K step j differ from those of step 0 by j * 32 bytes = 2 address units
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
           const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
-          const uint64_t b_hi0 = umma_desc_sw128(sA + 2 * GT_A_SLAB);
+          const uint64_t b_hi0 =
+              umma_desc_sw128(g.b_resident ? smem_first + (uint32_t)kb * 2u * b_image : sA + 2 * GT_A_SLAB);
           int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
           ksteps = ksteps > 4 ? 4 : ksteps;
           if (GT_DBG(g, 2)) ksteps = 0;
@@ -698,12 +726,15 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
 #ifdef CMACE_GEMM_DEBUG
   g.debug = getenv("CMACE_GEMM_DEBUG") ? atoi(getenv("CMACE_GEMM_DEBUG")) : 0;
 #endif
-  g.stage_bytes = 2 * GT_A_SLAB + 2 * g.npad * 128;
-  g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024) / g.stage_bytes;
+  // PLAIN row map with few K blocks: every CTA keeps the B images of one column tile in shared memory and only
+  // streams A, instead of fetching the same B block from L2 again for every 128-row tile
+  const int b_all = g.k_blocks * 2 * g.npad * 128;
+  g.b_resident = (g.mode == GT_MODE_PLAIN && b_all <= 64 * 1024 && num_sms >= g.n_tiles) ? b_all : 0;
+  g.stage_bytes = 2 * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
+  g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
-  g.raw_stages = 0;
-  const size_t smem = (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
+  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   if (g.mode == GT_MODE_PLAIN) {
@@ -716,6 +747,14 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   if (g.total_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many tiles", what);
   int64_t blocks = g.total_tiles < num_sms ? g.total_tiles : num_sms;
+  if (g.b_resident) {
+    // CTAs per column tile x column tiles; the tile index space becomes (iterations) x (grid)
+    const int64_t row_tiles = g.total_tiles / g.n_tiles;
+    int64_t per_col = num_sms / g.n_tiles;
+    per_col = per_col < row_tiles ? per_col : row_tiles;
+    blocks = per_col * g.n_tiles;
+    g.total_tiles = ((row_tiles + per_col - 1) / per_col) * blocks;
+  }
   if (blocks < 1) return CMACE_OK;
   kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g, tmap);
   return check_launch(what);

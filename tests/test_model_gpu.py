@@ -109,3 +109,21 @@ def test_single_gpu_slab_domain_equals_periodic(U):
     out = m(data)
     assert abs(float(e) - float(out["interaction_energy"])) < 1e-12 * abs(float(e))
     assert rel_err(f, out["forces"]) < 1e-12
+
+
+def test_last_radial_layer_inside_message_passing_matches_oracle(U, monkeypatch):
+    """The float32 model with R = H @ W formed inside the message-passing kernel (off by default) against the
+    oracle, same tolerances as the default path."""
+    from cuda_mace_b200 import ops, systems
+    from oracle import model as omodel
+
+    monkeypatch.setattr(ops, "FUSED_RADIAL_MESSAGE_PASSING", True)
+    s, ei, sh, params, m, data = build("water3000", U, torch.float32, n_atoms=375, seed=1)
+    e, e_inter, f = omodel.energy_and_forces(params, U, torch.from_numpy(s["positions"]),
+                                             systems.one_hot(s["species"], 2), torch.from_numpy(ei), torch.from_numpy(sh))
+    launches = ops._abi.launch_count
+    out = m(data)
+    ops.check_status()
+    assert ops._abi.launch_count > launches
+    assert abs(float(out["interaction_energy"]) - float(e_inter)) < 1e-5 * abs(float(e_inter))
+    assert rel_err(out["forces"], f) < 1e-4

@@ -18,6 +18,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(LIB_DIR, "libcuda_mace_b200.so")
 HOSTCHECK_PATH = os.path.join(LIB_DIR, "libcmace_hostcheck.so")
+TORCH_LIB_PATH = os.path.join(LIB_DIR, "libcuda_mace_b200_torch.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -75,7 +76,32 @@ def build(force=False, verbose=False):
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"g++ failed for hostcheck.cpp:\n{r.stdout}\n{r.stderr}")
+    build_torch_classes(force)
     return LIB_PATH
+
+
+def build_torch_classes(force=False):
+    """The TorchScript custom classes with the reference's names (csrc/torch_classes.cpp) on top of the C-ABI
+    library: compiled with g++ against the installed torch, linked to libcuda_mace_b200.so next to it."""
+    src = os.path.join(CSRC, "torch_classes.cpp")
+    hdr = os.path.join(HERE, "..", "include", "cuda_mace_b200.h")
+    if not force and os.path.exists(TORCH_LIB_PATH) and \
+            os.path.getmtime(TORCH_LIB_PATH) > max(os.path.getmtime(src), os.path.getmtime(hdr)):
+        return TORCH_LIB_PATH
+    import torch
+    from torch.utils import cpp_extension
+
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-w", src, "-o", TORCH_LIB_PATH,
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    cmd += ["-I" + p for p in cpp_extension.include_paths()] + ["-I" + os.path.join(cuda_home, "include")]
+    cmd += ["-L" + torch_lib, "-lc10", "-ltorch", "-ltorch_cpu", "-lc10_cuda", "-ltorch_cuda",
+            "-L" + LIB_DIR, "-lcuda_mace_b200", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed for torch_classes.cpp:\n{r.stdout}\n{r.stderr[-4000:]}")
+    return TORCH_LIB_PATH
 
 
 if __name__ == "__main__":

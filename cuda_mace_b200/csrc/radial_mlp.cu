@@ -91,6 +91,10 @@ __device__ __forceinline__ void store_split(uint32_t s_hi, float4 a) {
                : "memory");
 }
 
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void silu_both(float z, float &a, float &d) {
   const float s = sigmoid_fast(z);
   a = z * s;
@@ -146,8 +150,9 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
   const int64_t ntiles = (g.E + RH_TILE - 1) / RH_TILE;
   const int nchunks = g.nb / 4;           // 16-byte chunks per row of the basis
 
-  // completes one layer: barrier, MMAs by one thread, wait for them
-  auto run_layer = [&](uint32_t sB, int K, int npad) -> bool {
+  // one layer = start_layer (barrier, MMAs issued by one thread) ... finish_layer (wait for them); whatever is
+  // placed between the two overlaps with the tensor core: the global loads of the next elementwise phase
+  auto start_layer = [&](uint32_t sB, int K, int npad) {
     tc_fence_before();
     fence_proxy_async();
     group_sync(group);
@@ -156,26 +161,44 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
       issue_layer(tmem_acc, sA, sB, K, npad);
       umma_commit(mma_bar);
     }
+  };
+  auto finish_layer = [&]() -> bool {
     const bool got = warp_wait(mma_bar, phase, lane);
     phase ^= 1;
     tc_fence_after();
     return got;
   };
+  const int64_t tile_step = (int64_t)gridDim.x * 2;
+  int64_t tile = (int64_t)blockIdx.x * 2 + group;
 
-  for (int64_t tile = (int64_t)blockIdx.x * 2 + group; ok && tile < ntiles; tile += (int64_t)gridDim.x * 2) {
-    const int64_t e = tile * RH_TILE + r;
-    const bool row_ok = e < g.E;
-    float4 *dtile = g.dsave + (tile * 3) * 16 * RH_TILE + (h * 8) * RH_TILE + r;   // + (layer*16 + chunk)*128
-    if (!BACKWARD) {
-      // ---- layer 1 operand: the basis rows, raw + residual images, K block 0
-      for (int idx = gtid; idx < RH_TILE * nchunks; idx += RH_GROUP_THREADS) {
+  if (!BACKWARD) {
+    // the basis rows of a tile: one or two 16-byte chunks per thread, fetched one tile ahead
+    float4 pre[4];
+    auto load_basis = [&](int64_t t) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int idx = gtid + RH_GROUP_THREADS * i;
         const int rr = idx / nchunks, c = idx - rr * nchunks;
-        const int64_t ee = tile * RH_TILE + rr;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (ee < g.E) v = __ldg(reinterpret_cast<const float4 *>(g.in + ee * g.nb) + c);
-        store_split(sA + (uint32_t)sw128_offset(rr, c), v);
+        const int64_t ee = t * RH_TILE + rr;
+        pre[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < ntiles && rr < RH_TILE && ee < g.E) pre[i] = __ldg(reinterpret_cast<const float4 *>(g.in + ee * g.nb) + c);
       }
-      if (!(ok = run_layer(sW[0], g.nb, RH_H))) break;
+    };
+    load_basis(tile);
+    for (; ok && tile < ntiles; tile += tile_step) {
+      const int64_t e = tile * RH_TILE + r;
+      const bool row_ok = e < g.E;
+      float4 *dtile = g.dsave + (tile * 3) * 16 * RH_TILE + (h * 8) * RH_TILE + r;   // + (layer*16 + chunk)*128
+      // ---- layer 1 operand: the basis rows, raw + residual images, K block 0
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int idx = gtid + RH_GROUP_THREADS * i;
+        const int rr = idx / nchunks, c = idx - rr * nchunks;
+        if (rr < RH_TILE) store_split(sA + (uint32_t)sw128_offset(rr, c), pre[i]);
+      }
+      start_layer(sW[0], g.nb, RH_H);
+      load_basis(tile + tile_step);
+      if (!(ok = finish_layer())) break;
       for (int layer = 0; layer < 3; layer++) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
@@ -198,18 +221,53 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
             if (g.dsave != nullptr) dtile[(layer * 16 + c) * RH_TILE] = d;
           }
         }
-        if (layer < 2 && !(ok = run_layer(sW[layer + 1], RH_H, RH_H))) break;
+        if (layer < 2) {
+          start_layer(sW[layer + 1], RH_H, RH_H);
+          if (!(ok = finish_layer())) break;
+        }
       }
-    } else {
-      // ---- grad z3 = grad h3 * d3
+    }
+  } else {
+    // grad h3 and d3 of a tile are fetched while the previous tile's last product runs; d2 and d1 while the
+    // product that precedes their use runs
+    float4 pg[8], pd[8];
+    auto load_first = [&](int64_t t) {
+      const int64_t e = t * RH_TILE + r;
+      const float4 *dt = g.dsave + (t * 3 + 2) * 16 * RH_TILE + (h * 8) * RH_TILE + r;
 #pragma unroll
       for (int c = 0; c < 8; c++) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row_ok) v = __ldg(reinterpret_cast<const float4 *>(g.in + e * RH_H + 32 * h) + c);
-        const float4 d = dtile[(2 * 16 + c) * RH_TILE];
-        store_split(a_row + (uint32_t)sw128_offset(r, c), make_float4(v.x * d.x, v.y * d.y, v.z * d.z, v.w * d.w));
+        pg[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        pd[c] = pg[c];
+        if (t < ntiles) {
+          if (e < g.E) pg[c] = __ldg(reinterpret_cast<const float4 *>(g.in + e * RH_H + 32 * h) + c);
+          pd[c] = dt[c * RH_TILE];
+        }
       }
-      if (!(ok = run_layer(sW[0], RH_H, RH_H))) break;
+    };
+    load_first(tile);
+    for (; ok && tile < ntiles; tile += tile_step) {
+      const int64_t e = tile * RH_TILE + r;
+      const bool row_ok = e < g.E;
+      const float4 *dtile = g.dsave + (tile * 3) * 16 * RH_TILE + (h * 8) * RH_TILE + r;
+      // The phases of a tile wait one after the other for their operands, so HBM latency adds up three times per
+      // tile; pulling the group's next tile (96 KB of derivatives, 32 KB of gradient rows, both contiguous) into L2
+      // a whole tile ahead shortens every one of those waits.
+      if (gtid == 0 && tile + tile_step < ntiles) {   // (two tiles ahead measured slower)
+        const int64_t tn = tile + tile_step;
+        const char *dsrc = reinterpret_cast<const char *>(g.dsave + tn * 3 * 16 * RH_TILE);
+        for (int off = 0; off < 3 * 16 * RH_TILE * 16; off += 32768) l2_prefetch(dsrc + off, 32768);
+        const int64_t rows = g.E - tn * RH_TILE < RH_TILE ? g.E - tn * RH_TILE : RH_TILE;
+        l2_prefetch(reinterpret_cast<const char *>(g.in + tn * RH_TILE * RH_H), (uint32_t)(rows * RH_H * 4));
+      }
+      // ---- grad z3 = grad h3 * d3
+#pragma unroll
+      for (int c = 0; c < 8; c++)
+        store_split(a_row + (uint32_t)sw128_offset(r, c),
+                    make_float4(pg[c].x * pd[c].x, pg[c].y * pd[c].y, pg[c].z * pd[c].z, pg[c].w * pd[c].w));
+      start_layer(sW[0], RH_H, RH_H);
+#pragma unroll
+      for (int c = 0; c < 8; c++) pd[c] = dtile[(16 + c) * RH_TILE];        // d2
+      if (!(ok = finish_layer())) break;
       for (int layer = 1; layer >= 0; layer--) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
@@ -220,7 +278,7 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
 #pragma unroll
           for (int i = 0; i < 4; i++) {
             const int c = half * 4 + i;
-            const float4 d = dtile[(layer * 16 + c) * RH_TILE];
+            const float4 d = pd[c];
             float4 a;
             a.x = (__uint_as_float(v[4 * i]) + __uint_as_float(w[4 * i])) * d.x;
             a.y = (__uint_as_float(v[4 * i + 1]) + __uint_as_float(w[4 * i + 1])) * d.y;
@@ -229,7 +287,14 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
             store_split(a_row + (uint32_t)sw128_offset(r, c), a);
           }
         }
-        if (!(ok = run_layer(sW[2 - layer], RH_H, layer == 0 ? g.npad_last : RH_H))) break;
+        start_layer(sW[2 - layer], RH_H, layer == 0 ? g.npad_last : RH_H);
+        if (layer == 1) {
+#pragma unroll
+          for (int c = 0; c < 8; c++) pd[c] = dtile[c * RH_TILE];            // d1
+        } else {
+          load_first(tile + tile_step);
+        }
+        if (!(ok = finish_layer())) break;
       }
       if (!ok) break;
       // ---- grad basis: columns [0, nb) + [npad, npad + nb) of the accumulator

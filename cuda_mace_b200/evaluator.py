@@ -7,7 +7,9 @@ user of the package makes per step.
 
 `evaluate_host` moves the step's inputs (positions, species, edge list, shifts) to the device,
 rebuilds the edge topology for the list it was given, runs the model and copies energy and forces
-back, so it is the end-to-end path including every host<->device byte.
+back, so it is the end-to-end path including every host<->device byte.  The shift vectors of a periodic
+neighbour list take only a handful of distinct values (lattice translations), so the host batch carries
+them as a small table plus one byte per edge instead of three float64 per edge.
 """
 import torch
 
@@ -52,14 +54,22 @@ class EnergyForceEvaluator:
     # ---- end-to-end path with host buffers ----------------------------------------------------
     def host_batch(self, pos_dtype=torch.float64):
         """Pinned host copies of one step's inputs, as a data loader would hand them over."""
+        import numpy as np
+
         d = self.dom
         pin = lambda t: t.pin_memory() if torch.cuda.is_available() else t
-        return {
+        batch = {
             "positions": pin(torch.as_tensor(d.positions[: d.n_owned], dtype=pos_dtype)),
             "species": pin(torch.as_tensor(d.species, dtype=torch.int32)),
             "edge_index": pin(torch.as_tensor(d.edge_index, dtype=torch.int32)),
-            "shifts": pin(torch.as_tensor(d.shifts, dtype=pos_dtype)),
         }
+        table, index = np.unique(np.asarray(d.shifts), axis=0, return_inverse=True)
+        if table.shape[0] <= 256:
+            batch["shift_table"] = pin(torch.as_tensor(table, dtype=pos_dtype))
+            batch["shift_index"] = pin(torch.as_tensor(index.reshape(-1).astype(np.uint8)))
+        else:  # not a lattice-translation list: ship the vectors themselves
+            batch["shifts"] = pin(torch.as_tensor(d.shifts, dtype=pos_dtype))
+        return batch
 
     @staticmethod
     def h2d_bytes(batch):
@@ -68,7 +78,9 @@ class EnergyForceEvaluator:
     def evaluate_host(self, batch, out_forces=None):
         dev = self.device
         moved = {k: v.to(dev, non_blocking=True) for k, v in batch.items()}
-        self.set_neighbor_list(moved["species"], moved["edge_index"], moved["shifts"])
+        shifts = moved["shifts"] if "shifts" in moved else \
+            moved["shift_table"].index_select(0, moved["shift_index"].to(torch.int64))
+        self.set_neighbor_list(moved["species"], moved["edge_index"], shifts)
         energy, forces = self(moved["positions"])
         if out_forces is None:
             out_forces = torch.empty(forces.shape, dtype=forces.dtype, pin_memory=torch.cuda.is_available())

@@ -127,3 +127,22 @@ def test_last_radial_layer_inside_message_passing_matches_oracle(U, monkeypatch)
     assert ops._abi.launch_count > launches
     assert abs(float(out["interaction_energy"]) - float(e_inter)) < 1e-5 * abs(float(e_inter))
     assert rel_err(out["forces"], f) < 1e-4
+
+
+def test_host_buffer_path_equals_device_resident_path(U):
+    """evaluate_host (pinned host inputs, shift vectors as table + byte index, results copied back) gives the
+    energy and forces of the device-resident call on the same domain."""
+    from cuda_mace_b200 import domain, evaluator
+
+    s, ei, sh, params, m, data = build("cfg0", U, torch.float64)
+    dom = domain.partition_slabs(s["positions"], s["species"], s["box"], 1, 5.0, 0)
+    ev = evaluator.EnergyForceEvaluator(m, dom, "cuda")
+    e_dev, f_dev = ev(ev.load_domain())
+    batch = ev.host_batch()
+    assert "shift_index" in batch and batch["shift_index"].dtype == torch.uint8
+    assert batch["shift_table"].shape[0] <= 27
+    assert evaluator.EnergyForceEvaluator.h2d_bytes(batch) < dom.edge_index.nbytes // 2 + 2 * dom.edge_index.shape[1] + 10 ** 5
+    e_host, f_host = ev.evaluate_host(batch)
+    assert not f_host.is_cuda
+    assert abs(e_host - float(e_dev)) < 1e-12 * abs(e_host)
+    assert rel_err(f_host, f_dev) < 1e-12

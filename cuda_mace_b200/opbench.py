@@ -1,0 +1,168 @@
+"""Op-level timings of the CUDA operators on the isolated-operator configurations of the benchmark spec.
+
+    python -m cuda_mace_b200.opbench [--op all|symcon|imp|fused|linear|radial] [--dtype f32|f64] [--iters 20]
+
+symcon  SymmetricContraction, N = 4096 atoms, 128 channels, 10 species, forward and forward+backward
+imp     InvariantMessagePassing, N = 8192 receivers, Poisson(30) edges each, 128 channels, forward and backward
+fused   message passing with the last radial layer inside (float32), N receivers with Poisson(52) edges each
+linear  Linear, N = 3000 and N = 64000 nodes, 128 channels
+radial  the three hidden radial layers in one kernel (float32), E edges
+
+One JSON line per measurement: CUDA-event time per call (after warm-up, inputs larger than L2 or L2 flushed by
+the other operands of the same call), algorithmic bytes and the bandwidth they imply.  Inputs are seeded
+synthetic tensors with the shapes and distributions of the spec.
+"""
+import argparse
+import json
+
+import torch
+
+from . import cg, ops
+
+
+def _time(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(iters):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / iters
+
+
+def _emit(op, what, ms, nbytes, **extra):
+    line = {"op": op, "case": what, "ms": round(ms, 4), "algorithmic_bytes": int(nbytes),
+            "gb_per_s": round(nbytes / (ms * 1e-3) / 1e9, 1)}
+    line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def _graph(N, mean_degree, gen):
+    deg = torch.poisson(torch.full((N,), float(mean_degree)), generator=gen).long()
+    recv = torch.repeat_interleave(torch.arange(N), deg)
+    send = torch.randint(0, N, (recv.numel(),), generator=gen)
+    return send.int(), recv.int()
+
+
+def bench_symcon(dtype, iters, dev):
+    gen = torch.Generator().manual_seed(1)
+    N, C, Z = 4096, 128, 10
+    s = 4 if dtype == torch.float32 else 8
+    U = cg.u_matrices()
+    W = [torch.randn(Z, n, C, generator=gen, dtype=torch.float64).to(dtype) / n ** 0.5 for n in (23, 4, 1)]
+    mod = ops.SymmetricContraction(*U, *W).to(dev)
+    X = torch.randn(N, 16, C, generator=gen, dtype=torch.float64).to(dtype).to(dev).requires_grad_(True)
+    at = torch.randint(0, Z, (N,), generator=gen, dtype=torch.int32).to(dev)
+
+    def fwd_bwd():
+        X.grad = None
+        (mod(X, at) ** 2).sum().backward()
+
+    with torch.no_grad():
+        _emit("symcon", f"N={N} C={C} Z={Z} forward", _time(lambda: mod(X, at), iters), s * 17 * N * C)
+    _emit("symcon", f"N={N} C={C} Z={Z} forward+backward", _time(fwd_bwd, iters), s * (17 + 33) * N * C)
+
+
+def bench_imp(dtype, iters, dev):
+    gen = torch.Generator().manual_seed(2)
+    N, C = 8192, 128
+    s = 4 if dtype == torch.float32 else 8
+    send, recv = _graph(N, 30, gen)
+    E = send.numel()
+    X = torch.randn(N, C, generator=gen, dtype=torch.float64).to(dtype).to(dev).requires_grad_(True)
+    Y = torch.randn(16, E, generator=gen, dtype=torch.float64).to(dtype).to(dev).requires_grad_(True)
+    R = torch.randn(E, 4, C, generator=gen, dtype=torch.float64).to(dtype).to(dev).requires_grad_(True)
+    topo = ops.EdgeTopology(send.to(dev), recv.to(dev), N, N)
+    tp = ops.InvariantMessagePassingTP()
+    G = torch.randn(N, 16, C, generator=gen, dtype=torch.float64).to(dtype).to(dev)
+    out = tp.forward(X, Y, R, topo.sender, topo.receiver, N, topology=topo)
+    with torch.no_grad():
+        t_f = _time(lambda: tp.forward(X, Y, R, topo.sender, topo.receiver, N, topology=topo), iters)
+    _emit("imp", f"N={N} E={E} C={C} forward", t_f, s * (4 * E * C + 16 * E + N * C + 16 * N * C) + 8 * E)
+    t_b = _time(lambda: torch.autograd.grad(out, (X, Y, R), G, retain_graph=True), iters)
+    _emit("imp", f"N={N} E={E} C={C} backward (edge + sender pass)", t_b,
+          s * (8 * E * C + 32 * E + 2 * N * C + 16 * N * C) + 8 * E)
+
+
+def bench_fused(dtype, iters, dev, nodes):
+    if dtype != torch.float32:
+        return
+    gen = torch.Generator().manual_seed(0)
+    N, C, K = nodes, 128, 64
+    send, recv = _graph(N, 52, gen)
+    E = send.numel()
+    X = torch.randn(N, C, generator=gen).to(dev).requires_grad_(True)
+    Y = torch.randn(16, E, generator=gen).to(dev)
+    H = torch.randn(E, K, generator=gen).to(dev)
+    W = (torch.randn(K, 4 * C, generator=gen) / 8).to(dev)
+    WT = W.t().contiguous()
+    topo = ops.EdgeTopology(send.to(dev), recv.to(dev), N, N)
+    t = _time(lambda: ops.fused_radial_message_passing(X, Y, H, W, WT, topo), iters)
+    ops.check_status()
+    _emit("fused", f"N={N} E={E} C={C} K={K} forward, R written for the backward", t,
+          4 * (E * K + 16 * E + N * C + 16 * N * C + 4 * E * C) + 8 * E)
+    Xd = X.detach()   # no gradient requested: the kernel does not write R
+    t = _time(lambda: ops.fused_radial_message_passing(Xd, Y, H, W, WT, topo), iters)
+    _emit("fused", f"N={N} E={E} C={C} K={K} forward only", t, 4 * (E * K + 16 * E + N * C + 16 * N * C) + 8 * E)
+
+
+def bench_linear(dtype, iters, dev):
+    gen = torch.Generator().manual_seed(3)
+    C = 128
+    s = 4 if dtype == torch.float32 else 8
+    W = (torch.randn(4, C, C, generator=gen, dtype=torch.float64)).to(dtype).to(dev)
+    WT = W.transpose(-1, -2).contiguous()
+    for N in (3000, 64000):
+        X = torch.randn(N, 16, C, generator=gen, dtype=torch.float64).to(dtype).to(dev)
+        with torch.no_grad():
+            t = _time(lambda: ops.linear_forward(X, W, WT), iters)
+        _emit("linear", f"N={N} K=Nout={C}", t, s * (32 * N * C + 4 * C * C), gflops=round(32 * N * C * C / t / 1e6, 1))
+    ops.check_status()
+
+
+def bench_radial(dtype, iters, dev, edges):
+    if dtype != torch.float32:
+        return
+    gen = torch.Generator().manual_seed(4)
+    E = edges
+    Ws = [(torch.randn(a, b, generator=gen) / a ** 0.5).to(dev) for a, b in ((8, 64), (64, 64), (64, 64))]
+    WTs = [w.t().contiguous() for w in Ws]
+    basis = torch.randn(E, 8, generator=gen).to(dev).requires_grad_(True)
+    g = torch.randn(E, 64, generator=gen).to(dev)
+    out = ops.radial_hidden(basis, Ws, WTs)
+    t_f = _time(lambda: ops.radial_hidden(basis, Ws, WTs), iters)
+    _emit("radial", f"E={E} hidden layers forward (derivatives saved)", t_f, 4 * E * (8 + 64 + 192))
+    t_b = _time(lambda: torch.autograd.grad(out, basis, g, retain_graph=True), iters)
+    _emit("radial", f"E={E} hidden layers backward", t_b, 4 * E * (64 + 192 + 8))
+    ops.check_status()
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", default="all", choices=["all", "symcon", "imp", "fused", "linear", "radial"])
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--nodes", type=int, default=64000, help="receivers of the fused case")
+    ap.add_argument("--edges", type=int, default=3331524, help="edges of the radial case")
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("opbench needs a CUDA device (there is no CPU fallback for the kernels)")
+    dev = torch.device("cuda")
+    dtype = torch.float32 if args.dtype == "f32" else torch.float64
+    if args.op in ("all", "symcon"):
+        bench_symcon(dtype, args.iters, dev)
+    if args.op in ("all", "imp"):
+        bench_imp(dtype, args.iters, dev)
+    if args.op in ("all", "linear"):
+        bench_linear(dtype, args.iters, dev)
+    if args.op in ("all", "radial"):
+        bench_radial(dtype, args.iters, dev, args.edges)
+    if args.op in ("all", "fused"):
+        bench_fused(dtype, args.iters, dev, args.nodes)
+
+
+if __name__ == "__main__":
+    main()

@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--atoms-per-gpu", type=int, default=64000)
+    ap.add_argument("--workload", default="slab", choices=["slab", "water3000"],
+                    help="slab: the weak-scaled 4-species configuration (default, the headline); water3000: the "
+                         "single-GPU 3 000-atom H/O box of the spec (1 GPU only)")
     ap.add_argument("--cpu-sample-atoms", type=int, default=400)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -180,6 +183,11 @@ def main():
 
     workload = (f"slab: {args.atoms_per_gpu} atoms per GPU, H:C:N:O 50:30:10:10, 0.1 atoms/A^3, 128-channel "
                 f"2-layer invariant MACE, r_max {R_MAX} A, energy+forces")
+    if args.workload == "water3000":
+        if world != 1:
+            raise SystemExit("the water3000 workload is a single-GPU configuration")
+        workload = (f"water3000: 3000 atoms (1000 O, 2000 H) in a periodic cube at 0.1 atoms/A^3, 128-channel "
+                    f"2-layer invariant MACE, r_max {R_MAX} A, energy+forces")
 
     if args.impl == "reference":
         # the reference has no CPU implementation of its own; the float64 CPU restatement stands in
@@ -217,10 +225,14 @@ def main():
     s_bytes = 4 if args.dtype == "f32" else 8
 
     # ---- workload ------------------------------------------------------------------------------
-    n_total = args.atoms_per_gpu * world
-    sysd = systems.make_system("slab", n_atoms=n_total, seed=4)
+    if args.workload == "water3000":
+        sysd = systems.make_system("water3000")
+        n_total = sysd["positions"].shape[0]
+    else:
+        n_total = args.atoms_per_gpu * world
+        sysd = systems.make_system("slab", n_atoms=n_total, seed=4)
     dom = domain.partition_slabs(sysd["positions"], sysd["species"], sysd["box"], world, R_MAX, rank)
-    params = systems.init_params(128, 4, 1)
+    params = systems.init_params(128, sysd["n_species"], 1)
     net = model.InvariantMACE(params, cg.u_matrices(), dtype=dtype, device=dev)
     ev = evaluator.EnergyForceEvaluator(net, dom, dev)
     pos = ev.load_domain()
@@ -289,7 +301,7 @@ def main():
     per_kernel = {}
     top, top_ms = None, -1.0
     for name, (calls, tot) in sorted(kernel_ms.items()):
-        b = algorithmic_bytes(name, s_bytes, N, Ns, E, 128, 4)
+        b = algorithmic_bytes(name, s_bytes, N, Ns, E, 128, sysd["n_species"])
         avg = tot / calls
         per_kernel[name] = {"calls_per_step": calls / args.steps, "avg_ms": avg,
                             "share_of_step": tot / (ms_per_step * args.steps),
@@ -305,7 +317,7 @@ def main():
                     "traffic_source": (f"ncu capture of a smaller case scaled by edges, {per_edge[1]}"
                                        if per_edge else None),
                     "peak_source": peak_src,
-                    "algorithmic_bytes_per_launch": algorithmic_bytes(top, s_bytes, N, Ns, E, 128, 4),
+                    "algorithmic_bytes_per_launch": algorithmic_bytes(top, s_bytes, N, Ns, E, 128, sysd["n_species"]),
                     "avg_launch_ms": per_kernel[top]["avg_ms"]}
 
     line = {

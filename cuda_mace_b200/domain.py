@@ -101,6 +101,14 @@ class HaloPlan:
         self.send_down = torch.as_tensor(dom.send_down, dtype=torch.long, device=device)
         self.send_up = torch.as_tensor(dom.send_up, dtype=torch.long, device=device)
         self.n_owned, self.n_local = dom.n_owned, dom.n_local
+        self.device = torch.device(device)
+        self._ghost_shift = {}
+
+    def ghost_shift(self, dtype):
+        """Shift vectors of the ghost rows on the device (copied once per dtype, not per step)."""
+        if dtype not in self._ghost_shift:
+            self._ghost_shift[dtype] = torch.as_tensor(self.dom.ghost_shift, dtype=dtype).to(self.device)
+        return self._ghost_shift[dtype]
 
     def _exchange(self, out_down, out_up, in_from_down, in_from_up):
         """Sends out_down / out_up to the lower / upper neighbour and receives their counterparts.
@@ -168,8 +176,7 @@ def distributed_energy_forces(node_energy_fn, dom: SlabDomain, plan: HaloPlan, p
     owned atoms [n_owned], calling exchange(h_owned) -> h_local before the second interaction.
     Returns (total interaction energy summed over ranks, forces on owned atoms [n_owned, 3])."""
     pos = positions_owned.detach().requires_grad_(True)
-    ghost_shift = torch.as_tensor(dom.ghost_shift, dtype=pos.dtype, device=pos.device)
-    pos_local = halo_exchange(pos, plan) + ghost_shift
+    pos_local = halo_exchange(pos, plan) + plan.ghost_shift(pos.dtype)
     e_nodes = node_energy_fn(pos_local, lambda h: halo_exchange(h, plan))
     e_local = e_nodes.sum()
     (g,) = torch.autograd.grad(e_local, pos)

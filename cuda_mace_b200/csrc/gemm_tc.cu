@@ -463,6 +463,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         ok = false;
       }
     }
+    // One thread runs the whole loop: between two batches of MMAs there is nothing but the barrier test and a few
+    // integer operations, no warp-wide shuffle or re-convergence.  Whatever sits between the batches leaves the
+    // tensor core idle (the issue of an MMA blocks until the previous ones have drained, so the queue is shallow).
+    if (lane != 0) ok = false;
     for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
       const Tile T = locate_tile<MODE>(g, t);
       if (!T.valid) continue;
@@ -473,29 +477,25 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       // one MMA gives Ahi*Bhi in columns [0, npad) and Ahi*Blo in columns [npad, 2 npad)
       const uint32_t idesc2 = umma_idesc_tf32(GT_TILE_M, 2 * g.npad);
       const uint32_t idesc1 = umma_idesc_tf32(GT_TILE_M, nmma);
-      uint32_t got = 1;
       const long long ta = GT_NOW();
-      if (lane == 0) got = mbar_wait(acc_empty + 8 * acc, acc_phase[acc] ^ 1) ? 1u : 0u;
-      GT_PROF(g, 3, ta);
-      if (!__shfl_sync(0xffffffffu, got, 0)) {
+      if (!mbar_wait(acc_empty + 8 * acc, acc_phase[acc] ^ 1)) {
         report(g, 2);
         break;
       }
+      GT_PROF(g, 3, ta);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * 256;
       for (int kb = 0; kb < k_blocks; kb++) {
-        got = 1;
         const long long tf = GT_NOW();
-        if (lane == 0 && !GT_DBG(g, 1024)) got = mbar_wait(full_bar + 8 * stage, phase) ? 1u : 0u;
-        GT_PROF(g, 4, tf);
-        const long long ti = GT_NOW();
-        if (!__shfl_sync(0xffffffffu, got, 0)) {
+        if (!GT_DBG(g, 1024) && !mbar_wait(full_bar + 8 * stage, phase)) {
           report(g, 3);
           ok = false;
           break;
         }
+        GT_PROF(g, 4, tf);
+        const long long ti = GT_NOW();
         if (!GT_DBG(g, 512)) tc_fence_after();
-        if (lane == 0) {
+        {
           // descriptors of K step j differ from those of step 0 by j * 32 bytes = 2 address units
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
           const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
@@ -539,7 +539,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           }
           GT_PROF(g, 9, tm1);
         }
-        __syncwarp();
         GT_PROF(g, 5, ti);
         if (++stage == GT_STAGES) {
           stage = 0;

@@ -52,6 +52,12 @@ SIGNATURES = {
     "cmace_radial_hidden_fwd_f32": [_P, _I, _P, _P, _P, _L, _P, _P, _P, _P],
     "cmace_radial_hidden_bwd_f32": [_P, _P, _P, _P, _P, _I, _L, _P, _P, _P],
     "cmace_imp_radial_fused_fwd_f32": [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _P, _P, _P, _P],
+    "cmace_nl_num_cells": [_D, _D, _D, _D],
+    "cmace_nl_cell_ids_f64": [_P, _L, _D, _D, _D, _D, _D, _D, _I, _D, _P, _P],
+    "cmace_nl_count_f64": [_P, _L, _L, _D, _D, _D, _D, _D, _D, _I, _D, _P, _P, _P, _P],
+    "cmace_scan_workspace_bytes": [_L],
+    "cmace_exclusive_scan_i32": [_P, _L, _P, _P, _L, _P],
+    "cmace_nl_fill_f64": [_P, _L, _L, _D, _D, _D, _D, _D, _D, _I, _D, _P, _P, _P, _P, _P, _P, _P, _P],
     "cmace_symcon_plan_create": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, ctypes.POINTER(_P)],
     "cmace_symcon_plan_destroy": [_P],
     "cmace_symcon_plan_nterms": [_P],
@@ -67,13 +73,15 @@ _RESTYPES = {
     "cmace_imp_bwd_scratch_elems": _L,
     "cmace_gemm_packed_floats": _L,
     "cmace_radial_hidden_saved_floats": _L,
+    "cmace_nl_num_cells": _L,
+    "cmace_scan_workspace_bytes": _L,
     "cmace_imp_bwd_edge_f64_noalloc_max_elems": _L,
     "cmace_symcon_plan_destroy": None,
 }
 # functions whose integer result is a value, not a status
 _VALUE_FUNCS = {"cmace_abi_version", "cmace_sender_order_workspace_bytes", "cmace_imp_bwd_scratch_elems",
                 "cmace_gemm_packed_floats", "cmace_imp_bwd_edge_f64_noalloc_max_elems",
-                "cmace_radial_hidden_saved_floats",
+                "cmace_radial_hidden_saved_floats", "cmace_nl_num_cells", "cmace_scan_workspace_bytes",
                 "cmace_symcon_plan_destroy", "cmace_symcon_plan_nterms", "cmace_symcon_plan_nclasses",
                 "cmace_symcon_plan_is_canonical"}
 
@@ -88,6 +96,7 @@ KERNEL_LAUNCHES = {
     "cmace_imp_bwd_node": 1, "cmace_linear": 1, "cmace_symcon_fwd": 1, "cmace_symcon_bwd": 1,
     "cmace_gemm_pack_weights": 1, "cmace_gemm3x": 1, "cmace_linear_tc": 1,
     "cmace_radial_hidden_fwd": 1, "cmace_radial_hidden_bwd": 1, "cmace_imp_radial_fused_fwd": 1,
+    "cmace_nl_cell_ids": 1, "cmace_nl_count": 1, "cmace_exclusive_scan_i32": 1, "cmace_nl_fill": 1,
 }
 launch_count = 0       # kernels launched through this binding since import
 _timing = None         # list of (name, start_event, end_event) while timing is on

@@ -42,6 +42,8 @@ class SlabDomain:
     recv_up: tuple               # (start, count) ghost rows filled by the upper neighbour
     down: int                    # rank of the lower neighbour
     up: int                      # rank of the upper neighbour
+    box: np.ndarray = None       # (3,) edge lengths of the whole periodic system
+    pbc: tuple = (True, True, True)  # periodic axes of the local list: z is open once slabs carry ghost atoms
 
 
 def partition_slabs(positions, species, box, nranks, r_cut, rank):
@@ -54,7 +56,7 @@ def partition_slabs(positions, species, box, nranks, r_cut, rank):
         ei, sh = neighbor_list(positions, box, (True, True, True), r_cut)
         zero = np.zeros(0, dtype=np.int64)
         return SlabDomain(0, 1, N, N, np.arange(N), positions, species, np.zeros_like(positions), ei, sh,
-                          zero, zero, (N, 0), (N, 0), 0, 0)
+                          zero, zero, (N, 0), (N, 0), 0, 0, np.asarray(box, dtype=np.float64), (True, True, True))
     order = np.argsort(positions[:, 2], kind="stable")
     bounds = [(N * p) // nranks for p in range(nranks + 1)]
     zs = positions[order, 2]
@@ -89,7 +91,8 @@ def partition_slabs(positions, species, box, nranks, r_cut, rank):
     ei, sh = neighbor_list(pos_local, box, (True, True, False), r_cut, n_receivers=n_owned)
     return SlabDomain(rank, nranks, n_owned, pos_local.shape[0], mine, pos_local, spec_local, ghost_shift, ei, sh,
                       send_down, send_up, (n_owned, from_down.shape[0]),
-                      (n_owned + from_down.shape[0], from_up.shape[0]), down, up)
+                      (n_owned + from_down.shape[0], from_up.shape[0]), down, up,
+                      np.asarray(box, dtype=np.float64), (True, True, False))
 
 
 class HaloPlan:

@@ -36,6 +36,26 @@ class EnergyForceEvaluator:
         self.topology = ops.EdgeTopology(edge_index[1], edge_index[0], self.dom.n_owned, self.dom.n_local)
         return self
 
+    def rebuild_neighbor_list(self, positions_owned, r_cut=None):
+        """Builds the neighbour list of the current positions on the device (cell-list kernels) instead of taking
+        it from the host: ghost positions come from the neighbouring slabs, receivers are the owned atoms, the
+        slab's z axis is open once it carries ghosts.  One host synchronisation (edge count)."""
+        d = self.dom
+        if d.box is None:
+            raise RuntimeError("the domain does not carry its box")
+        r_cut = float(self.model.r_max if r_cut is None else r_cut)
+        with torch.no_grad():
+            pos_local = _domain.halo_exchange(positions_owned.detach(), self.plan) + self.plan.ghost_shift(positions_owned.dtype)
+        lo, ext = [0.0, 0.0, 0.0], [float(v) for v in d.box]
+        for ax in range(3):
+            if not d.pbc[ax]:
+                zmin, zmax = float(pos_local[:, ax].min()), float(pos_local[:, ax].max())
+                lo[ax], ext[ax] = zmin, max(zmax - zmin, 1e-6) * (1 + 1e-12) + 1e-9
+        edge_index, shifts, _ = ops.neighbor_list(pos_local, ext, d.pbc, r_cut, d.n_owned, lo=lo)
+        if self.species is None:
+            self.species = torch.as_tensor(d.species, dtype=torch.int32, device=self.device)
+        return self.set_neighbor_list(self.species, edge_index, shifts.to(positions_owned.dtype))
+
     def load_domain(self, pos_dtype=torch.float64):
         d = self.dom
         dev = self.device

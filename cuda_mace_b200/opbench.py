@@ -1,12 +1,13 @@
 """Op-level timings of the CUDA operators on the isolated-operator configurations of the benchmark spec.
 
-    python -m cuda_mace_b200.opbench [--op all|symcon|imp|fused|linear|radial] [--dtype f32|f64] [--iters 20]
+    python -m cuda_mace_b200.opbench [--op all|symcon|imp|fused|linear|radial|nlist] [--dtype f32|f64] [--iters 20]
 
 symcon  SymmetricContraction, N = 4096 atoms, 128 channels, 10 species, forward and forward+backward
 imp     InvariantMessagePassing, N = 8192 receivers, Poisson(30) edges each, 128 channels, forward and backward
 fused   message passing with the last radial layer inside (float32), N receivers with Poisson(52) edges each
 linear  Linear, N = 3000 and N = 64000 nodes, 128 channels
 radial  the three hidden radial layers in one kernel (float32), E edges
+nlist   neighbour list of the 64 000-atom slab system on the device (cell-list kernels) and on the host (numpy)
 
 One JSON line per measurement: CUDA-event time per call (after warm-up, inputs larger than L2 or L2 flushed by
 the other operands of the same call), algorithmic bytes and the bandwidth they imply.  Inputs are seeded
@@ -140,9 +141,30 @@ def bench_radial(dtype, iters, dev, edges):
     ops.check_status()
 
 
+def bench_nlist(iters, dev, nodes):
+    import time
+
+    import numpy as np
+
+    from . import systems
+
+    s = systems.make_system("slab", n_atoms=nodes)
+    pos = torch.from_numpy(s["positions"]).to(dev)
+    box = np.asarray(s["box"], dtype=np.float64)
+    ei, sh, si = ops.neighbor_list(pos, box, (True, True, True), 5.0)
+    E = int(ei.shape[1])
+    t = _time(lambda: ops.neighbor_list(pos, box, (True, True, True), 5.0), iters)
+    _emit("nlist", f"N={nodes} E={E} periodic box, device cell list (includes the host read of the edge count)", t,
+          nodes * 24 + E * (8 + 3 + 24))
+    t0 = time.perf_counter()
+    ei_h, sh_h = systems.neighbor_list(s["positions"], box, (True, True, True), 5.0)
+    _emit("nlist", f"N={nodes} E={ei_h.shape[1]} periodic box, host cell list (numpy, 1 call)",
+          (time.perf_counter() - t0) * 1e3, nodes * 24 + E * (8 + 3 + 24))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="all", choices=["all", "symcon", "imp", "fused", "linear", "radial"])
+    ap.add_argument("--op", default="all", choices=["all", "symcon", "imp", "fused", "linear", "radial", "nlist"])
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--nodes", type=int, default=64000, help="receivers of the fused case")
@@ -162,6 +184,8 @@ def main():
         bench_radial(dtype, args.iters, dev, args.edges)
     if args.op in ("all", "fused"):
         bench_fused(dtype, args.iters, dev, args.nodes)
+    if args.op in ("all", "nlist"):
+        bench_nlist(args.iters, dev, args.nodes)
 
 
 if __name__ == "__main__":

@@ -299,6 +299,55 @@ def topology_for(sender, receiver, nnodes, nsenders=None):
 
 
 # --------------------------------------------------------------------------------------
+# neighbour list on the device
+# --------------------------------------------------------------------------------------
+def neighbor_list(positions, box, pbc, r_cut, n_receivers=None, lo=(0.0, 0.0, 0.0)):
+    """Full neighbour list of an orthorhombic cell, built on the device with a cell list.
+
+    positions [N,3] CUDA tensor (converted to float64); box (3,) edge lengths (for a non-periodic axis the
+    extent the atoms lie in, starting at `lo`); pbc (3,) bools; only the first `n_receivers` atoms receive.
+    Returns edge_index [2,E] int32 (row 0 receivers, sorted; row 1 senders), shifts [E,3] float64 with
+    vector = pos[sender] - pos[receiver] + shift, and shift_index [E,3] int8 (shift = shift_index * box):
+    the same list as cuda_mace_b200.systems.neighbor_list builds on the host.  One host synchronisation (the
+    edge count) to size the outputs."""
+    _check_cuda(positions)
+    pos = positions.detach().to(torch.float64).contiguous()
+    dev = pos.device
+    n = int(pos.shape[0])
+    nrecv = n if n_receivers is None else int(n_receivers)
+    geom = [float(v) for v in lo] + [float(v) for v in box]
+    mask = sum(1 << d for d in range(3) if bool(pbc[d]))
+    st = _stream()
+    i32 = dict(dtype=torch.int32, device=dev)
+    ncells = int(_abi.call("cmace_nl_num_cells", *geom[3:], float(r_cut)))
+    if ncells < 1:
+        raise RuntimeError("neighbor_list: bad box or cutoff")
+    cell_id = torch.empty(max(n, 1), **i32)
+    _abi.call("cmace_nl_cell_ids_f64", _ptr(pos), n, *geom, mask, float(r_cut), _ptr(cell_id), st)
+    nbytes = int(_abi.call("cmace_sender_order_workspace_bytes", n))
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+    perm = torch.empty(max(n, 1), **i32)
+    cell_ptr = torch.empty(ncells + 1, **i32)
+    _abi.call("cmace_sender_order", _ptr(cell_id), n, ncells, _ptr(perm), _ptr(cell_ptr), _ptr(ws), nbytes, st)
+    count = torch.zeros(nrecv + 1, **i32)
+    _abi.call("cmace_nl_count_f64", _ptr(pos), n, nrecv, *geom, mask, float(r_cut), _ptr(perm), _ptr(cell_ptr),
+              _ptr(count), st)
+    row_ptr = torch.empty(nrecv + 1, **i32)
+    sbytes = int(_abi.call("cmace_scan_workspace_bytes", nrecv + 1))
+    sws = torch.empty(sbytes, dtype=torch.uint8, device=dev)
+    _abi.call("cmace_exclusive_scan_i32", _ptr(count), nrecv + 1, _ptr(row_ptr), _ptr(sws), sbytes, st)
+    E = int(row_ptr[nrecv].item())
+    sender = torch.empty(E, **i32)
+    receiver = torch.empty(E, **i32)
+    shift_index = torch.empty(E, 3, dtype=torch.int8, device=dev)
+    shifts = torch.empty(E, 3, dtype=torch.float64, device=dev)
+    if E > 0:
+        _abi.call("cmace_nl_fill_f64", _ptr(pos), n, nrecv, *geom, mask, float(r_cut), _ptr(perm), _ptr(cell_ptr),
+                  _ptr(row_ptr), _ptr(sender), _ptr(receiver), _ptr(shift_index), _ptr(shifts), st)
+    return torch.stack([receiver, sender]), shifts, shift_index
+
+
+# --------------------------------------------------------------------------------------
 # invariant message passing
 # --------------------------------------------------------------------------------------
 class _IMPFunction(torch.autograd.Function):

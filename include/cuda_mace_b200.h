@@ -56,6 +56,35 @@ int cmace_group_by_element(const int32_t *elem, int64_t nnodes, int nelements, i
                            int32_t *elem_start, void *workspace, int64_t workspace_bytes,
                            cmace_stream_t stream);
 
+/* ---- neighbour list on the device (orthorhombic cell, cell list) -----------------------------------
+ * The step before the hot path: upstream builds the list on the host (matscipy / ASE; the reference's tests use
+ * tests/test_utils.py:97-105) and the reference recomputes the receiver offsets on every call
+ * (src/invariant_message_passing.cpp:22); no counterpart inside the reference library.
+ * Full list, receivers = the first nrecv atoms, sorted by receiver:
+ *   vector(e) = pos[sender[e]] - pos[receiver[e]] + shift_idx[e] * (lx, ly, lz),  |vector| < r_cut.
+ * pos [natoms,3] float64; (lox,loy,loz) + (lx,ly,lz) the box (for a non-periodic axis: the range the atoms
+ * lie in); pbc_mask bit d = axis d periodic (then lx >= r_cut).  Sequence:
+ *   1. cmace_nl_cell_ids_f64            -> cell_id [natoms]
+ *   2. cmace_sender_order(cell_id, natoms, cmace_nl_num_cells(...), perm, cell_ptr [ncells+1], ...)
+ *   3. cmace_nl_count_f64               -> count [nrecv]
+ *   4. cmace_exclusive_scan_i32 over count[0..nrecv] (count[nrecv] = 0) -> row_ptr [nrecv+1]; E = row_ptr[nrecv]
+ *   5. cmace_nl_fill_f64                -> sender [E], receiver [E], shift_idx [E,3] int8 and/or shifts [E,3]
+ * row_ptr is the receiver CSR cmace_imp_* take.  The edges of a receiver come out in a fixed order. */
+int64_t cmace_nl_num_cells(double lx, double ly, double lz, double r_cut);
+int cmace_nl_cell_ids_f64(const double *pos, int64_t natoms, double lox, double loy, double loz, double lx,
+                          double ly, double lz, int pbc_mask, double r_cut, int32_t *cell_id,
+                          cmace_stream_t stream);
+int cmace_nl_count_f64(const double *pos, int64_t natoms, int64_t nrecv, double lox, double loy, double loz,
+                       double lx, double ly, double lz, int pbc_mask, double r_cut, const int32_t *perm,
+                       const int32_t *cell_ptr, int32_t *count, cmace_stream_t stream);
+int64_t cmace_scan_workspace_bytes(int64_t n);
+int cmace_exclusive_scan_i32(const int32_t *in, int64_t n, int32_t *out, void *workspace,
+                             int64_t workspace_bytes, cmace_stream_t stream);
+int cmace_nl_fill_f64(const double *pos, int64_t natoms, int64_t nrecv, double lox, double loy, double loz,
+                      double lx, double ly, double lz, int pbc_mask, double r_cut, const int32_t *perm,
+                      const int32_t *cell_ptr, const int32_t *row_ptr, int32_t *sender, int32_t *receiver,
+                      int8_t *shift_idx, double *shifts, cmace_stream_t stream);
+
 /* ---- per-edge basis: spherical harmonics (+ Bessel x cutoff) -----------------------------
  * cmace_sph_* replace jit_spherical_harmonics / jit_spherical_harmonics_backward
  * (jit_wrappers/src/spherical_harmonics_wrapper.cpp:15-137, kernels

@@ -44,6 +44,13 @@ def worker(rank, world, port, out_dir):
         p = ev.load_domain()
         e, f = ev(p)
         ops.check_status()
+        # second pass with the neighbour list of the slab (owned + ghost atoms, open z axis) rebuilt on the device
+        n_edges = ev.edge_index.shape[1]
+        ev.rebuild_neighbor_list(p)
+        assert ev.edge_index.shape[1] == n_edges
+        e2, f2 = ev(p)
+        assert abs(float(e2) - float(e)) < 1e-11 * abs(float(e))
+        assert float((f2 - f).abs().max()) < 1e-10 * float(f.abs().max())
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), e=e.cpu().numpy(), f=f.cpu().numpy(), ids=dom.owned_global)
         dist.barrier()
     finally:

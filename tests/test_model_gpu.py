@@ -146,3 +146,22 @@ def test_host_buffer_path_equals_device_resident_path(U):
     assert not f_host.is_cuda
     assert abs(e_host - float(e_dev)) < 1e-12 * abs(e_host)
     assert rel_err(f_host, f_dev) < 1e-12
+
+
+def test_neighbor_list_built_on_the_device_gives_the_same_energy_and_forces(U):
+    """The evaluator with its neighbour list rebuilt on the device from the positions (cell-list kernels) against the
+    same evaluator fed with the host list: same edge count, energy and forces to rounding (edge order inside a
+    receiver differs, so sums are reordered)."""
+    from cuda_mace_b200 import domain, evaluator
+
+    s, ei, sh, params, m, data = build("cfg0", U, torch.float64)
+    dom = domain.partition_slabs(s["positions"], s["species"], s["box"], 1, 5.0, 0)
+    ev = evaluator.EnergyForceEvaluator(m, dom, "cuda")
+    pos = ev.load_domain()
+    e_host, f_host = ev(pos)
+    n_edges_host = ev.edge_index.shape[1]
+    ev.rebuild_neighbor_list(pos)
+    assert ev.edge_index.shape[1] == n_edges_host and ev.edge_index.dtype == torch.int32
+    e_dev, f_dev = ev(pos)
+    assert abs(float(e_dev) - float(e_host)) < 1e-11 * abs(float(e_host))
+    assert rel_err(f_dev, f_host) < 1e-10

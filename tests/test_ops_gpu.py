@@ -445,3 +445,51 @@ def test_message_passing_with_the_last_radial_layer_inside(N, deg, C, K, nsend, 
     assert rel_err(Xg.grad, Xo.grad) < 1e-4
     assert rel_err(Yg.grad, Yo.grad) < 1e-4
     assert rel_err(Hg.grad, Ho.grad) < 1e-4
+
+
+def _edge_keys(edge_index, shift_index):
+    """One sortable integer per edge: (receiver, sender, shift index triple)."""
+    ei = edge_index.long().cpu()
+    si = shift_index.long().cpu() + 2
+    return torch.sort(((ei[0] * (2 ** 22) + ei[1]) * 125 + (si[:, 0] * 25 + si[:, 1] * 5 + si[:, 2])))[0]
+
+
+@pytest.mark.parametrize("name,n_atoms,pbc", [("cfg0", None, (True, True, True)), ("water3000", 375, (True, True, True)),
+                                              ("water3000", 3000, (True, True, True)), ("slab", 6000, (True, True, False)),
+                                              ("cfg0", None, (False, False, False))])
+def test_device_neighbor_list_equals_host_list(name, n_atoms, pbc, dev):
+    """The cell-list kernels give exactly the host list: same edges, same shifts (bit-exact index work), sorted by
+    receiver; also with a box of two cells per axis (cfg0), open boundaries, and receivers = a prefix of the atoms."""
+    import numpy as np
+
+    from cuda_mace_b200 import ops, systems
+
+    s = systems.make_system(name, n_atoms=n_atoms)
+    pos, box = s["positions"], np.asarray(s["box"], dtype=np.float64)
+    lo = np.zeros(3)
+    ext = box.copy()
+    for d in range(3):
+        if not pbc[d]:
+            lo[d], ext[d] = pos[:, d].min(), max(pos[:, d].max() - pos[:, d].min(), 1e-6) * (1 + 1e-12) + 1e-9
+    for n_recv in (None, pos.shape[0] // 3):
+        ei_h, sh_h = systems.neighbor_list(pos, box, pbc, 5.0, n_recv)
+        ei_d, sh_d, si_d = ops.neighbor_list(torch.from_numpy(pos).to(dev), ext, pbc, 5.0, n_recv, lo=lo)
+        assert ei_d.dtype == torch.int32 and ei_d.shape == (2, ei_h.shape[1])
+        assert bool((ei_d[0, 1:] >= ei_d[0, :-1]).all())          # sorted by receiver
+        si_h = torch.from_numpy(np.rint(sh_h / box).astype(np.int64))
+        assert torch.equal(_edge_keys(ei_d, si_d), _edge_keys(torch.from_numpy(ei_h), si_h))
+        assert torch.equal(sh_d.cpu(), si_d.double().cpu() * torch.from_numpy(ext))
+        # every vector is inside the cutoff
+        p = torch.from_numpy(pos).to(dev)
+        v = p[ei_d[1].long()] - p[ei_d[0].long()] + sh_d
+        assert float(v.norm(dim=1).max()) < 5.0 if v.numel() else True
+
+
+def test_device_neighbor_list_without_atoms_or_edges(dev):
+    from cuda_mace_b200 import ops
+
+    far = torch.tensor([[1.0, 1.0, 1.0], [20.0, 20.0, 20.0]], dtype=torch.float64, device=dev)
+    ei, sh, si = ops.neighbor_list(far, (40.0, 40.0, 40.0), (True, True, True), 5.0)
+    assert ei.shape == (2, 0) and sh.shape == (0, 3)
+    with pytest.raises(RuntimeError):
+        ops.neighbor_list(far, (3.0, 40.0, 40.0), (True, True, True), 5.0)  # periodic axis shorter than the cutoff

@@ -48,6 +48,9 @@ def parse():
     ap.add_argument("--cpu-sample-atoms", type=int, default=400)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--graph", action="store_true",
+                    help="1 GPU: replay the step as a CUDA graph in the device-resident leg (no per-kernel timings, "
+                         "no roofline object); useful for small systems, which are launch-bound")
     return ap.parse_args()
 
 
@@ -244,6 +247,10 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident timing ------------------------------------------------------------------
+    if args.graph:
+        if world != 1:
+            raise SystemExit("--graph needs a single GPU")
+        ev.capture(pos)
     for _ in range(max(args.warmup, 3)):
         energy, forces = ev(pos)
     barrier()
@@ -271,6 +278,7 @@ def main():
     # ---- end-to-end timing with host buffers -----------------------------------------------------
     e2e_value, h2d, d2h = None, 0, 0
     if not args.no_e2e:
+        ev._graph = None    # the host-buffer leg rebuilds the topology every step and runs eagerly
         batch = ev.host_batch()
         out_forces = torch.empty(N, 3, dtype=torch.float64, pin_memory=True)
         # the device-resident leg above leaves the host link idle; a few more warm-up calls than the minimum let it

@@ -27,6 +27,7 @@ class EnergyForceEvaluator:
         self.edge_index = None
         self.shifts = None
         self.topology = None
+        self._graph = None
 
     def set_neighbor_list(self, species, edge_index, shifts):
         """Device tensors: species [n_local] int32, edge_index [2,E] int32 (receivers sorted), shifts [E,3]."""
@@ -34,6 +35,7 @@ class EnergyForceEvaluator:
         self.edge_index = edge_index
         self.shifts = shifts
         self.topology = ops.EdgeTopology(edge_index[1], edge_index[0], self.dom.n_owned, self.dom.n_local)
+        self._graph = None   # a captured step belongs to the list it was captured with
         return self
 
     def rebuild_neighbor_list(self, positions_owned, r_cut=None):
@@ -64,7 +66,35 @@ class EnergyForceEvaluator:
                                torch.as_tensor(d.shifts, dtype=pos_dtype, device=dev))
         return torch.as_tensor(d.positions[: d.n_owned], dtype=pos_dtype, device=dev)
 
+    def capture(self, positions_owned):
+        """Records the whole energy+force step for the current neighbour list as a CUDA graph; later calls copy
+        the positions into the graph's input and replay it, which removes the per-launch cost that dominates
+        small systems (about a hundred launches per step).  Single-rank domains only: the halo exchange of a
+        multi-rank step is host-driven.  A new neighbour list drops the recording."""
+        if self.dom.nranks != 1:
+            raise RuntimeError("capture() needs a single-rank domain")
+        self._graph = None
+        static_pos = positions_owned.detach().clone()
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):      # warm-up outside the recording: weight packing, caches, allocator pools
+                self(static_pos)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        ops.check_status()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            energy, forces = self(static_pos)
+        self._graph = (graph, static_pos, energy, forces)
+        return self
+
     def __call__(self, positions_owned):
+        if self._graph is not None and not torch.cuda.is_current_stream_capturing():
+            graph, static_pos, energy, forces = self._graph
+            static_pos.copy_(positions_owned)
+            graph.replay()
+            return energy.clone(), forces.clone()
+
         def node_energy(pos_local, exchange):
             return self.model.node_energies(pos_local, self.species, self.edge_index, self.shifts,
                                             topology=self.topology, exchange=exchange, n_owned=self.dom.n_owned)

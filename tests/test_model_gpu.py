@@ -165,3 +165,25 @@ def test_neighbor_list_built_on_the_device_gives_the_same_energy_and_forces(U):
     e_dev, f_dev = ev(pos)
     assert abs(float(e_dev) - float(e_host)) < 1e-11 * abs(float(e_host))
     assert rel_err(f_dev, f_host) < 1e-10
+
+
+def test_captured_step_replays_with_new_positions(U):
+    """The step recorded as a CUDA graph gives, for positions it was not recorded with, the energy and forces of the
+    eager step; a new neighbour list drops the recording."""
+    from cuda_mace_b200 import domain, evaluator, ops
+
+    s, ei, sh, params, m, data = build("cfg0", U, torch.float32)
+    dom = domain.partition_slabs(s["positions"], s["species"], s["box"], 1, 5.0, 0)
+    ev = evaluator.EnergyForceEvaluator(m, dom, "cuda")
+    pos = ev.load_domain()
+    moved = pos + 0.01 * torch.randn(pos.shape, generator=torch.Generator().manual_seed(1), dtype=pos.dtype).cuda()
+    e_ref, f_ref = ev(moved)
+    ev.capture(pos)
+    launches = ops._abi.launch_count
+    e_rep, f_rep = ev(moved)
+    ops.check_status()
+    assert ops._abi.launch_count == launches          # replayed, not re-launched from Python
+    assert abs(float(e_rep) - float(e_ref)) < 1e-6 * abs(float(e_ref))
+    assert rel_err(f_rep, f_ref) < 1e-5
+    ev.set_neighbor_list(ev.species, ev.edge_index, ev.shifts)
+    assert ev._graph is None

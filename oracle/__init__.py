@@ -25,4 +25,11 @@ MACE / e3nn definitions: PARITY UNPINNED against upstream MACE for those parts.
 The operator semantics that live in the reference tree itself (the files listed
 above) are followed line by line and the small committed fixtures under
 tests/golden/ freeze this restatement's outputs.
+
+PINNED against the reference's own code, run on seeded inputs
+(tests/golden/make_reference_pins.py -> tests/golden/reference_pins.npz): the
+sparse packing of the U tensors (cuda_mace/ops/symmetric_contraction.py:91-187,
+bit for bit) and the natural-spline coefficient solve
+(cuda_mace/ops/cubic_spline.py:41-84).  The reference's kernels themselves only
+run on a GPU through its cmake / NVRTC build, which this project does not run.
 """

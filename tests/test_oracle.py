@@ -172,3 +172,48 @@ def test_spline_tabulation_tracks_exact_radial(U):
     assert (spl - exact).abs().max() < 1e-4 * exact.abs().max()
     assert oops.cubic_spline_eval(torch.tensor([5.5], dtype=torch.float64), P["spline_knots"], P["spline_coeffs"],
                                   P["spline_h"], 5.0).abs().max() == 0
+
+
+def _reference_pins():
+    import os
+
+    import numpy as np
+
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_pins.npz"))
+
+
+def test_sparse_u_tables_equal_the_reference_packing(U):
+    """The sparse U tables of the oracle and of the package equal, entry for entry, what the reference's own
+    setup_sparse_matrices (cuda_mace/ops/symmetric_contraction.py:91-187, run by tests/golden/make_reference_pins.py)
+    makes of the same dense U tensors: counts, packed index words (k, path and the two partner paths), values."""
+    import numpy as np
+
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    z = _reference_pins()
+    U32 = [u.to(torch.float32) for u in U]
+    for pack in (oops.pack_sparse_u, ops.pack_sparse_u):
+        maxnz, n3, i3, v3, n2, i2, v2, n1, i1 = pack(*U32)
+        assert int(maxnz) == int(z["u3_max_nonsparse"]) == 3
+        for mine, ref in ((n3, "U3_num_nonsparse"), (i3, "U3_indices"), (n2, "U2_num_nonsparse"), (i2, "U2_indices"),
+                          (n1, "U1_num_values"), (i1, "U1_index")):
+            assert np.array_equal(mine.cpu().numpy().astype(np.int64), z[ref].astype(np.int64)), ref
+        assert np.array_equal(v3.cpu().numpy().astype(np.float32), z["U3_values"])
+        assert np.array_equal(v2.cpu().numpy().astype(np.float32), z["U2_values"])
+    assert int(z["U3_num_nonsparse"].sum()) == 353 and int((z["U3_num_nonsparse"] > 0).sum()) == 234
+
+
+def test_spline_coefficients_equal_the_reference_solve():
+    """Natural-spline coefficients against the reference's own tridiagonal solve
+    (cuda_mace/ops/cubic_spline.py:41-84) on the same knots and values."""
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    z = _reference_pins()
+    x, y, h = torch.from_numpy(z["spline_knots"]), torch.from_numpy(z["spline_values"]), float(z["spline_h"])
+    ref = torch.from_numpy(z["spline_coefficients"])
+    for solve in (oops.cubic_spline_coefficients, ops.cubic_spline_coefficients):
+        got = solve(x, y, h)
+        assert got.shape == ref.shape
+        assert float((got - ref).abs().max()) < 1e-12 * float(ref.abs().max())

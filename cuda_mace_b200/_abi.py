@@ -52,6 +52,7 @@ SIGNATURES = {
     "cmace_radial_hidden_fwd_f32": [_P, _I, _P, _P, _P, _L, _P, _P, _P, _P],
     "cmace_radial_hidden_bwd_f32": [_P, _P, _P, _P, _P, _I, _L, _P, _P, _P],
     "cmace_imp_radial_fused_fwd_f32": [_P, _P, _P, _P, _P, _P, _L, _L, _I, _I, _P, _P, _P, _P],
+    "cmace_imp_staged_stalled": [],
     "cmace_nl_num_cells": [_D, _D, _D, _D],
     "cmace_nl_cell_ids_f64": [_P, _L, _D, _D, _D, _D, _D, _D, _I, _D, _P, _P],
     "cmace_nl_count_f64": [_P, _L, _L, _D, _D, _D, _D, _D, _D, _I, _D, _P, _P, _P, _P],
@@ -82,6 +83,7 @@ _RESTYPES = {
 _VALUE_FUNCS = {"cmace_abi_version", "cmace_sender_order_workspace_bytes", "cmace_imp_bwd_scratch_elems",
                 "cmace_gemm_packed_floats", "cmace_imp_bwd_edge_f64_noalloc_max_elems",
                 "cmace_radial_hidden_saved_floats", "cmace_nl_num_cells", "cmace_scan_workspace_bytes",
+                "cmace_imp_staged_stalled",
                 "cmace_symcon_plan_destroy", "cmace_symcon_plan_nterms", "cmace_symcon_plan_nclasses",
                 "cmace_symcon_plan_is_canonical"}
 

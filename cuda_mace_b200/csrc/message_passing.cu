@@ -16,6 +16,8 @@
 //   gradY[m, e]  = sum_c G[i, m, c] * R[e, l, c] * X[s, c]   (16-value warp transpose-reduce)
 // Backward, node pass: gradX[s, c] = sum over the edges sent by s of T[e, c], walking the
 // sender-grouped edge permutation; again one warp per node, no atomics.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cmace {
@@ -192,6 +194,186 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
   }
 }
 
+// ---- edge pass with the R rows staged through shared memory (float32, 128 channels) -------------------------
+// The kernel above keeps the loads of one pair of edges in flight per warp, and the register budget allows 12
+// warps per SM: about 48 KB in flight, not enough to cover HBM latency at full bandwidth.  Here every warp owns a
+// ring of BS_SLOTS shared-memory slots; one lane starts, BS_SLOTS edges ahead of where the warp computes, a bulk
+// copy of the edge's four R rows (2 KB, contiguous) and of its sender's feature row (512 B) that completes on the
+// slot's mbarrier.  160 KB per SM are then on their way from HBM at any time, independent of registers.
+// The arithmetic per edge is that of imp_bwd_edge_kernel.  Receivers are dealt out cyclically to the warps of a
+// persistent grid; every wait is bounded and sets *stalled when it gives up.  Measured at 64 000 atoms: 3.36 ms with
+// the register-prefetch kernel, 3.38 ms with 8 warps x 8 slots (two warps per scheduler cannot hide the latency of
+// their own instruction chains), 3.06 ms with 16 warps x 4 slots, 3.22 ms with 16 x 5 (the modulo by 5).
+constexpr int BS_WARPS = 16;
+constexpr int BS_SLOTS = 4;
+constexpr int BS_C = 128;
+constexpr int BS_R_BYTES = 4 * BS_C * 4;
+constexpr int BS_SLOT_BYTES = BS_R_BYTES + BS_C * 4;
+constexpr long long BS_TIMEOUT_CYCLES = 4000000000LL;
+
+struct EdgeCursor {
+  int64_t node, e, e1;
+};
+
+__device__ __forceinline__ void cursor_seek(EdgeCursor &c, const int32_t *__restrict__ row_ptr, int64_t nnodes,
+                                            int64_t stride) {
+  while (c.node < nnodes) {
+    c.e = row_ptr[c.node];
+    c.e1 = row_ptr[c.node + 1];
+    if (c.e < c.e1) return;
+    c.node += stride;
+  }
+  c.e = c.e1 = -1;
+}
+__device__ __forceinline__ void cursor_next(EdgeCursor &c, const int32_t *__restrict__ row_ptr, int64_t nnodes,
+                                            int64_t stride) {
+  if (++c.e < c.e1) return;
+  c.node += stride;
+  cursor_seek(c, row_ptr, nnodes, stride);
+}
+
+__global__ void __launch_bounds__(BS_WARPS * 32, 1)
+    imp_bwd_edge_staged_kernel(const float *__restrict__ X, const float *__restrict__ Y, const float *__restrict__ R,
+                               const float *__restrict__ G, const int32_t *__restrict__ sender,
+                               const int32_t *__restrict__ row_ptr, int64_t nnodes, int64_t nedges,
+                               float *__restrict__ gradR, float *__restrict__ gy, float *__restrict__ Tout,
+                               int *__restrict__ stalled) {
+  extern __shared__ __align__(128) unsigned char bs_smem[];
+  __shared__ __align__(8) uint64_t bs_bars[BS_WARPS][BS_SLOTS];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(bs_smem) + (uint32_t)w * BS_SLOTS * BS_SLOT_BYTES;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&bs_bars[w][0]);
+  if (lane == 0) {
+    for (int s = 0; s < BS_SLOTS; s++)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8 * s), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  const int64_t stride = (int64_t)gridDim.x * BS_WARPS;
+  EdgeCursor ic, cc;   // where copies are issued, where the warp computes
+  ic.node = cc.node = (int64_t)blockIdx.x * BS_WARPS + w;
+  cursor_seek(ic, row_ptr, nnodes, stride);
+  cc = ic;
+  int64_t chunk_base = -1, chunk_node = -1;
+  int snd = 0;
+  uint32_t icount = 0, ccount = 0;
+
+  auto issue_one = [&]() {
+    if (ic.e < 0) return;
+    // sender indices of the issue stream, 32 at a time
+    if (ic.node != chunk_node || ic.e >= chunk_base + 32) {
+      chunk_node = ic.node;
+      chunk_base = ic.e;
+      snd = (ic.e + lane < ic.e1) ? sender[ic.e + lane] : 0;
+    }
+    const int s = __shfl_sync(0xffffffffu, snd, (int)(ic.e - chunk_base));
+    if (lane == 0) {
+      const uint32_t slot = ring + (icount % BS_SLOTS) * BS_SLOT_BYTES, bar = bar0 + 8 * (icount % BS_SLOTS);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(BS_SLOT_BYTES) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(slot),
+                   "l"(R + ic.e * (4 * BS_C)), "r"(BS_R_BYTES), "r"(bar)
+                   : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       slot + BS_R_BYTES),
+                   "l"(X + (int64_t)s * BS_C), "r"(BS_C * 4), "r"(bar)
+                   : "memory");
+    }
+    icount++;
+    cursor_next(ic, row_ptr, nnodes, stride);
+  };
+  for (int i = 0; i < BS_SLOTS; i++) issue_one();
+
+  const int c0 = lane * 4;
+  const int ylm = lane & 15;
+  float g[16][4];
+  int64_t g_node = -1;
+  float yv_next = cc.e >= 0 ? __ldg(Y + (int64_t)ylm * nedges + cc.e) : 0.f;
+  while (cc.e >= 0) {
+    const int64_t e = cc.e, node = cc.node;
+    EdgeCursor nc = cc;
+    cursor_next(nc, row_ptr, nnodes, stride);
+    const float yv = yv_next;
+    if (nc.e >= 0) yv_next = __ldg(Y + (int64_t)ylm * nedges + nc.e);
+    if (node != g_node) {
+      g_node = node;
+#pragma unroll
+      for (int m = 0; m < 16; m++) load_vec<float, 4>(g[m], G + (node * 16 + m) * BS_C + c0);
+    }
+    // wait for the edge's slot
+    const uint32_t slot = ring + (ccount % BS_SLOTS) * BS_SLOT_BYTES, bar = bar0 + 8 * (ccount % BS_SLOTS);
+    const uint32_t parity = (ccount / BS_SLOTS) & 1u;
+    {
+      uint32_t ok = 0;
+      const long long t0 = clock64();
+      for (;;) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok || clock64() - t0 > BS_TIMEOUT_CYCLES) break;
+      }
+      if (!__all_sync(0xffffffffu, ok != 0)) {
+        if (lane == 0 && stalled) atomicExch(stalled, 1);
+        break;
+      }
+    }
+    float x[4], r[4][4];
+    {
+      float4 v;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                   : "r"(slot + BS_R_BYTES + lane * 16));
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+#pragma unroll
+      for (int l = 0; l < 4; l++) {
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "r"(slot + l * (BS_C * 4) + lane * 16));
+        r[l][0] = v.x; r[l][1] = v.y; r[l][2] = v.z; r[l][3] = v.w;
+      }
+    }
+    float u[4][4], p[16];
+#pragma unroll
+    for (int l = 0; l < 4; l++)
+#pragma unroll
+      for (int v = 0; v < 4; v++) u[l][v] = 0.f;
+#pragma unroll
+    for (int m = 0; m < 16; m++) {
+      const float y = __shfl_sync(0xffffffffu, yv, m);
+      float pm = 0.f;
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        u[l_of_lm(m)][v] = fmaf(y, g[m][v], u[l_of_lm(m)][v]);
+        pm = fmaf(g[m][v], r[l_of_lm(m)][v] * x[v], pm);
+      }
+      p[m] = pm;
+    }
+    float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+      float gr[4];
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        t[v] = fmaf(u[l][v], r[l][v], t[v]);
+        gr[v] = x[v] * u[l][v];
+      }
+      store_vec_stream<float, 4>(gradR + (e * 4 + l) * BS_C + c0, gr);
+    }
+    // every value read from the slot has been consumed by now: the next copy may go into it
+    __syncwarp();
+    ccount++;
+    issue_one();
+    if (Tout != nullptr) store_vec<float, 4>(Tout + e * BS_C + c0, t);
+    const float tot = warp_reduce16(p, lane);
+    if ((lane & 1) == 0) gy[(int64_t)(lane >> 1) * nedges + e] = tot;
+    cc = nc;
+  }
+}
+
 // gradY[m, e] = sum over chunks of partial[chunk, m, e]
 template <typename T>
 __global__ void sum_partials_kernel(const T *__restrict__ partial, int nchunks, int64_t n,
@@ -292,6 +474,27 @@ static void launch_bwd_edge(const T *X, const T *Y, const T *R, const T *G, cons
                                                                      nnodes, nedges, C, gradR, gy, Tout);
 }
 
+// the staged edge pass can be switched off with CMACE_IMP_STAGED=0 (falls back to the register-prefetch kernel)
+static bool staged_edge_pass_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char *v = getenv("CMACE_IMP_STAGED");
+    on = (v == nullptr || atoi(v) != 0) ? 1 : 0;
+  }
+  return on != 0;
+}
+static __device__ int g_staged_stall;   // set when a bounded wait of the staged edge pass gave up
+static int *staged_stall_flag() {
+  static int *per_device[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (per_device[dev] == nullptr) {
+    int *p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_staged_stall) == cudaSuccess) per_device[dev] = p;
+  }
+  return per_device[dev];
+}
+
 template <typename T>
 static int imp_bwd_edge(const T *X, const T *Y, const T *R, const T *G, const int32_t *sender,
                         const int32_t *row_ptr, int64_t nnodes, int64_t nedges, int C, T *gradR,
@@ -309,6 +512,25 @@ static int imp_bwd_edge(const T *X, const T *Y, const T *R, const T *G, const in
     return fail(CMACE_ERR_ARG, "cmace_imp_bwd_edge: gradY_partial scratch required for %d chunks", nchunks);
   T *gy = nchunks > 1 ? partial : gradY;
   cudaStream_t st = (cudaStream_t)stream;
+  if constexpr (sizeof(T) == 4) {
+    if (C == BS_C && staged_edge_pass_enabled() && aligned16(R) && aligned16(X) && aligned16(G)) {
+      static int num_sms = 0;
+      if (num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (num_sms <= 0) num_sms = 148;
+      }
+      const size_t smem = (size_t)BS_WARPS * BS_SLOTS * BS_SLOT_BYTES;
+      cudaError_t e = cudaFuncSetAttribute(imp_bwd_edge_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "cmace_imp_bwd_edge: %s", cudaGetErrorString(e));
+      int64_t blocks = (nnodes + BS_WARPS - 1) / BS_WARPS;
+      blocks = blocks < num_sms ? blocks : num_sms;
+      imp_bwd_edge_staged_kernel<<<(unsigned)blocks, BS_WARPS * 32, smem, st>>>(
+          X, Y, R, G, sender, row_ptr, nnodes, nedges, gradR, gy, Tout, staged_stall_flag());
+      return check_launch("cmace_imp_bwd_edge");
+    }
+  }
   switch (vec) {
     case 4:
       if constexpr (sizeof(T) == 4)
@@ -389,6 +611,15 @@ static double *static_scratch_address(int *err) {
 using namespace cmace;
 
 extern "C" {
+
+int cmace_imp_staged_stalled(void) {
+  int *flag = staged_stall_flag();
+  int v = 0;
+  if (flag == nullptr) return 0;
+  if (cudaMemcpy(&v, flag, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) cudaMemset(flag, 0, sizeof(int));
+  return v;
+}
 
 int cmace_imp_fwd_f32(const float *X, const float *Y, const float *R, const int32_t *sender,
                       const int32_t *row_ptr, int64_t nnodes, int64_t nedges, int channels, float *out,

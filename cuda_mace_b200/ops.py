@@ -98,6 +98,8 @@ def _status_tensor(device):
 
 def check_status():
     """Raises if any tensor-core kernel reported a timed-out wait since the last check (synchronises)."""
+    if _abi.call("cmace_imp_staged_stalled") != 0:
+        raise RuntimeError("cuda_mace_b200: the message-passing backward gave up waiting for a bulk copy")
     for idx, t in _status.items():
         code = int(t.item())
         if code != 0:

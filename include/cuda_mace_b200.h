@@ -146,6 +146,11 @@ int cmace_imp_fwd_f64(const double *X, const double *Y, const double *R, const i
                       const int32_t *row_ptr, int64_t nnodes, int64_t nedges, int channels,
                       double *out, cmace_stream_t stream);
 int64_t cmace_imp_bwd_scratch_elems(int64_t nedges, int channels, int is_f64);
+/* float32 with 128 channels runs the edge pass with the R rows staged through shared memory by bulk copies
+ * (CMACE_IMP_STAGED=0 in the environment selects the register-prefetch kernel).  Its waits on the copies are
+ * bounded; cmace_imp_staged_stalled() synchronises, returns 1 if one of them gave up since the last call (the
+ * results of that launch are then incomplete) and clears the flag. */
+int cmace_imp_staged_stalled(void);
 int cmace_imp_bwd_edge_f32(const float *X, const float *Y, const float *R, const float *G,
                            const int32_t *sender, const int32_t *row_ptr, int64_t nnodes,
                            int64_t nedges, int channels, float *gradR, float *gradY, float *T,

@@ -138,10 +138,9 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
 
 # DRAM traffic per edge (dram__bytes_read.sum + dram__bytes_write.sum of one launch / edges) from the ncu captures of
 # the 8 000-atom case summarised under profiles/ (E = 417 248 there); the traffic of every edge kernel grows in
-# proportion to E, so a full launch moves this many bytes times its own E.  For imp_bwd_edge the DRAM write
-# counter misses the kernel's streaming stores and the sectors written into L2 stand in for it.
+# proportion to E, so a full launch moves this many bytes times its own E.
 NCU_TRAFFIC_PER_EDGE = {
-    "cmace_imp_bwd_edge_f32": (4864.0, "profiles/imp_kernels_small_case_f32.txt"),
+    "cmace_imp_bwd_edge_f32": (4904.0, "profiles/imp_kernels_small_case_f32.txt"),   # staged kernel: 1002 + 1044 MB
     "cmace_imp_fwd_f32": (2170.0, "profiles/imp_kernels_small_case_f32.txt"),
     "cmace_gemm3x_f32[K=512,N=64]": (2285.0, "profiles/gemm3x_tf32_small_case_f32.txt"),
     "cmace_gemm3x_f32[K=64,N=512]": (2176.0, "profiles/gemm3x_tf32_small_case_f32.txt"),

@@ -23,9 +23,11 @@
 //   warp 8     MMA issuer: one elected thread issues tcgen05.mma kind::tf32 (M=128, N<=128, K=8),
 //              4 K-steps x 3 split terms per stage, and commits to the stage's "empty" barrier and,
 //              after the last K block of a tile, to the accumulator's "full" barrier.
-//   warps 9-16 epilogue: tcgen05.ld of the accumulator (each thread one row, 16 columns at a time), add the
-//              two column ranges, scale, transpose through shared memory, store 64-byte row pieces,
-//              release the accumulator.
+//   warps 9-16 epilogue: tcgen05.ld of the accumulator, add the two column ranges, scale, store, release the
+//              accumulator.  PLAIN: 16x256b loads (a thread holds column pairs of two rows) stored straight
+//              to global memory as 32-byte row pieces per four lanes -- no shared memory.  LINEAR: 32x32b
+//              loads (a thread holds one row, 16 columns at a time), transposed through a per-warp
+//              shared-memory buffer, stored as 64-byte row pieces.
 // Accumulators are double buffered in tensor memory (2 x 256 columns), so the epilogue of tile t
 // overlaps the MMAs of tile t+1, and a 3-stage shared-memory ring overlaps loads with MMAs.
 //
@@ -551,8 +553,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   } else {
     // ================================ epilogue ================================
     // Eight warps: two per tensor-memory lane quarter (a warp may only read lanes 32*(warp%4)..+31), the two
-    // taking alternate 32-column chunks of the tile.  Each chunk goes through a per-warp transpose buffer
-    // in two 16-column halves so that the global stores are 64-byte row pieces, 8 rows per instruction.
+    // taking alternate 32-column chunks of the tile.  In LINEAR mode each chunk goes through a per-warp transpose
+    // buffer in two 16-column halves so that the global stores are 64-byte row pieces, 8 rows per instruction;
+    // in PLAIN mode the buffer does not exist (the launch reserves no bytes for it) and is never touched.
     const int q = warp & 3;                          // tensor-memory lane quarter this warp may read
     const int half = (warp - (GT_PRODUCER_WARPS + 1)) >> 2;  // which alternate chunks this warp takes
     float *ep_buf = reinterpret_cast<float *>(smem + (smem_base - smem_u32(smem)) + GT_STAGES * GT_STAGE_BYTES) +
@@ -578,49 +581,94 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * 256 + ((uint32_t)(q * 32) << 16);
-      // rows each store instruction of this lane covers (8 rows x 64 bytes): row pointers, once per tile
-      float *rowptr[4];
+      if (MODE == GT_MODE_PLAIN) {
+        // Straight from tensor memory to global memory, no shared-memory transpose: the 16x256b load shape hands
+        // thread t two rows (t/4 and t/4 + 8 of a 16-row half) and, per 8-column block, the two columns
+        // 2(t%4), 2(t%4)+1 -- four neighbouring lanes hold 32 contiguous bytes of a row, so an 8-byte store per
+        // lane writes whole 32-byte sectors.  Shared memory is the scarce resource of this kernel (at the TF32
+        // rate the tensor core's own operand reads take most of its 128 bytes per clock): [E,64]x[64,512] went
+        // from 1.98 to 1.79 ms.  With gathered rows (LINEAR) the staged version below measured faster.
+        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
 #pragma unroll
-      for (int it = 0; it < 4; it++) {
-        const int64_t gr = __shfl_sync(0xffffffffu, grow, it * 8 + (lane >> 2));
-        rowptr[it] = gr >= 0 ? g.out + gr * g.N + n0 + (lane & 3) * 4 : nullptr;
-      }
-      for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+          for (int hr = 0; hr < 2; hr++) {
+            uint32_t v[16], w[16];
+            const uint32_t ta = taddr + ((uint32_t)(16 * hr) << 16) + (uint32_t)c0;
+            tmem_ld_16x256b_x4(ta, v);                 // Ahi*Bhi + Alo*Bhi
+            tmem_ld_16x256b_x4(ta + g.npad, w);        // Ahi*Blo
+            tmem_ld_wait();
+            const int64_t gra = __shfl_sync(0xffffffffu, grow, 16 * hr + (lane >> 2));
+            const int64_t grb = __shfl_sync(0xffffffffu, grow, 16 * hr + 8 + (lane >> 2));
+            float *pa = g.out + gra * g.N + n0 + c0 + 2 * (lane & 3);
+            float *pb = g.out + grb * g.N + n0 + c0 + 2 * (lane & 3);
 #pragma unroll
-        for (int h16 = 0; h16 < 32; h16 += 16) {
-          const int cc = c0 + h16;
-          if (cc >= ncols) break;  // warp-uniform
-          uint32_t v[16], w[16];
-          tmem_ld16_nowait(taddr + cc, v);             // Ahi*Bhi + Alo*Bhi
-          tmem_ld16_nowait(taddr + g.npad + cc, w);    // Ahi*Blo
-          tmem_ld_wait();
-          // lane = row: write the row's 16 values, then read back 8 rows x 64 bytes per instruction
-          float *mine = ep_buf + lane * GT_EP_STRIDE;
-#pragma unroll
-          for (int i = 0; i < 16; i += 4)
-            *reinterpret_cast<float4 *>(mine + i) =
-                make_float4((__uint_as_float(v[i]) + __uint_as_float(w[i])) * g.scale,
-                            (__uint_as_float(v[i + 1]) + __uint_as_float(w[i + 1])) * g.scale,
-                            (__uint_as_float(v[i + 2]) + __uint_as_float(w[i + 2])) * g.scale,
-                            (__uint_as_float(v[i + 3]) + __uint_as_float(w[i + 3])) * g.scale);
-          __syncwarp();
-          const bool col_ok = cc + (lane & 3) * 4 < ncols;
-#pragma unroll
-          for (int it = 0; it < 4; it++) {
-            const int rr = it * 8 + (lane >> 2);
-            float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 3) * 4);
-            if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) {
+            for (int j = 0; j < 4; j++) {
+              const bool col_ok = c0 + 8 * j + 2 * (lane & 3) < ncols && !GT_DBG(g, 4);
+              float2 oa = make_float2((__uint_as_float(v[4 * j]) + __uint_as_float(w[4 * j])) * g.scale,
+                                      (__uint_as_float(v[4 * j + 1]) + __uint_as_float(w[4 * j + 1])) * g.scale);
+              float2 ob = make_float2((__uint_as_float(v[4 * j + 2]) + __uint_as_float(w[4 * j + 2])) * g.scale,
+                                      (__uint_as_float(v[4 * j + 3]) + __uint_as_float(w[4 * j + 3])) * g.scale);
               if (ACT && g.ep_z != nullptr) {
-                const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + cc));
-                o.x *= silu_n_grad(z.x);
-                o.y *= silu_n_grad(z.y);
-                o.z *= silu_n_grad(z.z);
-                o.w *= silu_n_grad(z.w);
+                if (gra >= 0 && col_ok) {
+                  const float2 z = __ldg(reinterpret_cast<const float2 *>(g.ep_z + (pa - g.out) + 8 * j));
+                  oa.x *= silu_n_grad(z.x);
+                  oa.y *= silu_n_grad(z.y);
+                }
+                if (grb >= 0 && col_ok) {
+                  const float2 z = __ldg(reinterpret_cast<const float2 *>(g.ep_z + (pb - g.out) + 8 * j));
+                  ob.x *= silu_n_grad(z.x);
+                  ob.y *= silu_n_grad(z.y);
+                }
               }
-              *reinterpret_cast<float4 *>(rowptr[it] + cc) = o;
+              if (gra >= 0 && col_ok) *reinterpret_cast<float2 *>(pa + 8 * j) = oa;
+              if (grb >= 0 && col_ok) *reinterpret_cast<float2 *>(pb + 8 * j) = ob;
             }
           }
-          __syncwarp();
+        }
+      } else {
+        // rows each store instruction of this lane covers (8 rows x 64 bytes): row pointers, once per tile
+        float *rowptr[4];
+  #pragma unroll
+        for (int it = 0; it < 4; it++) {
+          const int64_t gr = __shfl_sync(0xffffffffu, grow, it * 8 + (lane >> 2));
+          rowptr[it] = gr >= 0 ? g.out + gr * g.N + n0 + (lane & 3) * 4 : nullptr;
+        }
+        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+  #pragma unroll
+          for (int h16 = 0; h16 < 32; h16 += 16) {
+            const int cc = c0 + h16;
+            if (cc >= ncols) break;  // warp-uniform
+            uint32_t v[16], w[16];
+            tmem_ld16_nowait(taddr + cc, v);             // Ahi*Bhi + Alo*Bhi
+            tmem_ld16_nowait(taddr + g.npad + cc, w);    // Ahi*Blo
+            tmem_ld_wait();
+            // lane = row: write the row's 16 values, then read back 8 rows x 64 bytes per instruction
+            float *mine = ep_buf + lane * GT_EP_STRIDE;
+  #pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              *reinterpret_cast<float4 *>(mine + i) =
+                  make_float4((__uint_as_float(v[i]) + __uint_as_float(w[i])) * g.scale,
+                              (__uint_as_float(v[i + 1]) + __uint_as_float(w[i + 1])) * g.scale,
+                              (__uint_as_float(v[i + 2]) + __uint_as_float(w[i + 2])) * g.scale,
+                              (__uint_as_float(v[i + 3]) + __uint_as_float(w[i + 3])) * g.scale);
+            __syncwarp();
+            const bool col_ok = cc + (lane & 3) * 4 < ncols;
+  #pragma unroll
+            for (int it = 0; it < 4; it++) {
+              const int rr = it * 8 + (lane >> 2);
+              float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 3) * 4);
+              if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) {
+                if (ACT && g.ep_z != nullptr) {
+                  const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + cc));
+                  o.x *= silu_n_grad(z.x);
+                  o.y *= silu_n_grad(z.y);
+                  o.z *= silu_n_grad(z.z);
+                  o.w *= silu_n_grad(z.w);
+                }
+                *reinterpret_cast<float4 *>(rowptr[it] + cc) = o;
+              }
+            }
+            __syncwarp();
+          }
         }
       }
       tc_fence_before();
@@ -730,10 +778,11 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   const int b_all = g.k_blocks * 2 * g.npad * 128;
   g.b_resident = (g.mode == GT_MODE_PLAIN && b_all <= 64 * 1024 && num_sms >= g.n_tiles) ? b_all : 0;
   g.stage_bytes = 2 * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
-  g.stages = (GT_SMEM_BUDGET - GT_EP_BYTES - 1024 - g.b_resident) / g.stage_bytes;
+  const int ep_bytes = g.mode == GT_MODE_PLAIN ? 0 : GT_EP_BYTES;   // only the LINEAR epilogue stages through shared memory
+  g.stages = (GT_SMEM_BUDGET - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
-  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + GT_EP_BYTES + 1024;
+  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024;
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   if (g.mode == GT_MODE_PLAIN) {

@@ -59,11 +59,16 @@ class InvariantMACE(torch.nn.Module):
                 L.register_buffer(f"W_radial{i}", Wn)
                 L.register_buffer(f"W_radial{i}_T", Wn.t().contiguous())
             L.n_radial = len(P["W_radial"])
-            L.linear = ops.Linear(P["W_lin"].to(**dd), scale=1.0 / float(P["avg_num_neighbors"]))
             if t == 0:
-                L.skip = ops.ElementalLinear((P["W_skip"] / math.sqrt(Z)).to(**dd))
+                # linear followed by skip_tp is one element-dependent map per l: the constant weights are multiplied
+                # once, in float64, instead of running two channel-mixing passes over [N,16,C] every step.  Each of
+                # the two operators divides by sqrt(fan_in); the fused one does so once, hence the factor here.
+                W_lin = P["W_lin"].double() / (float(P["avg_num_neighbors"]) * math.sqrt(P["W_lin"].shape[1]))
+                W_skip = P["W_skip"].double() / math.sqrt(Z)
+                L.linear = ops.ElementalLinear(torch.einsum("lab,zlbc->zlac", W_lin, W_skip).to(**dd))
                 L.register_buffer("W_readout", (P["W_readout"] / math.sqrt(C)).to(**d64))
             else:
+                L.linear = ops.Linear(P["W_lin"].to(**dd), scale=1.0 / float(P["avg_num_neighbors"]))
                 L.register_buffer("W_sc", (P["W_sc"] / math.sqrt(C * Z)).permute(1, 0, 2).contiguous().to(**dd))
                 L.register_buffer("W_readout1", (P["W_readout1"] / math.sqrt(C)).to(**d64))
                 L.register_buffer("W_readout2", (P["W_readout2"] / math.sqrt(P["W_readout2"].shape[0])).to(**d64))
@@ -155,9 +160,7 @@ class InvariantMACE(torch.nn.Module):
                     h = exchange(h)
             up = h @ L.W_up
             m = self._messages(L, up, Y, bessel, lengths, send, recv, n_owned, topology)
-            m = L.linear(m)
-            if t == 0:
-                m = L.skip(m, species_owned)
+            m = L.linear(m, species_owned) if t == 0 else L.linear(m)
             b = L.contraction(m, species_owned)[:, 0, :]
             h = b @ L.W_prod
             if sc is not None:

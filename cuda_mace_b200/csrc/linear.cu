@@ -4,8 +4,9 @@
 // (node, m) of one (element, l) pair form a dense GEMM problem of (#nodes of the element)*(2l+1)
 // rows, and every CTA takes one TILE_M x TILE_N output tile of one such problem.  Tiles are
 // located on the device from the element group bounds, so there is no host synchronisation and
-// no per-element launch.  This file holds the shared-memory tiled FMA kernel used for float64 and
-// as the float32 fallback; rows are gathered, so no intermediate re-layout of X is needed.
+// no per-element launch.  This file holds the float64 tensor-core (DMMA) kernel and the shared-memory tiled
+// FMA kernel that serves odd sizes and float32 callers that do not use the tcgen05 path; rows are gathered,
+// so no intermediate re-layout of X is needed.
 #include "common.cuh"
 
 namespace cmace {
@@ -101,6 +102,158 @@ __global__ void __launch_bounds__(LIN_THREADS)
   }
 }
 
+// ---- float64 on the tensor cores (DMMA) -----------------------------------------------------------
+// Same tile bookkeeping, 128 x 128 output tile per CTA, 16 warps of 32 x 32 (4 x 4 mma.sync m8n8k4 f64 tiles,
+// 32 accumulator doubles per thread).  A rows (gathered) and W rows arrive through a 3-stage cp.async ring of
+// 16-wide K slices; the row strides (20 and 132 doubles) make the fragment loads of both operands conflict-free:
+// a fragment load touches 8 rows x 4 consecutive doubles (A) or 4 rows x 8 columns (B), and 2 * stride mod 32 = 8
+// spreads the rows of each half-warp over all 32 banks.  Fragment layout of mma.m8n8k4.f64: A[lane/4][lane%4],
+// B[lane%4][lane/4], C[lane/4][2*(lane%4) + {0,1}].
+// The operator is bound by the FP64 tensor rate at K = Nout = 128 (16 flop/B against a machine balance of ~6).
+constexpr int DM_TILE = 128, DM_K = 16, DM_THREADS = 512, DM_STAGES = 3;
+constexpr int DM_AS = DM_K + 4, DM_BS = DM_TILE + 4;          // row strides in doubles
+constexpr int DM_STAGE_DOUBLES = DM_TILE * DM_AS + DM_K * DM_BS;
+constexpr int DM_SMEM_BYTES = DM_STAGES * DM_STAGE_DOUBLES * 8;
+
+__device__ __forceinline__ void cp_async_16_zfill(void *dst, const void *src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+
+__global__ void __launch_bounds__(DM_THREADS, 1)
+    linear_dmma_kernel(const double *__restrict__ X, const double *__restrict__ W,
+                       const int32_t *__restrict__ node_order, const int32_t *__restrict__ elem_start,
+                       int nelements, int64_t nnodes, int K, int Nout, double scale, double *__restrict__ out) {
+  extern __shared__ __align__(16) double dm_smem[];
+  __shared__ int64_t row_of[DM_TILE];
+
+  const int l = blockIdx.y;
+  const int nl = 2 * l + 1;
+  const int n0 = blockIdx.z * DM_TILE;
+
+  int z = 0;
+  int64_t tile = blockIdx.x, seg_begin = 0, seg_count = 0;
+  for (; z < nelements; z++) {
+    seg_begin = elem_start ? elem_start[z] : 0;
+    seg_count = elem_start ? (int64_t)elem_start[z + 1] - seg_begin : nnodes;
+    const int64_t tiles = (seg_count * nl + DM_TILE - 1) / DM_TILE;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (z >= nelements) return;
+
+  const int tid = threadIdx.x;
+  if (tid < DM_TILE) {
+    const int64_t rl = tile * DM_TILE + tid;
+    int64_t grow = -1;
+    if (rl < seg_count * nl) {
+      const int64_t slot = seg_begin + rl / nl;
+      const int64_t node = node_order ? (int64_t)node_order[slot] : slot;
+      grow = node * 16 + l * l + (rl % nl);
+    }
+    row_of[tid] = grow;
+  }
+  __syncthreads();
+
+  const double *Wz = W + ((int64_t)(z * 4 + l) * K) * Nout;
+  // copy assignments: 1024 16-byte chunks per operand and K slice, two per thread
+  int64_t a_src[2];
+  int a_dst[2], a_k[2], b_dst[2], b_k[2], b_c[2];
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const int c = tid + DM_THREADS * i;
+    const int ar = c >> 3, ach = c & 7;              // A: 128 rows x 8 chunks
+    a_src[i] = row_of[ar] >= 0 ? row_of[ar] * K + ach * 2 : -1;
+    a_k[i] = ach * 2;
+    a_dst[i] = ar * DM_AS + ach * 2;
+    const int bk = c >> 6, bch = c & 63;             // B: 16 K rows x 64 chunks
+    b_k[i] = bk;
+    b_c[i] = n0 + bch * 2;
+    b_dst[i] = DM_TILE * DM_AS + bk * DM_BS + bch * 2;
+  }
+  auto load_slice = [&](int kt) {
+    double *st = dm_smem + (kt % DM_STAGES) * DM_STAGE_DOUBLES;
+    const int k0 = kt * DM_K;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const bool av = a_src[i] >= 0 && k0 + a_k[i] < K;
+      cp_async_16_zfill(st + a_dst[i], av ? X + a_src[i] + k0 : X, av);
+      const bool bv = k0 + b_k[i] < K && b_c[i] < Nout;
+      cp_async_16_zfill(st + b_dst[i], bv ? Wz + (int64_t)(k0 + b_k[i]) * Nout + b_c[i] : W, bv);
+    }
+  };
+
+  const int warp = tid >> 5, lane = tid & 31;
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;
+  const int fr = lane >> 2, fk = lane & 3;
+  double acc[4][4][2];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+  const int nk = (K + DM_K - 1) / DM_K;
+#pragma unroll
+  for (int s = 0; s < DM_STAGES - 1; s++) {
+    if (s < nk) load_slice(s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int kt = 0; kt < nk; kt++) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(DM_STAGES - 2) : "memory");
+    __syncthreads();   // slice kt has landed for every thread, and everybody is done with slice kt - 1
+    if (kt + DM_STAGES - 1 < nk) load_slice(kt + DM_STAGES - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const double *As = dm_smem + (kt % DM_STAGES) * DM_STAGE_DOUBLES;
+    const double *Bs = As + DM_TILE * DM_AS;
+#pragma unroll
+    for (int kk = 0; kk < DM_K; kk += 4) {
+      double a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = As[(wm + i * 8 + fr) * DM_AS + kk + fk];
+#pragma unroll
+      for (int j = 0; j < 4; j++) b[j] = Bs[(kk + fk) * DM_BS + wn + j * 8 + fr];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+                       : "+d"(acc[i][j][0]), "+d"(acc[i][j][1])
+                       : "d"(a[i]), "d"(b[j]));
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int64_t grow = row_of[wm + i * 8 + fr];
+    if (grow < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int c = n0 + wn + j * 8 + 2 * fk;
+      if (c < Nout)   // Nout is even: both columns or none
+        *reinterpret_cast<double2 *>(out + grow * Nout + c) = make_double2(acc[i][j][0] * scale, acc[i][j][1] * scale);
+    }
+  }
+}
+
+static int linear_dmma(const double *X, const double *W, const int32_t *node_order, const int32_t *elem_start,
+                       int nelements, int64_t nnodes, int K, int Nout, double scale, double *out,
+                       cmace_stream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(linear_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM_BYTES) != cudaSuccess)
+      return fail(CMACE_ERR_CUDA, "cmace_linear_f64: cannot reserve shared memory");
+    attr_set = true;
+  }
+  const int64_t max_tiles = (nnodes * 7 + DM_TILE - 1) / DM_TILE + nelements;
+  if (max_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear: too many rows");
+  dim3 grid((unsigned)max_tiles, 4, (unsigned)((Nout + DM_TILE - 1) / DM_TILE));
+  linear_dmma_kernel<<<grid, DM_THREADS, DM_SMEM_BYTES, (cudaStream_t)stream>>>(
+      X, W, node_order, elem_start, nelements, nnodes, K, Nout, scale, out);
+  return check_launch("cmace_linear_f64");
+}
+
 template <typename T>
 static int linear(const T *X, const T *W, const int32_t *node_order, const int32_t *elem_start,
                   int nelements, int64_t nnodes, int K, int Nout, double scale, T *out,
@@ -110,6 +263,11 @@ static int linear(const T *X, const T *W, const int32_t *node_order, const int32
   if (!X || !W || !out) return fail(CMACE_ERR_ARG, "cmace_linear: null pointer");
   if ((nelements > 1) != (node_order != nullptr) || (node_order != nullptr) != (elem_start != nullptr))
     return fail(CMACE_ERR_ARG, "cmace_linear: node_order and elem_start go together with nelements > 1");
+  if constexpr (sizeof(T) == 8) {
+    // tensor-core path whenever its 16-byte copies are aligned: even K and Nout, 16-byte aligned bases
+    if (K % 2 == 0 && Nout % 2 == 0 && aligned16(X) && aligned16(W) && aligned16(out))
+      return linear_dmma(X, W, node_order, elem_start, nelements, nnodes, K, Nout, scale, out, stream);
+  }
   const int64_t max_tiles = (nnodes * 7 + TILE_M - 1) / TILE_M + nelements;
   if (max_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear: too many rows");
   dim3 grid((unsigned)max_tiles, 4, (unsigned)((Nout + TILE_N - 1) / TILE_N));

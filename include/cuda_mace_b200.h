@@ -190,7 +190,8 @@ int cmace_imp_bwd_node_f64(const double *T, const int32_t *perm, const int32_t *
  * cmace_group_by_element.  The backward of both is the same call with the transposed weights,
  * as in the reference (src/linear.cpp:29-44, :77-93), and with the FORWARD's scale (the
  * reference re-derives it from the transposed shape, which is only right for K = Nout).
- * One launch, no host synchronisation. */
+ * One launch, no host synchronisation.  The float64 entry point runs on the FP64 tensor cores (mma.sync
+ * m8n8k4.f64) when K and Nout are even and the pointers 16-byte aligned, otherwise on an FMA tile kernel. */
 int cmace_linear_f32(const float *X, const float *W, const int32_t *node_order,
                      const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
                      double scale, float *out, cmace_stream_t stream);

@@ -95,7 +95,9 @@ def test_topology(dev):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("N,K,Nout", [(130, 128, 128), (9, 64, 64), (40, 96, 32), (1, 32, 96)])
+# (77, 40, 136): K not a multiple of the K slice, two column tiles; (33, 15, 9): odd sizes take the FMA kernel in float64
+@pytest.mark.parametrize("N,K,Nout", [(130, 128, 128), (9, 64, 64), (40, 96, 32), (1, 32, 96), (77, 40, 136),
+                                      (33, 15, 9), (700, 128, 128)])
 def test_linear(dtype, N, K, Nout, dev):
     from cuda_mace_b200 import ops
     from oracle import ops as oops

@@ -48,6 +48,10 @@ def parse():
     ap.add_argument("--cpu-sample-atoms", type=int, default=400)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--radial", default="exact", choices=["exact", "spline"],
+                    help="exact: Bessel basis + multilayer perceptron per edge (the headline); spline: the reference's "
+                         "tabulated radial weights (cubic spline, --spline-knots knots), a secondary figure")
+    ap.add_argument("--spline-knots", type=int, default=256)
     ap.add_argument("--graph", action="store_true",
                     help="1 GPU: replay the step as a CUDA graph in the device-resident leg (no per-kernel timings, "
                          "no roofline object); useful for small systems, which are launch-bound")
@@ -131,6 +135,9 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
         "cmace_radial_hidden_fwd": 4 * E * (8 + 64 + 3 * 64),
         "cmace_radial_hidden_bwd": 4 * E * (64 + 3 * 64 + 8),
         "cmace_imp_radial_fused_fwd": 4 * (E * 64 + 16 * E + Ns * C + 16 * N * C + 4 * E * C) + 8 * E,
+        # tabulated radial weights (secondary configuration): r in, R [E,4C] out / gradR in, grad r out; table in L2
+        "cmace_spline_fwd": s * (E + 4 * E * C),
+        "cmace_spline_bwd": s * (2 * E + 4 * E * C),
         "cmace_edge_basis_fwd": s * E * (3 + 16 + 8),
         "cmace_edge_basis_bwd": s * E * (3 + 16 + 8 + 3),
     }.get(base)
@@ -235,7 +242,9 @@ def main():
         sysd = systems.make_system("slab", n_atoms=n_total, seed=4)
     dom = domain.partition_slabs(sysd["positions"], sysd["species"], sysd["box"], world, R_MAX, rank)
     params = systems.init_params(128, sysd["n_species"], 1)
-    net = model.InvariantMACE(params, cg.u_matrices(), dtype=dtype, device=dev)
+    if args.radial == "spline":
+        model.add_spline_knots(params, args.spline_knots)
+    net = model.InvariantMACE(params, cg.u_matrices(), dtype=dtype, device=dev, radial=args.radial)
     ev = evaluator.EnergyForceEvaluator(net, dom, dev)
     pos = ev.load_domain()
     E, N, Ns = dom.edge_index.shape[1], dom.n_owned, dom.n_local
@@ -341,6 +350,8 @@ def main():
         "gpu_launches": launches,
         "clocks": clocks,
     }
+    if args.radial == "spline":
+        line["config"]["radial"] = f"cubic spline table, {args.spline_knots} knots (not the headline configuration)"
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"], _ = cpu_reference_run(args, 2, 1)
     sys.stdout.flush()

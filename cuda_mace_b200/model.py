@@ -28,6 +28,17 @@ def _silu_n(x):
     return torch.nn.functional.silu(x) * SILU_2MOM
 
 
+def add_spline_knots(params, nknots=256):
+    """Adds the knot grid of the tabulated radial path to every layer's parameters: nknots equidistant knots on
+    [1e-12, r_max + 1] (cuda_mace/models/InvariantMACE.py:226-240).  The table itself is computed by the model."""
+    r_max = float(params["r_max"])
+    r = torch.linspace(1e-12, r_max + 1.0, nknots, dtype=torch.float64)
+    for P in params["layers"]:
+        P["spline_knots"] = r
+        P["spline_h"] = float(r[1] - r[0])
+    return params
+
+
 class InvariantMACE(torch.nn.Module):
     def __init__(self, params, U, dtype=torch.float32, device="cuda", radial="exact"):
         super().__init__()

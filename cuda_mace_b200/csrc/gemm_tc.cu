@@ -91,6 +91,7 @@ struct GemmArgs {
   int64_t total_tiles;          // upper bound of the tile index space
   int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
   int b_resident;               // PLAIN: bytes of this CTA's B images kept in shared memory for the whole kernel, or 0
+  int a_lo_tmem;                // PLAIN: 1 when the residual image of A lives in tensor memory (kernel variant TS)
   int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
   int a_act;                    // 1: apply SiLU to A while loading it
   const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
@@ -171,7 +172,11 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 
 // ACT: the activation switches (a_act, ep_z) are compiled in only for the variant that uses them, the plain
 // variant measured 14 % faster without the extra code in its producer and epilogue loops
-template <bool ACT, int MODE>
+// TS: the residual image lo = tf32(a - trunc(a)) of A goes to tensor memory instead of shared memory and the
+// Alo*Bhi product reads its A operand from there.  Shared-memory bandwidth is what the roles of this kernel compete
+// for; this takes the image's 16 KB store and its 16 KB read by the tensor core out of every pipeline item.  Needs
+// room in tensor memory next to the accumulators: two accumulators of 2 npad columns + 32 columns per ring slot.
+template <bool ACT, int MODE, bool TS = false>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -216,8 +221,65 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 
   const int k_blocks = g.k_blocks;
   const uint32_t b_image = (uint32_t)g.npad * 128u;  // bytes of one B image
+  const uint32_t b_off = TS ? GT_A_SLAB : 2 * GT_A_SLAB;          // the stage's B block follows its A image(s)
+  const uint32_t acc_stride = TS ? 2u * (uint32_t)g.npad : 256u;  // tensor-memory columns between the accumulators
+  const uint32_t lo_ring = tmem_base + 4u * (uint32_t)g.npad;     // TS: slot s holds its 32 columns at + 32 s
 
-  if (MODE == GT_MODE_PLAIN && warp < GT_PRODUCER_WARPS) {
+  if (MODE == GT_MODE_PLAIN && TS && warp < GT_PRODUCER_WARPS) {
+    // ================================ converters, residual image to tensor memory ================================
+    // A thread owns one row of the tile (the tensor-memory lane its warp may access) and 16 of the K block's 32
+    // columns: four 16-byte shared-memory loads (conflict-free: the 128-byte swizzle puts the same logical chunk of
+    // eight consecutive rows into eight different bank groups), three ALU operations per float, one tcgen05.st.
+    const int q = warp & 3, hf = warp >> 2;
+    const int r = q * 32 + lane;
+    uint32_t soff[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) soff[c] = (uint32_t)sw128_offset(r, 4 * hf + c);
+    const uint32_t t_lo = lo_ring + ((uint32_t)(q * 32) << 16) + 16u * (uint32_t)hf;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
+      if (!locate_tile<MODE>(g, t).valid) continue;
+      for (int kb = 0; kb < k_blocks; kb++) {
+        uint32_t got = 1;
+        const long long tw = GT_NOW();
+        if (lane == 0) got = mbar_wait(tma_full + 8 * stage, phase) ? 1u : 0u;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (warp == 0) GT_PROF(g, 1, tw);
+        const long long tc = GT_NOW();
+        if (!got) {
+          report(g, 1);
+          ok = false;
+          break;
+        }
+        const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+        uint32_t lo[16];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          float4 a;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
+                       : "r"(sA + soff[c])
+                       : "memory");
+          lo[4 * c] = __float_as_uint(to_tf32(a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u)));
+          lo[4 * c + 1] = __float_as_uint(to_tf32(a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u)));
+          lo[4 * c + 2] = __float_as_uint(to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u)));
+          lo[4 * c + 3] = __float_as_uint(to_tf32(a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u)));
+        }
+        tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+        if (warp == 0) GT_PROF(g, 2, tc);
+        if (++stage == GT_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (MODE == GT_MODE_PLAIN && warp < GT_PRODUCER_WARPS) {
     // ================================ converters ================================
     // The loader's TMA puts the raw float32 tile straight into the stage's "hi" image: kind::tf32 reads
     // the top 19 bits of each float32 and ignores the low 13 mantissa bits (checked on the hardware), so
@@ -441,7 +503,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           mbar_arrive_expect_tx(tma_full + 8 * stage, g.b_resident ? (uint32_t)GT_A_SLAB : GT_A_SLAB + 2 * b_image);
           tma_load_2d(sA, &tmap, kb * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
           if (!g.b_resident)
-            bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
+            bulk_copy_g2s(sA + b_off, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
                           tma_full + 8 * stage);
           if (++stage == GT_STAGES) {
             stage = 0;
@@ -486,7 +548,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       }
       GT_PROF(g, 3, ta);
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * 256;
+      const uint32_t d_tmem = tmem_base + acc * acc_stride;
       for (int kb = 0; kb < k_blocks; kb++) {
         const long long tf = GT_NOW();
         if (!GT_DBG(g, 1024) && !mbar_wait(full_bar + 8 * stage, phase)) {
@@ -502,7 +564,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
           const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
           const uint64_t b_hi0 =
-              umma_desc_sw128(g.b_resident ? smem_first + (uint32_t)kb * 2u * b_image : sA + 2 * GT_A_SLAB);
+              umma_desc_sw128(g.b_resident ? smem_first + (uint32_t)kb * 2u * b_image : sA + b_off);
           int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
           ksteps = ksteps > 4 ? 4 : ksteps;
           if (GT_DBG(g, 2)) ksteps = 0;
@@ -516,18 +578,22 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             al[j] = a_lo0 + (uint64_t)(2 * j);
             bh[j] = b_hi0 + (uint64_t)(2 * j);
           }
+          const uint32_t a_lo_t = lo_ring + 32u * (uint32_t)stage;   // TS: K step j at + 8 j columns
           if (ksteps == 4) {
             umma_tf32(d_tmem, ah[0], bh[0], idesc2, kb != 0);
-            umma_tf32_acc(d_tmem, al[0], bh[0], idesc1);
+            if (TS) umma_tf32_ts_acc(d_tmem, a_lo_t, bh[0], idesc1);
+            else umma_tf32_acc(d_tmem, al[0], bh[0], idesc1);
 #pragma unroll
             for (int j = 1; j < 4; j++) {
               umma_tf32_acc(d_tmem, ah[j], bh[j], idesc2);
-              umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
+              if (TS) umma_tf32_ts_acc(d_tmem, a_lo_t + 8u * j, bh[j], idesc1);
+              else umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
             }
           } else {
             for (int j = 0; j < ksteps; j++) {
               umma_tf32(d_tmem, ah[j], bh[j], idesc2, (kb | j) != 0);
-              umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
+              if (TS) umma_tf32_ts_acc(d_tmem, a_lo_t + 8u * j, bh[j], idesc1);
+              else umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
             }
           }
           GT_PROF(g, 8, tm0);
@@ -580,14 +646,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * 256 + ((uint32_t)(q * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * acc_stride + ((uint32_t)(q * 32) << 16);
       if (MODE == GT_MODE_PLAIN) {
         // Straight from tensor memory to global memory, no shared-memory transpose: the 16x256b load shape hands
         // thread t two rows (t/4 and t/4 + 8 of a 16-row half) and, per 8-column block, the two columns
         // 2(t%4), 2(t%4)+1 -- four neighbouring lanes hold 32 contiguous bytes of a row, so an 8-byte store per
         // lane writes whole 32-byte sectors.  Shared memory is the scarce resource of this kernel (at the TF32
         // rate the tensor core's own operand reads take most of its 128 bytes per clock): [E,64]x[64,512] went
-        // from 1.98 to 1.79 ms.  With gathered rows (LINEAR) the staged version below measured faster.
+        // from 1.98 to 1.79 ms.  With gathered rows (LINEAR) it measured the same as the staged version below.
         for (int c0 = half * 32; c0 < ncols; c0 += 64) {
 #pragma unroll
           for (int hr = 0; hr < 2; hr++) {
@@ -777,10 +843,16 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   // streams A, instead of fetching the same B block from L2 again for every 128-row tile
   const int b_all = g.k_blocks * 2 * g.npad * 128;
   g.b_resident = (g.mode == GT_MODE_PLAIN && b_all <= 64 * 1024 && num_sms >= g.n_tiles) ? b_all : 0;
-  g.stage_bytes = 2 * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
+  const bool act = g.a_act != 0 || g.ep_z != nullptr;
+  // residual image of A in tensor memory when at least four ring slots fit next to the two accumulators
+  static const bool ts_off = getenv("CMACE_GEMM_TS") && atoi(getenv("CMACE_GEMM_TS")) == 0;
+  const int ts_slots = (GT_TMEM_COLS - 4 * g.npad) / 32;
+  g.a_lo_tmem = (g.mode == GT_MODE_PLAIN && !act && ts_slots >= 4 && !ts_off) ? 1 : 0;
+  g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   const int ep_bytes = g.mode == GT_MODE_PLAIN ? 0 : GT_EP_BYTES;   // only the LINEAR epilogue stages through shared memory
   g.stages = (GT_SMEM_BUDGET - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
+  if (g.a_lo_tmem && g.stages > ts_slots) g.stages = ts_slots;
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
   const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024;
   CUtensorMap tmap;
@@ -788,9 +860,10 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (g.mode == GT_MODE_PLAIN) {
     if (int rc = encode_rows_tensor_map(&tmap, g.A, g.M, g.K, what)) return rc;
   }
-  const bool act = g.a_act != 0 || g.ep_z != nullptr;
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
-                                       : (act ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN> : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>);
+              : act                    ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN>
+              : g.a_lo_tmem            ? gemm3x_tf32_kernel<false, GT_MODE_PLAIN, true>
+                                       : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   if (g.total_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many tiles", what);

@@ -6,8 +6,8 @@
 // (the 1/sqrt(fan_in) factors and the normalisation constant of the activation are folded into the weights by
 // the caller).  The activations never leave the SM: a layer's accumulator is read from tensor memory, activated,
 // split into the hi / lo TF32 images and written to shared memory as the next layer's A operand.  Every product
-// uses the 3-term split  Ahi*Bhi + Ahi*Blo + Alo*Bhi  with the float32 accumulator in tensor memory, two
-// tcgen05.mma per K step (the hi and lo images of a weight matrix are read as one operand of twice the rows).
+// uses the 3-term split  Ahi*Bhi + Ahi*Blo + Alo*Bhi  with the float32 accumulator in tensor memory, three
+// tcgen05.mma per K step into the same columns (one tensor-memory load per value in the elementwise phase).
 // The forward stores the activation derivatives d_k = silu'(z_k) (three [E, 64] arrays in a tiled layout that
 // both kernels access with coalesced 16-byte transfers); the backward is then three products with an
 // elementwise factor between them and needs no special-function work.
@@ -32,7 +32,7 @@ constexpr int RH_A_SLAB = RH_TILE * 128;    // one image (hi or lo) of one 32-co
 constexpr int RH_A_GROUP = 4 * RH_A_SLAB;   // two K blocks x (hi, lo)
 constexpr int RH_W_SMALL = 2 * 64 * 128;    // packed [nb <= 32, 64]: one K block, hi + lo images of 64 rows
 constexpr int RH_W_BIG = 2 * RH_W_SMALL;    // packed [64, 64]: two K blocks
-constexpr int RH_TMEM_COLS = 256;           // two groups x (64 + 64) accumulator columns
+constexpr int RH_TMEM_COLS = 128;           // two groups x 64 accumulator columns
 
 struct RadialArgs {
   const float *in;        // forward: basis [E, nb]; backward: grad h3 [E, 64]
@@ -58,22 +58,23 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 }
 
 // One layer's products for a 128-row tile: A images at sA (per K block: hi slab, lo slab), packed weights at sB
-// (per K block: hi image then lo image of npad rows).  Columns [0, npad) of the accumulator receive
-// Ahi*Bhi + Alo*Bhi, columns [npad, 2 npad) receive Ahi*Blo.
+// (per K block: hi image then lo image of npad rows).  The three terms Ahi*Bhi + Ahi*Blo + Alo*Bhi accumulate into
+// the same npad columns, so the elementwise phase reads each value once and needs no addition.
 __device__ __forceinline__ void issue_layer(uint32_t d_tmem, uint32_t sA, uint32_t sB, int K, int npad) {
-  const uint32_t idesc2 = umma_idesc_tf32(RH_TILE, 2 * npad);
-  const uint32_t idesc1 = umma_idesc_tf32(RH_TILE, npad);
-  const uint32_t b_block = 2u * (uint32_t)npad * 128u;
+  const uint32_t idesc = umma_idesc_tf32(RH_TILE, npad);
+  const uint32_t b_image = (uint32_t)npad * 128u, b_block = 2u * b_image;
   for (int k0 = 0, kb = 0; k0 < K; k0 += 32, kb++) {
     const uint64_t a_hi = umma_desc_sw128(sA + kb * 2 * RH_A_SLAB);
     const uint64_t a_lo = umma_desc_sw128(sA + kb * 2 * RH_A_SLAB + RH_A_SLAB);
     const uint64_t b_hi = umma_desc_sw128(sB + kb * b_block);
+    const uint64_t b_lo = umma_desc_sw128(sB + kb * b_block + b_image);
     int ksteps = (K - k0) / 8;
     ksteps = ksteps > 4 ? 4 : ksteps;
     for (int j = 0; j < ksteps; j++) {
       // K step j starts 32 bytes = 2 address units further into every row
-      umma_tf32(d_tmem, a_hi + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc2, (kb | j) != 0);
-      umma_tf32_acc(d_tmem, a_lo + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc1);
+      umma_tf32(d_tmem, a_hi + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc, (kb | j) != 0);
+      umma_tf32_acc(d_tmem, a_hi + (uint64_t)(2 * j), b_lo + (uint64_t)(2 * j), idesc);
+      umma_tf32_acc(d_tmem, a_lo + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc);
     }
   }
 }
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = tmem_base_slot + group * 128;
+  const uint32_t tmem_acc = tmem_base_slot + group * RH_H;
 
   if (tid == 0) {
     mbar_arrive_expect_tx(wbar, w_bytes[0] + w_bytes[1] + w_bytes[2]);
@@ -200,26 +201,21 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
       load_basis(tile + tile_step);
       if (!(ok = finish_layer())) break;
       for (int layer = 0; layer < 3; layer++) {
+uint32_t v[32];
+        tmem_ld32_nowait(t_row + 32 * h, v);
+        tmem_ld_wait();
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-          uint32_t v[16], w[16];
-          tmem_ld16_nowait(t_row + 32 * h + 16 * half, v);
-          tmem_ld16_nowait(t_row + RH_H + 32 * h + 16 * half, w);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            float4 a, d;
-            silu_both(__uint_as_float(v[4 * i]) + __uint_as_float(w[4 * i]), a.x, d.x);
-            silu_both(__uint_as_float(v[4 * i + 1]) + __uint_as_float(w[4 * i + 1]), a.y, d.y);
-            silu_both(__uint_as_float(v[4 * i + 2]) + __uint_as_float(w[4 * i + 2]), a.z, d.z);
-            silu_both(__uint_as_float(v[4 * i + 3]) + __uint_as_float(w[4 * i + 3]), a.w, d.w);
-            const int c = half * 4 + i;
-            if (layer < 2)
-              store_split(a_row + (uint32_t)sw128_offset(r, c), a);
-            else if (row_ok)
-              *reinterpret_cast<float4 *>(g.out + e * RH_H + 32 * h + 4 * c) = a;
-            if (g.dsave != nullptr) dtile[(layer * 16 + c) * RH_TILE] = d;
-          }
+        for (int c = 0; c < 8; c++) {
+          float4 a, d;
+          silu_both(__uint_as_float(v[4 * c]), a.x, d.x);
+          silu_both(__uint_as_float(v[4 * c + 1]), a.y, d.y);
+          silu_both(__uint_as_float(v[4 * c + 2]), a.z, d.z);
+          silu_both(__uint_as_float(v[4 * c + 3]), a.w, d.w);
+          if (layer < 2)
+            store_split(a_row + (uint32_t)sw128_offset(r, c), a);
+          else if (row_ok)
+            *reinterpret_cast<float4 *>(g.out + e * RH_H + 32 * h + 4 * c) = a;
+          if (g.dsave != nullptr) dtile[(layer * 16 + c) * RH_TILE] = d;
         }
         if (layer < 2) {
           start_layer(sW[layer + 1], RH_H, RH_H);
@@ -269,23 +265,15 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
       for (int c = 0; c < 8; c++) pd[c] = dtile[(16 + c) * RH_TILE];        // d2
       if (!(ok = finish_layer())) break;
       for (int layer = 1; layer >= 0; layer--) {
+uint32_t v[32];
+        tmem_ld32_nowait(t_row + 32 * h, v);
+        tmem_ld_wait();
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-          uint32_t v[16], w[16];
-          tmem_ld16_nowait(t_row + 32 * h + 16 * half, v);
-          tmem_ld16_nowait(t_row + RH_H + 32 * h + 16 * half, w);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const int c = half * 4 + i;
-            const float4 d = pd[c];
-            float4 a;
-            a.x = (__uint_as_float(v[4 * i]) + __uint_as_float(w[4 * i])) * d.x;
-            a.y = (__uint_as_float(v[4 * i + 1]) + __uint_as_float(w[4 * i + 1])) * d.y;
-            a.z = (__uint_as_float(v[4 * i + 2]) + __uint_as_float(w[4 * i + 2])) * d.z;
-            a.w = (__uint_as_float(v[4 * i + 3]) + __uint_as_float(w[4 * i + 3])) * d.w;
-            store_split(a_row + (uint32_t)sw128_offset(r, c), a);
-          }
+        for (int c = 0; c < 8; c++) {
+          const float4 d = pd[c];
+          store_split(a_row + (uint32_t)sw128_offset(r, c),
+                      make_float4(__uint_as_float(v[4 * c]) * d.x, __uint_as_float(v[4 * c + 1]) * d.y,
+                                  __uint_as_float(v[4 * c + 2]) * d.z, __uint_as_float(v[4 * c + 3]) * d.w));
         }
         start_layer(sW[2 - layer], RH_H, layer == 0 ? g.npad_last : RH_H);
         if (layer == 1) {
@@ -297,20 +285,17 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
         if (!(ok = finish_layer())) break;
       }
       if (!ok) break;
-      // ---- grad basis: columns [0, nb) + [npad, npad + nb) of the accumulator
+      // ---- grad basis: columns [0, nb) of the accumulator
       if (h == 0) {
         for (int c0 = 0; c0 < g.nb; c0 += 8) {
-          uint32_t v[8], w[8];
+          uint32_t v[8];
           tmem_ld8(t_row + c0, v);
-          tmem_ld8(t_row + g.npad_last + c0, w);
           if (row_ok) {
             float *o = g.out + e * g.nb + c0;
-            *reinterpret_cast<float4 *>(o) =
-                make_float4(__uint_as_float(v[0]) + __uint_as_float(w[0]), __uint_as_float(v[1]) + __uint_as_float(w[1]),
-                            __uint_as_float(v[2]) + __uint_as_float(w[2]), __uint_as_float(v[3]) + __uint_as_float(w[3]));
-            *reinterpret_cast<float4 *>(o + 4) =
-                make_float4(__uint_as_float(v[4]) + __uint_as_float(w[4]), __uint_as_float(v[5]) + __uint_as_float(w[5]),
-                            __uint_as_float(v[6]) + __uint_as_float(w[6]), __uint_as_float(v[7]) + __uint_as_float(w[7]));
+            *reinterpret_cast<float4 *>(o) = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]),
+                                                         __uint_as_float(v[2]), __uint_as_float(v[3]));
+            *reinterpret_cast<float4 *>(o + 4) = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]),
+                                                             __uint_as_float(v[6]), __uint_as_float(v[7]));
           }
         }
       }

@@ -29,6 +29,10 @@ SIGNATURES = {
     "cmace_edge_basis_fwd_f64": [_P, _L, _D, _I, _I, _P, _P, _P],
     "cmace_edge_basis_bwd_f32": [_P, _P, _P, _L, _D, _I, _I, _P, _P],
     "cmace_edge_basis_bwd_f64": [_P, _P, _P, _L, _D, _I, _I, _P, _P],
+    "cmace_edge_vectors_fwd_f32": [_P, _P, _P, _P, _L, _P, _P],
+    "cmace_edge_vectors_fwd_f64": [_P, _P, _P, _P, _L, _P, _P],
+    "cmace_edge_vectors_bwd_f32": [_P, _P, _P, _P, _L, _L, _P, _P],
+    "cmace_edge_vectors_bwd_f64": [_P, _P, _P, _P, _L, _L, _P, _P],
     "cmace_spline_fwd_f32": [_P, _P, _P, _L, _I, _I, _D, _D, _P, _P],
     "cmace_spline_fwd_f64": [_P, _P, _P, _L, _I, _I, _D, _D, _P, _P],
     "cmace_spline_bwd_f32": [_P, _P, _P, _P, _L, _I, _I, _D, _D, _P, _P],
@@ -94,6 +98,7 @@ _lib = None
 KERNEL_LAUNCHES = {
     "cmace_receiver_csr": 1, "cmace_sender_order": 3, "cmace_group_by_element": 3,
     "cmace_sph_fwd": 1, "cmace_sph_bwd": 1, "cmace_edge_basis_fwd": 1, "cmace_edge_basis_bwd": 1,
+    "cmace_edge_vectors_fwd": 1, "cmace_edge_vectors_bwd": 1,
     "cmace_spline_fwd": 1, "cmace_spline_bwd": 1, "cmace_imp_fwd": 1, "cmace_imp_bwd_edge": 1, "cmace_imp_bwd_edge_f64_noalloc": 2,
     "cmace_imp_bwd_node": 1, "cmace_linear": 1, "cmace_symcon_fwd": 1, "cmace_symcon_bwd": 1,
     "cmace_gemm_pack_weights": 1, "cmace_gemm3x": 1, "cmace_linear_tc": 1,

@@ -39,6 +39,27 @@ def add_spline_knots(params, nknots=256):
     return params
 
 
+class _SelectElementBlock(torch.autograd.Function):
+    """big [N, Z*C] -> out[n] = big[n, z_n*C:(z_n+1)*C].  With big = h @ [W_0 | W_1 | ...] this is the element-dependent
+    product h[n] @ W[z_n] as ONE dense product plus a row-wise selection (instead of one masked product per
+    element); the backward scatters the gradient into the selected block of an otherwise zero [N, Z*C] array."""
+
+    @staticmethod
+    def forward(ctx, big, z, C):
+        N = z.shape[0]
+        ctx.save_for_backward(z)
+        ctx.width = big.shape[1]
+        return big.view(N, ctx.width // C, C)[torch.arange(N, device=big.device), z]
+
+    @staticmethod
+    def backward(ctx, g):
+        (z,) = ctx.saved_tensors
+        N, C = g.shape
+        out = torch.zeros(N, ctx.width // C, C, dtype=g.dtype, device=g.device)
+        out[torch.arange(N, device=g.device), z] = g
+        return out.view(N, ctx.width), None, None
+
+
 class InvariantMACE(torch.nn.Module):
     def __init__(self, params, U, dtype=torch.float32, device="cuda", radial="exact"):
         super().__init__()
@@ -63,6 +84,7 @@ class InvariantMACE(torch.nn.Module):
         for t, P in enumerate(params["layers"]):
             L = torch.nn.Module()
             L.register_buffer("W_up", (P["W_up"] / math.sqrt(C)).to(**dd))
+            L.register_buffer("W_up_T", L.W_up.t().contiguous())
             for i, W in enumerate(P["W_radial"]):
                 # 1/sqrt(fan_in) of e3nn's FullyConnectedNet; the second-moment constant of the activation
                 # that feeds layers 1.. is folded in as well, so the activation itself is a plain SiLU
@@ -80,12 +102,15 @@ class InvariantMACE(torch.nn.Module):
                 L.register_buffer("W_readout", (P["W_readout"] / math.sqrt(C)).to(**d64))
             else:
                 L.linear = ops.Linear(P["W_lin"].to(**dd), scale=1.0 / float(P["avg_num_neighbors"]))
-                L.register_buffer("W_sc", (P["W_sc"] / math.sqrt(C * Z)).permute(1, 0, 2).contiguous().to(**dd))
+                # W_sc [C, Z, C]: as one [C, Z*C] matrix, column block z is the matrix of element z
+                L.register_buffer("W_sc", (P["W_sc"] / math.sqrt(C * Z)).reshape(C, Z * C).contiguous().to(**dd))
+                L.register_buffer("W_sc_T", L.W_sc.t().contiguous())
                 L.register_buffer("W_readout1", (P["W_readout1"] / math.sqrt(C)).to(**d64))
                 L.register_buffer("W_readout2", (P["W_readout2"] / math.sqrt(P["W_readout2"].shape[0])).to(**d64))
             L.contraction = ops.SymmetricContraction(U3, U2, U1, P["W3"].to(dtype), P["W2"].to(dtype),
                                                      P["W1"].to(dtype)).to(device)
             L.register_buffer("W_prod", (P["W_prod"] / math.sqrt(C)).to(**dd))
+            L.register_buffer("W_prod_T", L.W_prod.t().contiguous())
             if radial == "spline":
                 L.spline = ops.CubicSpline(P["spline_knots"].to(**dd), self._tabulate(P).to(**dd),
                                            float(P["spline_h"]), self.r_max)
@@ -150,8 +175,12 @@ class InvariantMACE(torch.nn.Module):
         n_owned = N if n_owned is None else int(n_owned)
         if topology is None:
             topology = ops.topology_for(send, recv, n_owned, N)
-        vectors = positions.index_select(0, send.long()) - positions.index_select(0, recv.long()) + shifts
-        vectors = vectors.to(self.dtype)
+        if positions.is_cuda and positions.dtype == torch.float64 and shifts.dtype == torch.float64:
+            # one kernel forward; one kernel for the whole position gradient in the backward (no atomics)
+            vectors = ops.edge_vectors(positions, shifts, topology, self.dtype)
+        else:
+            vectors = positions.index_select(0, send.long()) - positions.index_select(0, recv.long()) + shifts
+            vectors = vectors.to(self.dtype)
         if self.radial == "exact":
             Y, bessel = self.edge_basis(vectors)
             lengths = None
@@ -166,14 +195,14 @@ class InvariantMACE(torch.nn.Module):
             sc = None
             if t == 1:
                 # FullyConnectedTensorProduct(h, one_hot): sc[n] = h[n] @ W_sc[z_n]
-                sc = self._sc_by_element(h, L.W_sc, species_owned)
+                sc = _SelectElementBlock.apply(self._mm(h, L.W_sc, L.W_sc_T), species_owned.long(), C)
                 if exchange is not None:
                     h = exchange(h)
-            up = h @ L.W_up
+            up = self._mm(h, L.W_up, L.W_up_T)
             m = self._messages(L, up, Y, bessel, lengths, send, recv, n_owned, topology)
             m = L.linear(m, species_owned) if t == 0 else L.linear(m)
             b = L.contraction(m, species_owned)[:, 0, :]
-            h = b @ L.W_prod
+            h = self._mm(b, L.W_prod, L.W_prod_T)
             if sc is not None:
                 h = h + sc
             h64 = h.double()
@@ -184,13 +213,11 @@ class InvariantMACE(torch.nn.Module):
         return self.scale * (es[0] + es[1]) + self.shift
 
     @staticmethod
-    def _sc_by_element(h, W_sc, species):
-        """sc[n] = h[n] @ W_sc[z_n] without materialising a [N,C,C] gather: one masked matmul per element."""
-        out = torch.zeros(h.shape[0], W_sc.shape[2], dtype=h.dtype, device=h.device)
-        for z in range(W_sc.shape[0]):
-            mask = (species == z).to(h.dtype)[:, None]
-            out = out + (h * mask) @ W_sc[z]
-        return out
+    def _mm(x, W, W_T):
+        """x @ W for a constant weight: on the tensor cores (3-term TF32 split) in float32, torch.matmul otherwise."""
+        if ops.tensor_core_ok(x.dtype, W.shape[0], W.shape[1]):
+            return ops.matmul3x(x, W, W_T)
+        return x @ W
 
     def forward(self, data, training=False, compute_force=True, topology=None):
         """data: positions [N,3], node_attrs [N,Z] one-hot (or species [N]), edge_index [2,E], shifts [E,3].

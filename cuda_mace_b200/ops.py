@@ -788,6 +788,41 @@ class _EdgeBasisFunction(torch.autograd.Function):
         return gxyz, None, None, None, None
 
 
+class _EdgeVectorsFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, positions, shifts, topo, dtype):
+        E = topo.nedges
+        vec = torch.empty(E, 3, dtype=dtype, device=positions.device)
+        _abi.call("cmace_edge_vectors_fwd_" + _suffix(vec), _ptr(positions), _ptr(topo.sender), _ptr(topo.receiver),
+                  _ptr(shifts), E, _ptr(vec), _stream())
+        ctx.topo = topo
+        return vec
+
+    @staticmethod
+    def backward(ctx, g):
+        topo = ctx.topo
+        g = g.contiguous()
+        perm, send_ptr = topo.sender_order()
+        grad = torch.empty(topo.nsenders, 3, dtype=torch.float64, device=g.device)
+        _abi.call("cmace_edge_vectors_bwd_" + _suffix(g), _ptr(g), _ptr(topo.row_ptr), _ptr(perm), _ptr(send_ptr),
+                  topo.nnodes, topo.nsenders, _ptr(grad), _stream())
+        return grad, None, None, None
+
+
+def edge_vectors(positions, shifts, topology, dtype):
+    """vec[e] = positions[sender] - positions[receiver] + shifts[e] as [E,3] of `dtype`, from float64 positions
+    [nsenders,3] and float64 shifts [E,3] (or None); the backward gives the position gradient in one kernel from the
+    topology's two edge groupings (no atomics).  What the reference does with get_edge_vectors_and_lengths
+    (models/InvariantMACE.py:297-304) and autograd."""
+    _check_cuda(positions)
+    if positions.dtype != torch.float64 or positions.shape != (topology.nsenders, 3):
+        raise RuntimeError("edge_vectors: positions must be float64 [nsenders, 3]")
+    if shifts is not None and (shifts.dtype != torch.float64 or shifts.shape != (topology.nedges, 3)):
+        raise RuntimeError("edge_vectors: shifts must be float64 [E, 3]")
+    return _EdgeVectorsFunction.apply(positions.contiguous(), None if shifts is None else shifts.contiguous(),
+                                      topology, dtype)
+
+
 class SphericalHarmonics(torch.nn.Module):
     """xyz [E,3] -> Y [16,E]: real harmonics to l=3 of the normalised vectors, e3nn component order and
     normalisation; same call as torch.classes.spherical_harmonics.SphericalHarmonics.forward

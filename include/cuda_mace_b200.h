@@ -110,6 +110,25 @@ int cmace_edge_basis_bwd_f32(const float *xyz, const float *gY, const float *gB,
 int cmace_edge_basis_bwd_f64(const double *xyz, const double *gY, const double *gB, int64_t nedges,
                              double r_max, int nbessel, int p, double *gxyz, cmace_stream_t stream);
 
+/* ---- edge vectors and their position gradient ---------------------------------------------------
+ * vec[e] = pos[sender[e]] - pos[receiver[e]] + shifts[e] (float64 arithmetic, stored in the kernels' precision;
+ * shifts may be NULL) and its adjoint grad_pos[n] = sum_{sender = n} g[e] - sum_{receiver = n} g[e], which is
+ * minus the force when g is the energy gradient with respect to the edge vectors.  The reference leaves both to
+ * torch (get_edge_vectors_and_lengths, models/InvariantMACE.py:297-304, and autograd's index_add).  The adjoint
+ * walks the receiver-sorted list (row_ptr [nrecv+1] from cmace_receiver_csr) and the sender grouping (perm,
+ * send_ptr [nsend+1] from cmace_sender_order), one warp per atom, float64 sums in a fixed order: no atomics.
+ * pos and grad_pos are [nsend,3] float64; receivers index the first nrecv atoms. */
+int cmace_edge_vectors_fwd_f32(const double *pos, const int32_t *sender, const int32_t *receiver,
+                               const double *shifts, int64_t nedges, float *vec, cmace_stream_t stream);
+int cmace_edge_vectors_fwd_f64(const double *pos, const int32_t *sender, const int32_t *receiver,
+                               const double *shifts, int64_t nedges, double *vec, cmace_stream_t stream);
+int cmace_edge_vectors_bwd_f32(const float *g, const int32_t *row_ptr, const int32_t *perm,
+                               const int32_t *send_ptr, int64_t nrecv, int64_t nsend, double *grad_pos,
+                               cmace_stream_t stream);
+int cmace_edge_vectors_bwd_f64(const double *g, const int32_t *row_ptr, const int32_t *perm,
+                               const int32_t *send_ptr, int64_t nrecv, int64_t nsend, double *grad_pos,
+                               cmace_stream_t stream);
+
 /* ---- cubic spline of the radial weights ----------------------------------------------------
  * Replace jit_evaluate_spline / jit_backward_spline (jit_wrappers/src/cubic_spline_wrapper.cpp:14-153,
  * kernels cuda/src/cubic_spline_impl.cu:5-107).  coeffs [nintervals, 4, noutputs]; R [E, noutputs];

@@ -495,3 +495,34 @@ def test_device_neighbor_list_without_atoms_or_edges(dev):
     assert ei.shape == (2, 0) and sh.shape == (0, 3)
     with pytest.raises(RuntimeError):
         ops.neighbor_list(far, (3.0, 40.0, 40.0), (True, True, True), 5.0)  # periodic axis shorter than the cutoff
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_owned,n_ghost", [(50, 0), (40, 17)])
+def test_edge_vectors_and_position_gradient(dtype, n_owned, n_ghost, dev):
+    """Edge vectors and their adjoint against index_select / autograd in float64; ghost atoms only send."""
+    from cuda_mace_b200 import ops
+
+    g = torch.Generator().manual_seed(7 + n_ghost)
+    N = n_owned + n_ghost
+    deg = torch.randint(0, 9, (n_owned,), generator=g)
+    recv = torch.repeat_interleave(torch.arange(n_owned), deg)
+    send = torch.randint(0, N, (recv.numel(),), generator=g)
+    E = recv.numel()
+    pos = torch.randn(N, 3, generator=g, dtype=torch.float64) * 3
+    shifts = torch.randn(E, 3, generator=g, dtype=torch.float64)
+    w = torch.randn(E, 3, generator=g, dtype=torch.float64)
+    po = pos.clone().requires_grad_(True)
+    ref = (po[send] - po[recv] + shifts).to(dtype)
+    (ref.double() * w).sum().backward()
+    topo = ops.EdgeTopology(send.to(dev), recv.to(dev), n_owned, N)
+    pg = pos.to(dev).requires_grad_(True)
+    vec = ops.edge_vectors(pg, shifts.to(dev), topo, dtype)
+    assert vec.dtype == dtype and torch.equal(vec.cpu(), ref.detach())
+    (vec.double() * w.to(dev)).sum().backward()
+    tol = 1e-13 if dtype == torch.float64 else 1e-6
+    assert rel_err(pg.grad, po.grad) < tol
+    # no shifts, no edges
+    assert torch.equal(ops.edge_vectors(pg, None, topo, dtype).cpu(), (pos[send] - pos[recv]).to(dtype))
+    e = torch.zeros(0, dtype=torch.int32, device=dev)
+    assert ops.edge_vectors(pg, None, ops.EdgeTopology(e, e, n_owned, N), dtype).shape == (0, 3)

@@ -119,9 +119,10 @@ class ClockSampler:
 
 def algorithmic_bytes(name, s, N, Ns, E, C, Z):
     """Bytes each kernel has to move when every tensor is read or written once (indices 4 B)."""
-    if name.startswith("cmace_gemm3x_f32["):  # tagged with its shape: A [E,K] in, [E,N] out, weights
-        k, n = (int(x.split("=")[1]) for x in name[name.index("[") + 1:-1].split(","))
-        return 4 * (E * k + E * n + k * n)
+    if name.startswith("cmace_gemm3x_f32["):  # tagged with its shape: A [rows,K] in, [rows,N] out, weights
+        dims = dict(x.split("=") for x in name[name.index("[") + 1:-1].split(","))
+        rows, k, n = int(dims.get("M", E)), int(dims["K"]), int(dims["N"])   # no M: a product over the edges
+        return 4 * (rows * k + rows * n + k * n)
     base = name[:-4]
     return {
         "cmace_imp_fwd": s * (4 * E * C + 16 * E + Ns * C + 16 * N * C) + 8 * E,
@@ -138,6 +139,8 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
         # tabulated radial weights (secondary configuration): r in, R [E,4C] out / gradR in, grad r out; table in L2
         "cmace_spline_fwd": s * (E + 4 * E * C),
         "cmace_spline_bwd": s * (2 * E + 4 * E * C),
+        "cmace_edge_vectors_fwd": 24 * Ns + 24 * E + 8 * E + s * 3 * E,
+        "cmace_edge_vectors_bwd": 2 * s * 3 * E + 4 * E + 24 * Ns,
         "cmace_edge_basis_fwd": s * E * (3 + 16 + 8),
         "cmace_edge_basis_bwd": s * E * (3 + 16 + 8 + 3),
     }.get(base)
@@ -316,6 +319,9 @@ def main():
     peak, peak_src = peaks()
     per_kernel = {}
     top, top_ms = None, -1.0
+    # products over the edges keep the short name [K=..,N=..]; the node products carry their row count
+    kernel_ms = {(name.replace(f"M={E},", "") if name.startswith("cmace_gemm3x_f32[") else name): v
+                 for name, v in kernel_ms.items()}
     for name, (calls, tot) in sorted(kernel_ms.items()):
         b = algorithmic_bytes(name, s_bytes, N, Ns, E, 128, sysd["n_species"])
         avg = tot / calls

@@ -106,52 +106,120 @@ struct Tile {
   int l, nl, mat, ntile;
 };
 
-template <int MODE>
-__device__ __forceinline__ Tile locate_tile(const GemmArgs &g, int64_t t) {
-  Tile T;
-  T.valid = false;
-  T.l = 0;
-  T.nl = 1;
-  T.mat = 0;
-  T.seg_begin = 0;
-  T.seg_rows = 0;
-  // tile indices fit 32 bits (checked on the host): cheap division
-  const uint32_t t32 = (uint32_t)t, rt32 = t32 / (uint32_t)g.n_tiles;
-  T.ntile = (int)(t32 - rt32 * (uint32_t)g.n_tiles);
-  int64_t rt = rt32;
-  if (MODE == GT_MODE_PLAIN) {
-    if (g.b_resident) {
-      // a CTA keeps one column tile of B: iteration j of CTA b works on row tile b / n_tiles + j * (CTAs per column tile)
-      const uint32_t j = t32 / gridDim.x;
-      T.ntile = (int)(blockIdx.x % (uint32_t)g.n_tiles);
-      rt = blockIdx.x / (uint32_t)g.n_tiles + (int64_t)j * (gridDim.x / (uint32_t)g.n_tiles);
-    }
-    T.row0 = rt * GT_TILE_M;
-    T.valid = T.row0 < g.M;
-    T.seg_rows = g.M;
-    return T;
+// LINEAR: the (l, element) problems in the order their tiles are numbered (l outer, element inner), built once
+// per CTA in shared memory.  Every role of the kernel walks its tiles in increasing order, so locating a tile is a
+// cursor that moves forward: no division or search per tile (one thread runs the MMA role, and scalar code
+// there costs about ten cycles per instruction: a handful of integer divisions per tile used to cost more than
+// the tile's MMAs).
+constexpr int GT_MAX_PROBLEMS = 512;   // 4 x 128 elements
+struct ProblemTable {
+  int32_t tile_begin[GT_MAX_PROBLEMS + 1];
+  int32_t seg_begin[GT_MAX_PROBLEMS];
+  int32_t seg_rows[GT_MAX_PROBLEMS];
+};
+
+// filled by all threads of the CTA; the caller synchronises afterwards
+__device__ __forceinline__ void build_problem_table(const GemmArgs &g, ProblemTable *tab) {
+  const int nprob = 4 * g.nelements;
+  for (int p = threadIdx.x; p < nprob; p += blockDim.x) {
+    const int l = p / g.nelements, z = p - l * g.nelements;
+    const int32_t b = g.elem_start ? g.elem_start[z] : 0;
+    const int64_t cnt = g.elem_start ? (int64_t)g.elem_start[z + 1] - b : g.M;
+    const uint32_t rows = (uint32_t)(cnt * (2 * l + 1));   // fits 32 bits (checked on the host)
+    tab->seg_begin[p] = b;
+    tab->seg_rows[p] = (int32_t)rows;
+    tab->tile_begin[p + 1] = (int32_t)((rows + GT_TILE_M - 1) / GT_TILE_M);   // count; prefix-summed below
   }
-  for (int l = 0; l < 4; l++) {
-    const int nl = 2 * l + 1;
-    for (int z = 0; z < g.nelements; z++) {
-      const int64_t b = g.elem_start ? g.elem_start[z] : 0;
-      const int64_t cnt = g.elem_start ? (int64_t)g.elem_start[z + 1] - b : g.M;
-      const int64_t tiles = (cnt * nl + GT_TILE_M - 1) / GT_TILE_M;
-      if (rt < tiles) {
-        T.valid = true;
-        T.row0 = rt * GT_TILE_M;
-        T.seg_begin = b;
-        T.seg_rows = cnt * nl;
-        T.l = l;
-        T.nl = nl;
-        T.mat = z * 4 + l;
-        return T;
-      }
-      rt -= tiles;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t acc = 0;
+    tab->tile_begin[0] = 0;
+    for (int p = 0; p < nprob; p++) {
+      acc += tab->tile_begin[p + 1];
+      tab->tile_begin[p + 1] = acc;
     }
   }
-  return T;
 }
+
+// The tiles of this CTA in increasing order.  PLAIN: tile t = (row tile, column tile) with the column tile fastest,
+// or, with resident B images, a fixed column tile per CTA and row tiles blockIdx / n_tiles + j * (CTAs per column tile).
+template <int MODE>
+struct TileWalker {
+  int64_t t, total, rt, rt_step, M;
+  int ntile, nt_step, n_tiles;
+  const ProblemTable *tab;
+  int nprob, nelements, prob, l, z;
+  bool started;
+
+  __device__ __forceinline__ TileWalker(const GemmArgs &g, const ProblemTable *tab_) {
+    started = false;
+    t = blockIdx.x;
+    total = g.total_tiles;
+    M = g.M;
+    n_tiles = g.n_tiles;
+    tab = tab_;
+    nelements = g.nelements;
+    nprob = 4 * g.nelements;
+    prob = l = z = 0;
+    rt = 0;
+    ntile = 0;
+    rt_step = 0;
+    nt_step = 0;
+    if (MODE == GT_MODE_PLAIN) {
+      rt = blockIdx.x / (uint32_t)n_tiles;
+      ntile = (int)(blockIdx.x - (uint32_t)rt * (uint32_t)n_tiles);
+      rt_step = gridDim.x / (uint32_t)n_tiles;
+      nt_step = g.b_resident ? 0 : (int)(gridDim.x - (uint32_t)rt_step * (uint32_t)n_tiles);
+    }
+  }
+
+  // moves to the next tile; false when the CTA has no more
+  __device__ __forceinline__ bool next(Tile &T) {
+    if (started) {
+      t += gridDim.x;
+      if (MODE == GT_MODE_PLAIN) {
+        rt += rt_step;
+        ntile += nt_step;
+        if (ntile >= n_tiles) {
+          ntile -= n_tiles;
+          rt++;
+        }
+      }
+    }
+    started = true;
+    T.valid = false;
+    if (t >= total) return false;
+    if (MODE == GT_MODE_PLAIN) {
+      T.row0 = rt * GT_TILE_M;
+      if (T.row0 >= M) return false;   // padded index space of the resident-B mode: row tiles only grow
+      T.seg_begin = 0;
+      T.seg_rows = M;
+      T.l = 0;
+      T.nl = 1;
+      T.mat = 0;
+      T.ntile = ntile;
+      T.valid = true;
+      return true;
+    }
+    while (prob < nprob && t >= tab->tile_begin[prob + 1]) {
+      prob++;
+      if (++z == nelements) {
+        z = 0;
+        l++;
+      }
+    }
+    if (prob >= nprob) return false;
+    T.row0 = (t - tab->tile_begin[prob]) * GT_TILE_M;
+    T.seg_begin = tab->seg_begin[prob];
+    T.seg_rows = tab->seg_rows[prob];
+    T.l = l;
+    T.nl = 2 * l + 1;
+    T.mat = z * 4 + l;
+    T.ntile = 0;
+    T.valid = true;
+    return true;
+  }
+};
 
 // global row (in units of rows of A / out) of local row r of a tile, or -1
 template <int MODE>
@@ -159,8 +227,15 @@ __device__ __forceinline__ int64_t global_row(const GemmArgs &g, const Tile &T, 
   const int64_t lr = T.row0 + r;
   if (lr >= T.seg_rows) return -1;
   if (MODE == GT_MODE_PLAIN) return lr;
-  // rows of one (element, l) problem fit 32 bits (checked on the host): cheap division
-  const uint32_t lr32 = (uint32_t)lr, q = lr32 / (uint32_t)T.nl;
+  // rows of one (element, l) problem fit 32 bits (checked on the host); constant divisors compile to a multiplication
+  const uint32_t lr32 = (uint32_t)lr;
+  uint32_t q;
+  switch (T.l) {
+    case 0: q = lr32; break;
+    case 1: q = lr32 / 3u; break;
+    case 2: q = lr32 / 5u; break;
+    default: q = lr32 / 7u; break;
+  }
   const int64_t slot = T.seg_begin + q;
   const int64_t node = g.node_order ? (int64_t)g.node_order[slot] : slot;
   return node * 16 + T.l * T.l + (int)(lr32 - q * (uint32_t)T.nl);
@@ -176,12 +251,19 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 // Alo*Bhi product reads its A operand from there.  Shared-memory bandwidth is what the roles of this kernel compete
 // for; this takes the image's 16 KB store and its 16 KB read by the tensor core out of every pipeline item.  Needs
 // room in tensor memory next to the accumulators: two accumulators of 2 npad columns + 32 columns per ring slot.
-template <bool ACT, int MODE, bool TS = false>
+// WIDE (implies TS; K = 64 with resident B images): a pipeline item is the whole K extent of a tile (two K blocks), and the
+// three split terms accumulate into the same columns, which leaves room for the ring of residual images beside two
+// 128-column accumulators.  Per item the roles synchronise once instead of twice, the MMA thread issues 24
+// instructions back to back, and the epilogue reads half as many columns.
+template <bool ACT, int MODE, bool TS = false, bool WIDE = false>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 5];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ int32_t tab_words[MODE == GT_MODE_LINEAR ? sizeof(ProblemTable) / 4 : 1];
+  const ProblemTable *tab = reinterpret_cast<const ProblemTable *>(tab_words);
+  if (MODE == GT_MODE_LINEAR) build_problem_table(g, reinterpret_cast<ProblemTable *>(tab_words));
 
   // dynamic smem base rounded up to 1024 bytes (the swizzle pattern repeats every 1024 bytes)
   const uint32_t smem_first = (smem_u32(smem) + 1023u) & ~1023u;
@@ -222,26 +304,31 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   const int k_blocks = g.k_blocks;
   const uint32_t b_image = (uint32_t)g.npad * 128u;  // bytes of one B image
   const uint32_t b_off = TS ? GT_A_SLAB : 2 * GT_A_SLAB;          // the stage's B block follows its A image(s)
-  const uint32_t acc_stride = TS ? 2u * (uint32_t)g.npad : 256u;  // tensor-memory columns between the accumulators
-  const uint32_t lo_ring = tmem_base + 4u * (uint32_t)g.npad;     // TS: slot s holds its 32 columns at + 32 s
+  // tensor-memory columns between the accumulators; TS: ring of residual images behind them, 32 (WIDE: 64) columns a slot
+  const uint32_t acc_stride = WIDE ? (uint32_t)g.npad : TS ? 2u * (uint32_t)g.npad : 256u;
+  const uint32_t lo_ring = tmem_base + (WIDE ? 2u : 4u) * (uint32_t)g.npad;
+  const int items = WIDE ? k_blocks / 2 : k_blocks;               // pipeline items per tile
 
   if (MODE == GT_MODE_PLAIN && TS && warp < GT_PRODUCER_WARPS) {
     // ================================ converters, residual image to tensor memory ================================
     // A thread owns one row of the tile (the tensor-memory lane its warp may access) and 16 of the K block's 32
     // columns: four 16-byte shared-memory loads (conflict-free: the 128-byte swizzle puts the same logical chunk of
     // eight consecutive rows into eight different bank groups), three ALU operations per float, one tcgen05.st.
+    // (WIDE: the warp's half is one of the item's two K blocks, eight loads and one 32-column store.)
     const int q = warp & 3, hf = warp >> 2;
     const int r = q * 32 + lane;
-    uint32_t soff[4];
+    uint32_t soff[WIDE ? 8 : 4];
 #pragma unroll
-    for (int c = 0; c < 4; c++) soff[c] = (uint32_t)sw128_offset(r, 4 * hf + c);
-    const uint32_t t_lo = lo_ring + ((uint32_t)(q * 32) << 16) + 16u * (uint32_t)hf;
+    for (int c = 0; c < (WIDE ? 8 : 4); c++)
+      soff[c] = WIDE ? (uint32_t)(hf * GT_A_SLAB) + (uint32_t)sw128_offset(r, c) : (uint32_t)sw128_offset(r, 4 * hf + c);
+    const uint32_t t_lo = lo_ring + ((uint32_t)(q * 32) << 16) + (WIDE ? 32u : 16u) * (uint32_t)hf;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
-      if (!locate_tile<MODE>(g, t).valid) continue;
-      for (int kb = 0; kb < k_blocks; kb++) {
+    TileWalker<MODE> tiles(g, tab);
+    Tile T;
+    while (ok && tiles.next(T)) {
+      for (int kb = 0; kb < items; kb++) {
         uint32_t got = 1;
         const long long tw = GT_NOW();
         if (lane == 0) got = mbar_wait(tma_full + 8 * stage, phase) ? 1u : 0u;
@@ -254,9 +341,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           break;
         }
         const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-        uint32_t lo[16];
+        uint32_t lo[WIDE ? 32 : 16];
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
+        for (int c = 0; c < (WIDE ? 8 : 4); c++) {
           float4 a;
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                        : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
@@ -267,7 +354,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           lo[4 * c + 2] = __float_as_uint(to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u)));
           lo[4 * c + 3] = __float_as_uint(to_tf32(a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u)));
         }
-        tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
+        if constexpr (WIDE) tmem_st32(t_lo + 64u * (uint32_t)stage, lo);
+        else tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -295,8 +383,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
-      if (!locate_tile<MODE>(g, t).valid) continue;
+    TileWalker<MODE> tiles(g, tab);
+    Tile T;
+    while (ok && tiles.next(T)) {
       for (int kb = 0; kb < k_blocks; kb++) {
         uint32_t got = 1;
         const long long tw = GT_NOW();
@@ -355,25 +444,17 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     const int rbase = p >> 3;        // rows rbase + GT_ROW_STEP * i
     // head: the next (tile, K block) item whose loads have not been issued yet
     struct Head {
-      int64_t t;
       Tile T;
       int kb;
       bool valid;
       int64_t grow[GT_ROWS_PER_THREAD];
     } head;
+    TileWalker<MODE> tiles(g, tab);
     auto advance = [&]() {
       if (++head.kb < k_blocks && head.valid) return;
       head.kb = 0;
-      for (;;) {
-        head.t += gridDim.x;
-        if (head.t >= g.total_tiles) {
-          head.valid = false;
-          return;
-        }
-        head.T = locate_tile<MODE>(g, head.t);
-        if (head.T.valid) break;
-      }
-      head.valid = true;
+      head.valid = tiles.next(head.T);
+      if (!head.valid) return;
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row<MODE>(g, head.T, rbase + GT_ROW_STEP * i);
     };
@@ -448,7 +529,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       return true;
     };
 
-    head.t = (int64_t)blockIdx.x - gridDim.x;
     head.kb = k_blocks;  // forces advance() to step to the first tile
     head.valid = false;
     advance();
@@ -486,12 +566,12 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           bulk_copy_g2s(smem_first + off, src + off, n, b_full);
         }
       }
-      for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
-        const Tile T = locate_tile<MODE>(g, t);
-        if (!T.valid) continue;
+      TileWalker<MODE> tiles(g, tab);
+      Tile T;
+      while (ok && tiles.next(T)) {
         const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
                                     ((int64_t)(T.mat * g.n_tiles + T.ntile) * k_blocks) * (2 * (int64_t)b_image);
-        for (int kb = 0; kb < k_blocks; kb++) {
+        for (int kb = 0; kb < items; kb++) {
           const long long tl = GT_NOW();
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1)) {
             report(g, 5);
@@ -500,6 +580,16 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           }
           GT_PROF(g, 10, tl);
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+          if (WIDE) {   // both K blocks of the tile, B is resident
+            mbar_arrive_expect_tx(tma_full + 8 * stage, 2u * GT_A_SLAB);
+            tma_load_2d(sA, &tmap, 2 * kb * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
+            tma_load_2d(sA + GT_A_SLAB, &tmap, (2 * kb + 1) * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
+            if (++stage == GT_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
           mbar_arrive_expect_tx(tma_full + 8 * stage, g.b_resident ? (uint32_t)GT_A_SLAB : GT_A_SLAB + 2 * b_image);
           tma_load_2d(sA, &tmap, kb * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
           if (!g.b_resident)
@@ -531,9 +621,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // integer operations, no warp-wide shuffle or re-convergence.  Whatever sits between the batches leaves the
     // tensor core idle (the issue of an MMA blocks until the previous ones have drained, so the queue is shallow).
     if (lane != 0) ok = false;
-    for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
-      const Tile T = locate_tile<MODE>(g, t);
-      if (!T.valid) continue;
+    TileWalker<MODE> tiles(g, tab);
+    Tile T;
+    while (ok && tiles.next(T)) {
       int ncols = g.N - T.ntile * 128;
       ncols = ncols > 128 ? 128 : ncols;
       const int nmma = (ncols + 15) & ~15;
@@ -549,7 +639,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       GT_PROF(g, 3, ta);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * acc_stride;
-      for (int kb = 0; kb < k_blocks; kb++) {
+      for (int kb = 0; kb < items; kb++) {
         const long long tf = GT_NOW();
         if (!GT_DBG(g, 1024) && !mbar_wait(full_bar + 8 * stage, phase)) {
           report(g, 3);
@@ -559,7 +649,25 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         GT_PROF(g, 4, tf);
         const long long ti = GT_NOW();
         if (!GT_DBG(g, 512)) tc_fence_after();
-        {
+        if (WIDE) {
+          // two K blocks, four K steps each, three terms into the same columns
+          const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+          const uint32_t a_lo_t = lo_ring + 64u * (uint32_t)stage;
+#pragma unroll
+          for (int kbi = 0; kbi < 2; kbi++) {
+            const uint64_t a_hi0 = umma_desc_sw128(sA + kbi * GT_A_SLAB);
+            const uint64_t b_hi0 = umma_desc_sw128(smem_first + (uint32_t)(2 * kb + kbi) * 2u * b_image);
+            const uint64_t b_lo0 = umma_desc_sw128(smem_first + (uint32_t)(2 * kb + kbi) * 2u * b_image + b_image);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              umma_tf32(d_tmem, a_hi0 + (uint64_t)(2 * j), b_hi0 + (uint64_t)(2 * j), idesc1, (kb | kbi | j) != 0);
+              umma_tf32_acc(d_tmem, a_hi0 + (uint64_t)(2 * j), b_lo0 + (uint64_t)(2 * j), idesc1);
+              umma_tf32_ts_acc(d_tmem, a_lo_t + 32u * kbi + 8u * j, b_hi0 + (uint64_t)(2 * j), idesc1);
+            }
+          }
+          umma_commit(empty_bar + 8 * stage);
+          if (kb == items - 1) umma_commit(acc_full + 8 * acc);
+        } else {
           // descriptors of K step j differ from those of step 0 by j * 32 bytes = 2 address units
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
           const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
@@ -629,9 +737,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     const int r = q * 32 + lane;            // row of the tile
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
-    for (int64_t t = blockIdx.x; t < g.total_tiles; t += gridDim.x) {
-      const Tile T = locate_tile<MODE>(g, t);
-      if (!T.valid) continue;
+    TileWalker<MODE> tiles(g, tab);
+    Tile T;
+    while (tiles.next(T)) {
       const int64_t grow = global_row<MODE>(g, T, r);
       const int n0 = T.ntile * 128;
       int ncols = g.N - n0;
@@ -660,33 +768,59 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             uint32_t v[16], w[16];
             const uint32_t ta = taddr + ((uint32_t)(16 * hr) << 16) + (uint32_t)c0;
             tmem_ld_16x256b_x4(ta, v);                 // Ahi*Bhi + Alo*Bhi
-            tmem_ld_16x256b_x4(ta + g.npad, w);        // Ahi*Blo
+            if constexpr (WIDE) {
+#pragma unroll
+              for (int i = 0; i < 16; i++) w[i] = 0u;  // all three terms are in v
+            } else {
+              tmem_ld_16x256b_x4(ta + g.npad, w);      // Ahi*Blo
+            }
             tmem_ld_wait();
             const int64_t gra = __shfl_sync(0xffffffffu, grow, 16 * hr + (lane >> 2));
             const int64_t grb = __shfl_sync(0xffffffffu, grow, 16 * hr + 8 + (lane >> 2));
-            float *pa = g.out + gra * g.N + n0 + c0 + 2 * (lane & 3);
-            float *pb = g.out + grb * g.N + n0 + c0 + 2 * (lane & 3);
+            // One exchange with the neighbouring lane turns the 8-byte pieces into 16-byte ones: the even lane keeps
+            // column blocks 0 and 1 and receives its neighbour's halves of them, the odd lane blocks 2 and 3.  A store
+            // instruction then writes two whole 32-byte sectors of a row instead of one (the stores of this kernel
+            // are bound by the number of requests, not by bytes).
+            const bool odd = (lane & 1) != 0;
+            float sv[16];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const bool col_ok = c0 + 8 * j + 2 * (lane & 3) < ncols && !GT_DBG(g, 4);
-              float2 oa = make_float2((__uint_as_float(v[4 * j]) + __uint_as_float(w[4 * j])) * g.scale,
-                                      (__uint_as_float(v[4 * j + 1]) + __uint_as_float(w[4 * j + 1])) * g.scale);
-              float2 ob = make_float2((__uint_as_float(v[4 * j + 2]) + __uint_as_float(w[4 * j + 2])) * g.scale,
-                                      (__uint_as_float(v[4 * j + 3]) + __uint_as_float(w[4 * j + 3])) * g.scale);
+            for (int i = 0; i < 16; i++) sv[i] = (__uint_as_float(v[i]) + __uint_as_float(w[i])) * g.scale;
+            float4 oa[2], ob[2];
+#pragma unroll
+            for (int m = 0; m < 2; m++) {
+              float rc[4];
+#pragma unroll
+              for (int x = 0; x < 4; x++)
+                rc[x] = __shfl_xor_sync(0xffffffffu, odd ? sv[4 * m + x] : sv[4 * (2 + m) + x], 1);
+              oa[m] = odd ? make_float4(rc[0], rc[1], sv[4 * (2 + m)], sv[4 * (2 + m) + 1])
+                          : make_float4(sv[4 * m], sv[4 * m + 1], rc[0], rc[1]);
+              ob[m] = odd ? make_float4(rc[2], rc[3], sv[4 * (2 + m) + 2], sv[4 * (2 + m) + 3])
+                          : make_float4(sv[4 * m + 2], sv[4 * m + 3], rc[2], rc[3]);
+            }
+            const int cbase = c0 + 2 * (lane & 2) + (odd ? 16 : 0);   // first column of this lane's piece m = 0
+            float *pa = g.out + gra * g.N + n0 + cbase;
+            float *pb = g.out + grb * g.N + n0 + cbase;
+#pragma unroll
+            for (int m = 0; m < 2; m++) {
+              const bool col_ok = cbase + 8 * m < ncols && !GT_DBG(g, 4);
               if (ACT && g.ep_z != nullptr) {
                 if (gra >= 0 && col_ok) {
-                  const float2 z = __ldg(reinterpret_cast<const float2 *>(g.ep_z + (pa - g.out) + 8 * j));
-                  oa.x *= silu_n_grad(z.x);
-                  oa.y *= silu_n_grad(z.y);
+                  const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (pa - g.out) + 8 * m));
+                  oa[m].x *= silu_n_grad(z.x);
+                  oa[m].y *= silu_n_grad(z.y);
+                  oa[m].z *= silu_n_grad(z.z);
+                  oa[m].w *= silu_n_grad(z.w);
                 }
                 if (grb >= 0 && col_ok) {
-                  const float2 z = __ldg(reinterpret_cast<const float2 *>(g.ep_z + (pb - g.out) + 8 * j));
-                  ob.x *= silu_n_grad(z.x);
-                  ob.y *= silu_n_grad(z.y);
+                  const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (pb - g.out) + 8 * m));
+                  ob[m].x *= silu_n_grad(z.x);
+                  ob[m].y *= silu_n_grad(z.y);
+                  ob[m].z *= silu_n_grad(z.z);
+                  ob[m].w *= silu_n_grad(z.w);
                 }
               }
-              if (gra >= 0 && col_ok) *reinterpret_cast<float2 *>(pa + 8 * j) = oa;
-              if (grb >= 0 && col_ok) *reinterpret_cast<float2 *>(pb + 8 * j) = ob;
+              if (gra >= 0 && col_ok) *reinterpret_cast<float4 *>(pa + 8 * m) = oa[m];
+              if (grb >= 0 && col_ok) *reinterpret_cast<float4 *>(pb + 8 * m) = ob[m];
             }
           }
         }
@@ -848,11 +982,21 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   static const bool ts_off = getenv("CMACE_GEMM_TS") && atoi(getenv("CMACE_GEMM_TS")) == 0;
   const int ts_slots = (GT_TMEM_COLS - 4 * g.npad) / 32;
   g.a_lo_tmem = (g.mode == GT_MODE_PLAIN && !act && ts_slots >= 4 && !ts_off) ? 1 : 0;
-  g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
+  // whole-K items when K is exactly two K blocks and B is resident; at least two ring slots of 64 columns
+  // (measured 1-9 % slower than two items per tile on the [E,64]x[64,512] and [E,64]x[64,64] products, so it is opt-in)
+  static const bool wide_off = !(getenv("CMACE_GEMM_WIDE") && atoi(getenv("CMACE_GEMM_WIDE")) == 1);
+  const int wide_slots = (GT_TMEM_COLS - 2 * g.npad) / 64;
+  const bool wide = g.mode == GT_MODE_PLAIN && !act && !ts_off && !wide_off && g.b_resident && g.K == 2 * GT_KBLOCK &&
+                    wide_slots >= 2;
+  if (wide) g.a_lo_tmem = 1;
+  g.stage_bytes = wide ? 2 * GT_A_SLAB : (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   const int ep_bytes = g.mode == GT_MODE_PLAIN ? 0 : GT_EP_BYTES;   // only the LINEAR epilogue stages through shared memory
-  g.stages = (GT_SMEM_BUDGET - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
+  // the LINEAR variant holds its problem table in static shared memory
+  const int budget = GT_SMEM_BUDGET - (g.mode == GT_MODE_LINEAR ? (int)sizeof(ProblemTable) + 1024 : 0);
+  g.stages = (budget - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
-  if (g.a_lo_tmem && g.stages > ts_slots) g.stages = ts_slots;
+  if (g.a_lo_tmem && !wide && g.stages > ts_slots) g.stages = ts_slots;
+  if (wide && g.stages > wide_slots) g.stages = wide_slots;
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
   const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024;
   CUtensorMap tmap;
@@ -862,6 +1006,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   }
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
               : act                    ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN>
+              : wide                   ? gemm3x_tf32_kernel<false, GT_MODE_PLAIN, true, true>
               : g.a_lo_tmem            ? gemm3x_tf32_kernel<false, GT_MODE_PLAIN, true>
                                        : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -928,6 +1073,8 @@ int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node
   if (nnodes > 0x7fffffffLL / 16) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: too many nodes");
   if (K % 8 != 0 || Nout % 4 != 0 || Nout > 128)
     return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: K multiple of 8, Nout multiple of 4 and Nout <= 128");
+  if (4 * nelements > GT_MAX_PROBLEMS)
+    return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: at most %d elements", GT_MAX_PROBLEMS / 4);
   if (nnodes == 0) return CMACE_OK;
   if (!X || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_linear_tc: null pointer");
   if ((nelements > 1) != (node_order != nullptr) || (node_order != nullptr) != (elem_start != nullptr))

@@ -132,7 +132,7 @@ def _gemm3x(A, Bt, scale=1.0, act_a=False, ep_z=None):
             raise RuntimeError("ep_z must have the output's shape")
     out = torch.empty(M, N, dtype=torch.float32, device=A.device)
     _abi.call("cmace_gemm3x_f32", _ptr(A), _ptr(_pack(Bt)), M, K, N, float(scale), 1 if act_a else 0, _ptr(ep_z),
-              _ptr(out), _ptr(_status_tensor(A.device)), _stream(), tag=f"K={K},N={N}")
+              _ptr(out), _ptr(_status_tensor(A.device)), _stream(), tag=f"M={M},K={K},N={N}")
     return out
 
 
@@ -499,7 +499,7 @@ def _linear_call(X, W, W_other, node_order, elem_start, nelements, scale):
     if W.dtype != X.dtype:
         raise TypeError("X and W must have the same dtype")
     out = torch.empty(N, 16, Nout, dtype=X.dtype, device=X.device)
-    if tensor_core_ok(X.dtype, K, Nout) and Nout <= 128:
+    if tensor_core_ok(X.dtype, K, Nout) and Nout <= 128 and nelements <= 128:   # the kernel's problem table holds 4 x 128
         _abi.call("cmace_linear_tc_f32", _ptr(X), _ptr(_pack(W_other)), _ptr(node_order), _ptr(elem_start),
                   nelements, N, K, Nout, float(scale), _ptr(out), _ptr(_status_tensor(X.device)), _stream())
         return out

@@ -63,6 +63,7 @@ constexpr int GT_TMEM_COLS = 512;                   // two accumulators of 2 x 1
 constexpr int GT_PREFETCH = 2;                      // K blocks of global loads in flight per producer thread
 constexpr int GT_EP_STRIDE = 20;                    // floats per row of an epilogue transpose buffer (16 + padding)
 constexpr int GT_EP_BYTES = 8 * 32 * GT_EP_STRIDE * 4;  // one buffer per epilogue warp, 20 KB in all
+constexpr int GT_EP_TMA_BYTES = 8 * 32 * 128;       // PLAIN with TMA stores: 32 rows x 128 bytes per epilogue warp
 #ifdef CMACE_GEMM_DEBUG
 #define GT_DBG(g, bit) (((g).debug & (bit)) != 0)
 #define GT_PROF(g, slot, t0) do { if (((g).debug & 4096) && blockIdx.x == 0 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long *>((g).status) + (slot), (unsigned long long)(clock64() - (t0))); } while (0)
@@ -92,6 +93,7 @@ struct GemmArgs {
   int stages, stage_bytes;      // shared-memory ring: depth and bytes per stage (A hi+lo, B hi+lo)
   int b_resident;               // PLAIN: bytes of this CTA's B images kept in shared memory for the whole kernel, or 0
   int a_lo_tmem;                // PLAIN: 1 when the residual image of A lives in tensor memory (kernel variant TS)
+  int ep_tma;                   // PLAIN: 1 when the epilogue stores tiles with TMA from a staging buffer
   int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
   int a_act;                    // 1: apply SiLU to A while loading it
   const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
@@ -257,7 +259,8 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 // instructions back to back, and the epilogue reads half as many columns.
 template <bool ACT, int MODE, bool TS = false, bool WIDE = false>
 __global__ void __launch_bounds__(GT_THREADS, 1)
-    gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap) {
+    gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap,
+                       const __grid_constant__ CUtensorMap tmap_out) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 5];
   __shared__ uint32_t tmem_base_slot;
@@ -755,7 +758,45 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * acc_stride + ((uint32_t)(q * 32) << 16);
-      if (MODE == GT_MODE_PLAIN) {
+      if (MODE == GT_MODE_PLAIN && !ACT && g.ep_tma) {
+        // Tile store by TMA.  Global stores from registers cost the load/store data pipe one pass per 32-byte sector
+        // whatever their shape (64 KB per tile = 2048 passes, the pipe measured 70 % busy on [E,64]x[64,512]); here
+        // a warp writes its 32 rows x 32 columns into a swizzled 4 KB staging buffer (eight conflict-free 16-byte
+        // stores per thread) and one thread hands the buffer to the copy engine, which clips rows and columns
+        // outside the matrix.
+        const uint32_t stg = smem_base + GT_STAGES * GT_STAGE_BYTES + (uint32_t)(warp - (GT_PRODUCER_WARPS + 1)) * 4096u;
+        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+          if (lane == 0) tma_store_wait_read();   // the previous store has left the staging buffer
+          __syncwarp();
+#pragma unroll
+          for (int h16 = 0; h16 < 2; h16++) {
+            uint32_t v[16], w[16];
+            tmem_ld16_nowait(taddr + (uint32_t)(c0 + 16 * h16), v);
+            if constexpr (WIDE) {
+#pragma unroll
+              for (int i = 0; i < 16; i++) w[i] = 0u;
+            } else {
+              tmem_ld16_nowait(taddr + (uint32_t)(g.npad + c0 + 16 * h16), w);
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+              const uint32_t dst = stg + (uint32_t)sw128_offset(lane, 4 * h16 + c);
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                           "f"((__uint_as_float(v[4 * c]) + __uint_as_float(w[4 * c])) * g.scale),
+                           "f"((__uint_as_float(v[4 * c + 1]) + __uint_as_float(w[4 * c + 1])) * g.scale),
+                           "f"((__uint_as_float(v[4 * c + 2]) + __uint_as_float(w[4 * c + 2])) * g.scale),
+                           "f"((__uint_as_float(v[4 * c + 3]) + __uint_as_float(w[4 * c + 3])) * g.scale)
+                           : "memory");
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          // a box that starts inside the matrix: the engine clips what hangs over, a start outside is never issued
+          if (lane == 0 && T.row0 + q * 32 < g.M && !GT_DBG(g, 4))
+            tma_store_2d(&tmap_out, n0 + c0, (int)T.row0 + q * 32, stg);
+        }
+      } else if (MODE == GT_MODE_PLAIN) {
         // Straight from tensor memory to global memory, no shared-memory transpose: the 16x256b load shape hands
         // thread t two rows (t/4 and t/4 + 8 of a 16-row half) and, per 8-column block, the two columns
         // 2(t%4), 2(t%4)+1 -- four neighbouring lanes hold 32 contiguous bytes of a row, so an 8-byte store per
@@ -878,6 +919,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       acc_phase[acc] ^= 1;
       acc ^= 1;
     }
+    // the copy engine still reads this warp's staging buffer and writes its tile: wait before the CTA retires
+    if (MODE == GT_MODE_PLAIN && !ACT && g.ep_tma && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -962,6 +1005,22 @@ int encode_rows_tensor_map(CUtensorMap *tmap, const float *A, int64_t rows, int 
   return CMACE_OK;
 }
 
+// out [rows, N] as 32-row x 32-column boxes (128 bytes per row: one swizzle span) for the epilogue's tile stores
+static int encode_out_tensor_map(CUtensorMap *tmap, float *out, int64_t rows, int N, const char *what) {
+  memset(tmap, 0, sizeof(*tmap));
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available", what);
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled (out) failed (%d)", what, (int)r);
+  return CMACE_OK;
+}
+
 static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -990,7 +1049,11 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
                     wide_slots >= 2;
   if (wide) g.a_lo_tmem = 1;
   g.stage_bytes = wide ? 2 * GT_A_SLAB : (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
-  const int ep_bytes = g.mode == GT_MODE_PLAIN ? 0 : GT_EP_BYTES;   // only the LINEAR epilogue stages through shared memory
+  // PLAIN: tile stores by TMA from a 4 KB staging buffer per epilogue warp (N >= 32: the box is 32 columns wide);
+  // LINEAR: the transpose buffers of its epilogue
+  static const bool ep_tma_off = getenv("CMACE_GEMM_EP_TMA") && atoi(getenv("CMACE_GEMM_EP_TMA")) == 0;
+  g.ep_tma = (g.mode == GT_MODE_PLAIN && !act && g.N >= 32 && !ep_tma_off) ? 1 : 0;
+  const int ep_bytes = g.mode == GT_MODE_PLAIN ? (g.ep_tma ? GT_EP_TMA_BYTES : 0) : GT_EP_BYTES;
   // the LINEAR variant holds its problem table in static shared memory
   const int budget = GT_SMEM_BUDGET - (g.mode == GT_MODE_LINEAR ? (int)sizeof(ProblemTable) + 1024 : 0);
   g.stages = (budget - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
@@ -999,10 +1062,14 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (wide && g.stages > wide_slots) g.stages = wide_slots;
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
   const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024;
-  CUtensorMap tmap;
+  CUtensorMap tmap, tmap_out;
   memset(&tmap, 0, sizeof(tmap));
+  memset(&tmap_out, 0, sizeof(tmap_out));
   if (g.mode == GT_MODE_PLAIN) {
     if (int rc = encode_rows_tensor_map(&tmap, g.A, g.M, g.K, what)) return rc;
+  }
+  if (g.ep_tma) {
+    if (int rc = encode_out_tensor_map(&tmap_out, g.out, g.M, g.N, what)) return rc;
   }
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
               : act                    ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN>
@@ -1022,7 +1089,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     g.total_tiles = ((row_tiles + per_col - 1) / per_col) * blocks;
   }
   if (blocks < 1) return CMACE_OK;
-  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g, tmap);
+  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g, tmap, tmap_out);
   return check_launch(what);
 }
 

@@ -17,19 +17,23 @@
 //              pre-packed B block (hi and lo images, swizzled by the pack kernel).  Nothing waits in
 //              registers for HBM.
 //   warps 0-7  converters (PLAIN): read the raw tile back from shared memory and store the residual image
-//              lo = tf32(a - trunc(a)) next to it.
+//              lo = tf32(a - trunc(a)) next to it -- or, where tensor memory has room beside the accumulators
+//              (kernel variant TS), into a ring of tensor-memory columns, from where the Alo*Bhi product
+//              takes its A operand.
 //              With the LINEAR row map (gathered rows) the same warps load the row segments into registers
 //              themselves, two items ahead, and convert from there.
 //   warp 8     MMA issuer: one elected thread issues tcgen05.mma kind::tf32 (M=128, N<=128, K=8),
 //              4 K-steps x 3 split terms per stage, and commits to the stage's "empty" barrier and,
 //              after the last K block of a tile, to the accumulator's "full" barrier.
 //   warps 9-16 epilogue: tcgen05.ld of the accumulator, add the two column ranges, scale, store, release the
-//              accumulator.  PLAIN: 16x256b loads (a thread holds column pairs of two rows) stored straight
-//              to global memory as 32-byte row pieces per four lanes -- no shared memory.  LINEAR: 32x32b
-//              loads (a thread holds one row, 16 columns at a time), transposed through a per-warp
+//              accumulator.  PLAIN: a warp writes its 32 rows x 32 columns into a swizzled 4 KB staging buffer
+//              and one thread stores it by TMA (the engine clips what lies outside the matrix); with the
+//              activation-fused variant or N < 32, 16x256b loads stored straight from registers.  LINEAR:
+//              32x32b loads (a thread holds one row, 16 columns at a time), transposed through a per-warp
 //              shared-memory buffer, stored as 64-byte row pieces.
 // Accumulators are double buffered in tensor memory (2 x 256 columns), so the epilogue of tile t
-// overlaps the MMAs of tile t+1, and a 3-stage shared-memory ring overlaps loads with MMAs.
+// overlaps the MMAs of tile t+1, and a 3-8 stage shared-memory ring overlaps loads with MMAs.
+// Every role walks its tiles with a forward-moving cursor (TileWalker): no division per tile.
 //
 // Row maps: PLAIN (row r of tile t is r + 128 t; used for the radial multilayer perceptron, N may be
 // several 128-column tiles) and LINEAR (rows are the (node, m) pairs of one (element, l) problem of the

@@ -272,7 +272,9 @@ def test_cpu_tensors_are_rejected():
 
 
 @pytest.mark.parametrize("M,K,N", [(1000, 64, 512), (300, 8, 64), (129, 64, 64), (257, 512, 64), (64, 64, 8),
-                                   (5000, 128, 128), (1, 32, 96)])
+                                   (5000, 128, 128), (1, 32, 96),
+                                   # column counts that are not a multiple of the 32-column store box, ragged row tails
+                                   (513, 64, 40), (777, 96, 136), (40001, 64, 72), (95, 512, 104)])
 def test_tensor_core_gemm_has_float32_accuracy(M, K, N, dev):
     """tcgen05 kind::tf32 with the hi/lo split against a float64 matmul: float32-grade, not TF32-grade."""
     from cuda_mace_b200 import ops

@@ -70,4 +70,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_reference_pins.py <path of the cuda-mace checkout>")
+    main(sys.argv[1])

@@ -150,7 +150,8 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
 # the 8 000-atom case summarised under profiles/ (E = 417 248 there); the traffic of every edge kernel grows in
 # proportion to E, so a full launch moves this many bytes times its own E.
 NCU_TRAFFIC_PER_EDGE = {
-    "cmace_imp_bwd_edge_f32": (4904.0, "profiles/imp_kernels_small_case_f32.txt"),   # staged kernel: 1002 + 1044 MB
+    # staged kernel, mean of a step's two launches: 1016 + 1050 MB with the T array, 1008 + 840 MB without
+    "cmace_imp_bwd_edge_f32": (4691.0, "profiles/imp_kernels_small_case_f32.txt"),
     "cmace_imp_fwd_f32": (2170.0, "profiles/imp_kernels_small_case_f32.txt"),
     "cmace_gemm3x_f32[K=512,N=64]": (2285.0, "profiles/gemm3x_tf32_small_case_f32.txt"),
     "cmace_gemm3x_f32[K=64,N=512]": (2176.0, "profiles/gemm3x_tf32_small_case_f32.txt"),

@@ -85,14 +85,16 @@ def paths_nu3():
 
 
 def u_matrices(dtype=torch.float64):
-    """(U3, U2, U1) dense CPU tensors; every path has unit Frobenius norm, first non-zero > 0."""
+    """(U3, U2, U1) dense CPU tensors; every path has unit Frobenius norm and a positive m1 = m2 = m3 = 0 entry.
+    That sign rule does not depend on the order of (l1, l2, l3), so U3[i,j,k,(l1,l2,l3)] = U3[j,i,k,(l2,l1,l3)] =
+    U3[j,k,i,(l2,l3,l1)]: the symmetry the reference's contraction kernel assumes when it forms its gradient
+    from one stored value and the weights of the three permuted paths (symmetric_contraction_impl.cu:160-169)."""
     lof = np.asarray(L_OF_LM)
     paths = paths_nu3()
     U3 = np.zeros((16, 16, 16, len(paths)))
     for p, (l1, l2, l3) in enumerate(paths):
         t = real_wigner_3j(l1, l2, l3)
-        flat = t.ravel()
-        t = t * np.sign(flat[np.flatnonzero(flat)[0]])
+        t = t * np.sign(t[l1, l2, l3])  # the m = 0 entry of every index
         i0, j0, k0 = l1 * l1, l2 * l2, l3 * l3
         U3[i0 : i0 + 2 * l1 + 1, j0 : j0 + 2 * l2 + 1, k0 : k0 + 2 * l3 + 1, p] = t
     U2 = np.zeros((16, 16, 4))

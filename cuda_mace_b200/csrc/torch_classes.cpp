@@ -12,6 +12,7 @@
 // output and scratch allocation through the caching allocator, argument checks, the autograd Functions
 // (gradients for the float inputs only, as in the reference) and the current CUDA stream.
 #include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAFunctions.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/custom_class.h>
 #include <torch/script.h>
@@ -46,15 +47,30 @@ bool is_f64(const Tensor &t) {
 
 Tensor int32_contig(const Tensor &t) { return t.to(torch::kInt32).contiguous(); }
 
-Tensor status_tensor(const Tensor &like) {
+std::mutex &status_mutex() {
   static std::mutex m;
+  return m;
+}
+std::map<int, Tensor> &status_map() {
   static std::map<int, Tensor> per_device;
-  std::lock_guard<std::mutex> lock(m);
+  return per_device;
+}
+
+// int32[1] per device that kernels with bounded waits set when a wait gives up
+Tensor status_tensor(const Tensor &like) {
+  std::lock_guard<std::mutex> lock(status_mutex());
   const int dev = like.device().index();
+  auto &per_device = status_map();
   auto it = per_device.find(dev);
   if (it == per_device.end())
     it = per_device.emplace(dev, torch::zeros({1}, torch::dtype(torch::kInt32).device(like.device()))).first;
   return it->second;
+}
+
+Tensor status_peek(int dev) {
+  std::lock_guard<std::mutex> lock(status_mutex());
+  auto it = status_map().find(dev);
+  return it == status_map().end() ? Tensor() : it->second;
 }
 
 // ---- edge topology: receiver CSR and, for the backward, the sender-grouped edge order --------------------
@@ -165,21 +181,28 @@ class IMPAutograd : public torch::autograd::Function<IMPAutograd> {
 };
 
 // ---- Linear / ElementalLinear --------------------------------------------------------------------------
-// packed tensor-core image of a float32 weight (transposed copy), cached per storage and version
+// packed tensor-core image of a float32 weight (transposed copy).  An entry keeps the source tensor alive, so its
+// storage cannot be handed to another tensor of the same shape while the entry lives; the version counter catches
+// in-place edits.
+struct PackedEntry {
+  Tensor source, packed;
+};
+
 Tensor packed_weights(const Tensor &Bt) {
   static std::mutex m;
-  static std::map<std::tuple<void *, int64_t, int64_t>, Tensor> cache;
-  Tensor B3 = Bt.reshape({-1, Bt.size(-2), Bt.size(-1)}).contiguous();
-  const auto key = std::make_tuple(Bt.data_ptr(), (int64_t)Bt._version(), (int64_t)Bt.numel());
+  using Key = std::tuple<void *, int64_t, int, std::vector<int64_t>>;
+  static std::map<Key, PackedEntry> cache;
+  const Key key = std::make_tuple(Bt.data_ptr(), (int64_t)Bt._version(), (int)Bt.device().index(), Bt.sizes().vec());
   std::lock_guard<std::mutex> lock(m);
   auto it = cache.find(key);
-  if (it != cache.end()) return it->second;
+  if (it != cache.end()) return it->second.packed;
   if (cache.size() > 64) cache.clear();
+  Tensor B3 = Bt.reshape({-1, Bt.size(-2), Bt.size(-1)}).contiguous();
   const int nmat = (int)B3.size(0), N = (int)B3.size(1), K = (int)B3.size(2);
   Tensor packed = torch::empty({cmace_gemm_packed_floats(nmat, N, K)}, B3.options());
   check(cmace_gemm_pack_weights_f32(B3.data_ptr<float>(), nmat, N, K, packed.data_ptr<float>(), stream_of(B3)),
         "cmace_gemm_pack_weights_f32");
-  cache.emplace(key, packed);
+  cache.emplace(key, PackedEntry{Bt, packed});
   return packed;
 }
 
@@ -239,17 +262,24 @@ class LinearAutograd : public torch::autograd::Function<LinearAutograd> {
 // ---- symmetric contraction -----------------------------------------------------------------------------
 struct PlanHolder {
   cmace_symcon_plan *plan = nullptr;
+  std::vector<Tensor> tables;  // the tensors the plan was made from: kept so that their addresses stay theirs
   ~PlanHolder() {
     if (plan) cmace_symcon_plan_destroy(plan);
   }
 };
 
+// The caller has made X's device current: the plan's tables are allocated on the current device.
 std::shared_ptr<PlanHolder> plan_for(int64_t u3_max, const Tensor &U3_num, const Tensor &U3_idx, const Tensor &U3_val,
                                      const Tensor &U2_num, const Tensor &U2_idx, const Tensor &U2_val, int64_t w3,
-                                     int64_t w2, int64_t w1) {
+                                     int64_t w2, int64_t w1, int device) {
   static std::mutex m;
-  static std::map<std::tuple<void *, void *, void *, void *>, std::shared_ptr<PlanHolder>> cache;
-  const auto key = std::make_tuple(U3_idx.data_ptr(), U3_val.data_ptr(), U2_idx.data_ptr(), U2_val.data_ptr());
+  using Key = std::tuple<void *, void *, void *, void *, void *, void *, int64_t, int64_t, int64_t, int64_t, int,
+                         int64_t>;
+  static std::map<Key, std::shared_ptr<PlanHolder>> cache;
+  const int64_t versions = (int64_t)U3_idx._version() + (int64_t)U3_val._version() + (int64_t)U2_idx._version() +
+                           (int64_t)U2_val._version() + (int64_t)U3_num._version() + (int64_t)U2_num._version();
+  const Key key = std::make_tuple(U3_num.data_ptr(), U3_idx.data_ptr(), U3_val.data_ptr(), U2_num.data_ptr(),
+                                  U2_idx.data_ptr(), U2_val.data_ptr(), u3_max, w3, w2, w1, device, versions);
   std::lock_guard<std::mutex> lock(m);
   auto it = cache.find(key);
   if (it != cache.end()) return it->second;
@@ -261,6 +291,7 @@ std::shared_ptr<PlanHolder> plan_for(int64_t u3_max, const Tensor &U3_num, const
   Tensor i2 = U2_idx.detach().to(torch::kCPU, torch::kInt16).contiguous();
   Tensor v2 = U2_val.detach().to(torch::kCPU, torch::kFloat64).contiguous();
   auto holder = std::make_shared<PlanHolder>();
+  holder->tables = {U3_num, U3_idx, U3_val, U2_num, U2_idx, U2_val};
   check(cmace_symcon_plan_create((int)u3_max, n3.data_ptr<int16_t>(), i3.data_ptr<int32_t>(), v3.data_ptr<double>(),
                                  n2.data_ptr<int16_t>(), i2.data_ptr<int16_t>(), v2.data_ptr<double>(), (int)w3,
                                  (int)w2, (int)w1, &holder->plan),
@@ -406,6 +437,8 @@ class SplineAutograd : public torch::autograd::Function<SplineAutograd> {
 class InvariantMessagePassingTP : public torch::CustomClassHolder {
  public:
   Tensor forward(Tensor X, Tensor Y, Tensor radial, Tensor sender_list, Tensor receiver_list, int64_t nnodes) {
+    check_cuda(X, "X");
+    c10::cuda::CUDAGuard guard(X.device());
     return IMPAutograd::apply(X, Y, radial, sender_list, receiver_list, nnodes);
   }
   std::vector<Tensor> __getstate__() { return {}; }
@@ -418,11 +451,12 @@ class SymmetricContraction : public torch::CustomClassHolder {
                  Tensor U3_values, Tensor U2_num_nonzero, Tensor U2_indices, Tensor U2_values, Tensor U1_num_nonzero,
                  Tensor U1_index, Tensor W3, Tensor W2, Tensor W1, int64_t W3_size, int64_t W2_size, int64_t W1_size) {
     check_cuda(X, "X");
+    c10::cuda::CUDAGuard guard(X.device());
     (void)U1_num_nonzero;  // accepted for signature compatibility; the reference kernel does not read them either
     (void)U1_index;        // (symmetric_contraction_impl.cu:115-117)
     auto box = c10::make_intrusive<PlanBox>();
     box->holder = plan_for(U3_max_nonsparse, U3_num_nonzero, U3_indices, U3_values, U2_num_nonzero, U2_indices,
-                           U2_values, W3_size, W2_size, W1_size);
+                           U2_values, W3_size, W2_size, W1_size, (int)X.device().index());
     // the reference's buffers are [nlout, Z, w, C]; output irrep 0 is the one it contracts (impl.cu:64-76)
     auto first = [](const Tensor &w) { return (w.dim() == 4 ? w.select(0, 0) : w).contiguous(); };
     Tensor w3 = first(W3), w2 = first(W2), w1 = first(W1);
@@ -439,6 +473,7 @@ class Linear : public torch::CustomClassHolder {
  public:
   Tensor forward(Tensor X, Tensor W, Tensor W_T) {
     check_cuda(X, "X");
+    c10::cuda::CUDAGuard guard(X.device());
     Tensor none = torch::empty({0}, torch::dtype(torch::kInt32).device(X.device()));
     return LinearAutograd::apply(X, W, W_T, none, none, 1);
   }
@@ -453,6 +488,11 @@ class ElementalLinear : public torch::CustomClassHolder {
     check_cuda(X, "X");
     c10::cuda::CUDAGuard guard(X.device());
     const int64_t Z = one_hot_encoding.size(1), N = one_hot_encoding.size(0);
+    TORCH_CHECK(N == X.size(0) && W.dim() == 4 && W.size(0) == Z, "one_hot_encoding must be [nnodes, Z] with W [Z, 4, K, N]");
+    if (Z == 1) {  // a single-species model: every row uses W[0], no grouping needed
+      Tensor none = torch::empty({0}, torch::dtype(torch::kInt32).device(X.device()));
+      return LinearAutograd::apply(X, W, W_T, none, none, 1);
+    }
     Tensor elem = one_hot_encoding.argmax(1).to(torch::kInt32).contiguous();
     const int64_t nbytes = cmace_sender_order_workspace_bytes(N);
     Tensor ws = torch::empty({std::max<int64_t>(nbytes, 1)}, elem.options().dtype(torch::kUInt8));
@@ -469,7 +509,11 @@ class ElementalLinear : public torch::CustomClassHolder {
 
 class SphericalHarmonics : public torch::CustomClassHolder {
  public:
-  Tensor forward(Tensor xyz) { return SphAutograd::apply(xyz); }
+  Tensor forward(Tensor xyz) {
+    check_cuda(xyz, "xyz");
+    c10::cuda::CUDAGuard guard(xyz.device());
+    return SphAutograd::apply(xyz);
+  }
   std::vector<Tensor> __getstate__() { return {}; }
   void __setstate__(const std::vector<Tensor> &) {}
 };
@@ -477,51 +521,91 @@ class SphericalHarmonics : public torch::CustomClassHolder {
 class CubicSpline : public torch::CustomClassHolder {
  public:
   Tensor forward(Tensor r, Tensor r_knots, Tensor coeffs, double r_width, double r_max) {
+    check_cuda(r, "r");
+    c10::cuda::CUDAGuard guard(r.device());
     return SplineAutograd::apply(r, r_knots, coeffs, r_width, r_max);
   }
   std::vector<Tensor> __getstate__() { return {}; }
   void __setstate__(const std::vector<Tensor> &) {}
 };
 
-#define CMACE_REGISTER(NS, CLS)                                                                        \
-  TORCH_LIBRARY(NS, m) {                                                                               \
-    m.class_<CLS>(#CLS)                                                                                \
-        .def(torch::init<>())                                                                          \
-        .def("forward", &CLS::forward)                                                                 \
-        .def_pickle([](const c10::intrusive_ptr<CLS> &self) -> std::vector<Tensor> { return self->__getstate__(); }, \
-                    [](const std::vector<Tensor> &state) -> c10::intrusive_ptr<CLS> {                  \
-                      auto obj = c10::make_intrusive<CLS>();                                           \
-                      obj->__setstate__(state);                                                        \
-                      return obj;                                                                      \
-                    });                                                                                \
-  }
+// Argument names are the reference's (src/invariant_message_passing.cpp:78 - "raidal" is its spelling -,
+// src/linear.cpp:110,:126, src/symmetric_contraction.cpp:129-146), so keyword calls written against it work here;
+// SphericalHarmonics and CubicSpline are registered without names there too (src/spherical_harmonics.cpp:57,
+// src/cubic_spline.cpp:58).
+#define CMACE_PICKLE(CLS)                                                                                         \
+  def_pickle([](const c10::intrusive_ptr<CLS> &self) -> std::vector<Tensor> { return self->__getstate__(); },     \
+             [](const std::vector<Tensor> &state) -> c10::intrusive_ptr<CLS> {                                    \
+               auto obj = c10::make_intrusive<CLS>();                                                             \
+               obj->__setstate__(state);                                                                          \
+               return obj;                                                                                        \
+             })
 
-CMACE_REGISTER(inv_message_passing, InvariantMessagePassingTP)
-CMACE_REGISTER(symm_contract, SymmetricContraction)
-CMACE_REGISTER(spherical_harmonics, SphericalHarmonics)
-CMACE_REGISTER(cubic_spline, CubicSpline)
+TORCH_LIBRARY(inv_message_passing, m) {
+  m.class_<InvariantMessagePassingTP>("InvariantMessagePassingTP")
+      .def(torch::init<>(), "", {})
+      .def("forward", &InvariantMessagePassingTP::forward, "",
+           {torch::arg("X"), torch::arg("Y"), torch::arg("raidal"), torch::arg("sender_list"),
+            torch::arg("receiver_list"), torch::arg("nnodes")})
+      .CMACE_PICKLE(InvariantMessagePassingTP);
+}
+
+TORCH_LIBRARY(symm_contract, m) {
+  m.class_<SymmetricContraction>("SymmetricContraction")
+      .def(torch::init<>(), "", {})
+      .def("forward", &SymmetricContraction::forward, "",
+           {torch::arg("X"), torch::arg("atom_types"), torch::arg("U3_max_nonsparse"), torch::arg("U3_num_nonzero"),
+            torch::arg("U3_indices"), torch::arg("U3_values"), torch::arg("U2_num_nonzero"), torch::arg("U2_indices"),
+            torch::arg("U2_values"), torch::arg("U1_num_nonzero"), torch::arg("U1_index"), torch::arg("W3"),
+            torch::arg("W2"), torch::arg("W1"), torch::arg("W3_size"), torch::arg("W2_size"), torch::arg("W1_size")})
+      .CMACE_PICKLE(SymmetricContraction);
+}
+
+TORCH_LIBRARY(spherical_harmonics, m) {
+  m.class_<SphericalHarmonics>("SphericalHarmonics")
+      .def(torch::init<>())
+      .def("forward", &SphericalHarmonics::forward)
+      .CMACE_PICKLE(SphericalHarmonics);
+}
+
+TORCH_LIBRARY(cubic_spline, m) {
+  m.class_<CubicSpline>("CubicSpline")
+      .def(torch::init<>(), "", {})
+      .def("forward", &CubicSpline::forward)
+      .CMACE_PICKLE(CubicSpline);
+}
 
 TORCH_LIBRARY(linear_wmma, m) {
   m.class_<Linear>("Linear")
-      .def(torch::init<>())
-      .def("forward", &Linear::forward)
-      .def_pickle([](const c10::intrusive_ptr<Linear> &self) -> std::vector<Tensor> { return self->__getstate__(); },
-                  [](const std::vector<Tensor> &state) -> c10::intrusive_ptr<Linear> {
-                    auto obj = c10::make_intrusive<Linear>();
-                    obj->__setstate__(state);
-                    return obj;
-                  });
+      .def(torch::init<>(), "", {})
+      .def("forward", &Linear::forward, "", {torch::arg("X"), torch::arg("W"), torch::arg("W_T")})
+      .CMACE_PICKLE(Linear);
   m.class_<ElementalLinear>("ElementalLinear")
-      .def(torch::init<>())
-      .def("forward", &ElementalLinear::forward)
-      .def_pickle(
-          [](const c10::intrusive_ptr<ElementalLinear> &self) -> std::vector<Tensor> { return self->__getstate__(); },
-          [](const std::vector<Tensor> &state) -> c10::intrusive_ptr<ElementalLinear> {
-            auto obj = c10::make_intrusive<ElementalLinear>();
-            obj->__setstate__(state);
-            return obj;
-          });
+      .def(torch::init<>(), "", {})
+      .def("forward", &ElementalLinear::forward, "",
+           {torch::arg("X"), torch::arg("W"), torch::arg("W_T"), torch::arg("one_hot_encoding")})
+      .CMACE_PICKLE(ElementalLinear);
 }
 
-// internal holder of a contraction plan inside an autograd node
-TORCH_LIBRARY(cmace_b200_internal, m) { m.class_<PlanBox>("PlanBox").def(torch::init<>()); }
+// Reads and clears what the kernels' bounded waits report (synchronises the device).  Returns 0 when every wait
+// since the last call completed; otherwise a non-zero code: the outputs of the call that gave up are incomplete and
+// must be discarded.  Python: torch.ops.cmace_b200_internal.check_status().
+int64_t check_status_op() {
+  int64_t code = cmace_imp_staged_stalled() != 0 ? 1 : 0;
+  for (int dev = 0; dev < (int)c10::cuda::device_count(); ++dev) {
+    Tensor t = status_peek(dev);
+    if (!t.defined()) continue;
+    const int64_t v = t.item<int32_t>();
+    if (v != 0) {
+      t.zero_();
+      code = code ? code : 2 + v;
+    }
+  }
+  return code;
+}
+
+// internal holder of a contraction plan inside an autograd node, and the status check
+TORCH_LIBRARY(cmace_b200_internal, m) {
+  m.class_<PlanBox>("PlanBox").def(torch::init<>());
+  m.def("check_status() -> int", &check_status_op);
+}

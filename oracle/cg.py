@@ -13,10 +13,19 @@ for (l_i, l_j, l_k) = path p, which is non-zero exactly when the triple obeys th
 triangle rule and l1+l2+l3 is even.  The integral is evaluated exactly with a
 Gauss-Legendre x uniform-phi quadrature of this directory's own harmonics, so
 the tensors are consistent with the harmonics' sign and axis conventions by
-construction.  Each path is scaled to unit Frobenius norm with its first
-non-zero entry positive.  Upstream's tensors may differ from these by one scale
-factor (and sign) per path, which the learnable weights absorb: PARITY
-UNPINNED against upstream for the per-path scale.
+construction.  Each path is scaled to unit Frobenius norm, with the sign that
+makes its m1 = m2 = m3 = 0 entry positive (the Gaunt integral of three m = 0
+harmonics is a square, so this is the integral's own sign).  That rule does not
+depend on the order of (l1, l2, l3), which keeps the tensor symmetric under a
+simultaneous permutation of its indices and of the path's l's:
+U3[i,j,k,(l1,l2,l3)] = U3[j,i,k,(l2,l1,l3)] = U3[j,k,i,(l2,l3,l1)].  The
+reference's contraction kernel RELIES on that symmetry for its gradient
+(cuda_mace/cuda/src/symmetric_contraction_impl.cu:160-169 sums the weights of
+the three permuted paths against one stored value), so tables without it give
+the reference a wrong gradient; upstream's U_matrix_real must have it too.
+Upstream's tensors may still differ from these by one scale factor (and sign)
+per symmetric class of paths, which the learnable weights absorb: PARITY
+UNPINNED against upstream for that scale.
 
 Shapes follow cuda_mace/ops/symmetric_contraction.py:100-176:
 U3 [16,16,16,P3], U2 [16,16,P2], U1 [16,P1] with P3=23, P2=4, P1=1.
@@ -72,8 +81,7 @@ def u_matrices(dtype=torch.float64):
         )
         t = np.where(mask, gaunt, 0.0)
         t = t / np.sqrt((t * t).sum())
-        first = t.ravel()[np.flatnonzero(t.ravel())[0]]
-        U3[..., p] = t * np.sign(first)
+        U3[..., p] = t * np.sign(t[l1 * l1 + l1, l2 * l2 + l2, l3 * l3 + l3])  # m = 0 sits at index l^2 + l
     U2 = np.zeros((16, 16, 4))
     for l in range(4):
         idx = np.flatnonzero(lof == l)

@@ -95,6 +95,45 @@ def symmetric_contraction_chunked(X, atom_types, U3, U2, U1, W3, W2, W1, chunk=2
     return torch.cat(outs, dim=0)
 
 
+def symmetric_contraction_sparse_tables(X, atom_types, tables, W3, W2, W1):
+    """The reference kernel's own loop over the SPARSE tables, value and gradient, restated statement by statement
+    from symmetric_contraction_kernel<scalar_t, true> (cuda_mace/cuda/src/symmetric_contraction_impl.cu:108-180).
+
+    `tables` = pack_sparse_u(...).  Returns (out [N, C], grad [N, 16, C]) where grad is what the kernel stores as
+    d out / d x_i: per (i, j) and stored non-zero k it adds u3 * (W3[p1] + W3[p2] + W3[p3]) * x_k * x_j with the
+    three path indices unpacked from one int32 (:147-169), i.e. it assumes that the value stored for
+    U3[i, j, k, p1] is also the value of U3[j, i, k, p2] and of U3[j, k, i, p3].  That holds for tables that are
+    symmetric under a simultaneous permutation of indices and path (see oracle/cg.py); for other tables the forward
+    value is still right and this gradient is not the derivative.  Used to pin the restatement of that rule
+    against the gradient the reference's kernel produced on the GPU."""
+    maxnz, n3, idx3, val3, n2, idx2, val2, _, _ = tables
+    z = atom_types.long()
+    N, _, C = X.shape
+    W3n, W2n, W1n = W3[z], W2[z], W1[z]  # [N, P, C]
+    zero = torch.zeros(N, C, dtype=X.dtype)
+    out = zero.clone()
+    grad = torch.zeros_like(X)
+    for i in range(16):
+        uw1 = W1n[:, 0] if i == 0 else zero
+        output_2 = zero.clone()
+        deriv1 = uw1.clone()
+        for j in range(16):
+            uw2 = float(val2[i, j]) * W2n[:, int(idx2[i, j])] if int(n2[i, j]) > 0 else zero
+            output_3 = zero.clone()
+            deriv_1_j = uw2.clone()
+            for k in range(int(n3[i, j])):
+                packed = int(idx3[k, i, j])
+                p1, kdx, p3, p2 = packed & 0xFF, (packed >> 8) & 0xFF, (packed >> 16) & 0xFF, (packed >> 24) & 0xFF
+                u3 = float(val3[k, i, j])
+                output_3 = output_3 + u3 * W3n[:, p1] * X[:, kdx]
+                deriv_1_j = deriv_1_j + u3 * (W3n[:, p1] + W3n[:, p2] + W3n[:, p3]) * X[:, kdx]
+            output_2 = output_2 + (output_3 + uw2) * X[:, j]
+            deriv1 = deriv1 + (uw2 + deriv_1_j) * X[:, j]
+        out = out + (output_2 + uw1) * X[:, i]
+        grad[:, i] = deriv1
+    return out, grad
+
+
 def pack_sparse_u(U3, U2, U1):
     """Packs dense U tensors into the reference's sparse tables.
 

@@ -139,3 +139,142 @@ def test_contraction_harmonics_and_spline_classes(classes, U):
     out = classes.cubic_spline.CubicSpline().forward(rg, d(knots), d(coeffs), h, 5.0)
     (out ** 2).sum().backward()
     assert rel_err(out, rref) < 1e-10 and rel_err(rg.grad, ro.grad) < 1e-10
+
+
+def test_schemas_equal_the_reference_library(classes):
+    """Argument names, types and order of forward / __getstate__ / __setstate__ are those the reference's own
+    library registers (tests/golden/reference_schemas.json, written by tests/golden/make_reference_schemas.py from
+    the library built out of the reference's sources), so positional AND keyword calls written against it work."""
+    import json
+    import os
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_schemas.json")) as f:
+        ref = json.load(f)
+    assert sorted(ref) == sorted(f"{ns}.{name}" for ns, name in CLASSES)
+    for ns, name in CLASSES:
+        obj = getattr(getattr(classes, ns), name)()
+        for method, schema in ref[f"{ns}.{name}"].items():
+            assert str(obj._get_method(method).schema) == schema, (ns, name, method)
+
+
+REFERENCE_ROOT = "/root/reference"
+
+
+def _load_reference_python(rel_path, name):
+    """Loads one of the reference's Python operator modules by file path, with empty stand-ins for the mace / e3nn
+    imports at its top (never called here), as tests/golden/make_reference_pins.py does."""
+    import importlib.util
+    import os
+    import sys
+    import types
+
+    for mod in ("e3nn", "mace", "mace.tools", "mace.tools.cg", "mace.modules", "mace.modules.symmetric_contraction"):
+        sys.modules.setdefault(mod, types.ModuleType(mod))
+    sys.modules["e3nn"].o3 = types.SimpleNamespace(Linear=object)
+    sys.modules["mace.tools.cg"].U_matrix_real = None
+    sys.modules["mace.modules.symmetric_contraction"].SymmetricContraction = object
+    spec = importlib.util.spec_from_file_location(name, os.path.join(REFERENCE_ROOT, rel_path))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def test_reference_python_layer_binds_to_this_library(classes):
+    """The drop-in seen from the reference's side: its own Python operator modules (cuda_mace/ops/*.py), loaded by
+    file path, find every handle they ask for in THIS library (ops/__init__.py:7-15 only loads a library; the
+    modules then call torch.classes.<ns>.<Class>()), and the argument lists their forward methods pass
+    (ops/invariant_message_passing.py:20-22, ops/linear.py:54,:108, ops/symmetric_contraction.py:68-86,
+    ops/cubic_spline.py:35-37) bind to the registered schemas.  Runs where the reference checkout is (no GPU
+    needed); the numerical side of the same classes is test_*_class above."""
+    import inspect
+    import os
+
+    if not os.path.isdir(os.path.join(REFERENCE_ROOT, "cuda_mace", "ops")):
+        pytest.skip("no reference checkout on this machine")
+    imp = _load_reference_python("cuda_mace/ops/invariant_message_passing.py", "ref_ops_imp")
+    mod = imp.InvariantMessagePassingTP()          # constructs torch.classes.inv_message_passing....()
+    assert "inv_message_passing.InvariantMessagePassingTP" in str(mod.cuda_obj._type())
+    lin = _load_reference_python("cuda_mace/ops/linear.py", "ref_ops_linear")
+    spl = _load_reference_python("cuda_mace/ops/cubic_spline.py", "ref_ops_spline")
+    sym = _load_reference_python("cuda_mace/ops/symmetric_contraction.py", "ref_ops_symcon")
+    # number of arguments each reference forward hands to cuda_obj.forward == arguments of the registered schema
+    expected = {(imp.InvariantMessagePassingTP, "inv_message_passing", "InvariantMessagePassingTP"): 6,
+                (lin.Linear, "linear_wmma", "Linear"): 3, (lin.ElementalLinear, "linear_wmma", "ElementalLinear"): 4,
+                (spl.CubicSpline, "cubic_spline", "CubicSpline"): 5,
+                (sym.SymmetricContraction, "symm_contract", "SymmetricContraction"): 17}
+    for (cls, ns, name), nargs in expected.items():
+        src = inspect.getsource(cls.forward)
+        assert "self.cuda_obj.forward(" in src
+        schema = getattr(getattr(classes, ns), name)()._get_method("forward").schema
+        assert len(schema.arguments) - 1 == nargs, (name, schema)
+    # the spline module builds its coefficient table with plain torch: run it and check it is what this
+    # project's packing produces (the table is an argument of the class's forward)
+    from cuda_mace_b200 import ops
+
+    knots = torch.linspace(1e-12, 6.0, 17, dtype=torch.float64)
+    vals = torch.sin(knots)[:, None] * torch.arange(1, 5, dtype=torch.float64)
+    h = float(knots[1] - knots[0])
+    theirs = spl.CubicSpline.cubic_spline_coefficients(None, knots, vals, h)
+    assert rel_err(ops.cubic_spline_coefficients(knots, vals, h), theirs) < 1e-12
+
+
+@pytest.mark.gpu
+def test_weight_caches_do_not_outlive_their_tensors(classes):
+    """Two temporary weights of the same shape, the first freed before the second is made: the caching allocator
+    may hand the second the first one's address, and the packed-image cache must not answer with the first one's
+    image."""
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(9)
+    N, K = 64, 64
+    X = torch.randn(N, 16, K, generator=g)
+    lin = classes.linear_wmma.Linear()
+    seen = set()
+    with torch.no_grad():
+        for trial in range(4):
+            W = torch.randn(4, K, K, generator=g)
+            Wd = W.cuda()
+            WTd = W.transpose(-1, -2).contiguous().cuda()
+            seen.add((Wd.data_ptr(), WTd.data_ptr()))
+            out = lin.forward(X.cuda(), Wd, WTd)
+            assert rel_err(out, oops.linear(X.double(), W.double())) < 1e-5, trial
+            del Wd, WTd, out
+    assert len(seen) < 4, "the allocator never reused an address, so the test did not exercise the cache key"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+def test_elemental_linear_class_single_species(classes, dtype):
+    """Z = 1 (the reference's own test cells are single-species diamond): every node uses W[0]."""
+    from oracle import ops as oops
+
+    tol = 1e-10 if dtype == torch.float64 else 1e-4
+    g = torch.Generator().manual_seed(12)
+    N, K = 50, 64
+    X = torch.randn(N, 16, K, generator=g, dtype=torch.float64).to(dtype)
+    WZ = torch.randn(1, 4, K, K, generator=g, dtype=torch.float64).to(dtype)
+    one_hot = torch.ones(N, 1, dtype=dtype)
+    Xo = X.double().clone().requires_grad_(True)
+    ref = oops.elemental_linear(Xo, WZ.double(), one_hot.double())
+    (ref ** 2).sum().backward()
+    Xg = X.cuda().requires_grad_(True)
+    out = classes.linear_wmma.ElementalLinear().forward(Xg, WZ.cuda(), WZ.transpose(-1, -2).contiguous().cuda(),
+                                                        one_hot.cuda())
+    (out ** 2).sum().backward()
+    assert rel_err(out, ref) < tol and rel_err(Xg.grad, Xo.grad) < tol
+
+
+@pytest.mark.gpu
+def test_keyword_call_and_status_op(classes):
+    """A keyword call with the reference's argument names (including its spelling "raidal"), and the status
+    operator that reports kernels whose bounded waits gave up (0 = none did)."""
+    send, recv = random_graph(4, 30, 6)
+    E = send.numel()
+    g = torch.Generator().manual_seed(2)
+    X, Y, R = torch.randn(30, 32, generator=g).cuda(), torch.randn(16, E, generator=g).cuda(), \
+        torch.randn(E, 4, 32, generator=g).cuda()
+    tp = classes.inv_message_passing.InvariantMessagePassingTP()
+    a = tp.forward(X, Y, R, send.cuda(), recv.cuda(), 30)
+    b = tp.forward(X=X, Y=Y, raidal=R, sender_list=send.cuda(), receiver_list=recv.cuda(), nnodes=30)
+    assert torch.equal(a, b)
+    assert torch.ops.cmace_b200_internal.check_status() == 0

@@ -41,6 +41,9 @@ KEYS = {
     "elinear": (("out", "out"), ("grad_X", "grad")),
 }
 DTYPES = {"f32": torch.float32, "f64": torch.float64}
+# The reference keeps the U values in float32 tables whatever the dtype of X (const float *U3_values,
+# symmetric_contraction_impl.cu:11,:14), so its float64 contraction carries float32 rounding of the couplings.
+LOOSER = {("symcon", "f64"): 1e-6}
 
 
 def _ops_with_dtype(ref):
@@ -56,7 +59,8 @@ def _compare(got, want, op, tag, what):
         a = torch.as_tensor(np.asarray(got[name])) if not torch.is_tensor(got[name]) else got[name]
         b = torch.as_tensor(np.asarray(want[name])) if not torch.is_tensor(want[name]) else want[name]
         err = rel_err(a, b)
-        assert err < TOL[DTYPES[tag]][kind], f"{what}: {op}.{tag}.{name} differs by {err:.3e}"
+        tol = LOOSER.get((op, tag), TOL[DTYPES[tag]][kind])
+        assert err < tol, f"{what}: {op}.{tag}.{name} differs by {err:.3e}"
 
 
 @pytest.fixture(scope="module")

@@ -2,7 +2,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype f32|f64] [--atoms-per-gpu A]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
-    python bench.py --impl reference ...        # CPU restatement of the path on the host cores
+    python bench.py --impl reference ...        # the reference's own kernels (same GPU) on a bounded sample of the
+                                                # workload; the CPU restatement on the host cores beside it
 
 Workload: the weak-scaled slab configuration: 64 000 atoms per GPU (H:C:N:O = 50:30:10:10,
 0.1 atoms/A^3, 0.9 A minimum distance, 80 x 80 A cross-section, periodic), 128-channel 2-layer
@@ -11,10 +12,19 @@ random-init weights.  With N GPUs the box is N times longer and is cut into N sl
 halos; ghost node features are exchanged once per evaluation and ghost gradients are sent back.
 
 One step = one energy+force evaluation of all atoms.  `value` is measured with every input
-resident on the device; `e2e` goes through EnergyForceEvaluator.evaluate_host with pinned host
+resident on the device and nothing but the step inside the timed region (the per-kernel timings of
+the `kernels` table come from a separate pass that brackets every entry-point call with CUDA events); `e2e` goes through EnergyForceEvaluator.evaluate_host with pinned host
 buffers, so host->device copies of positions / species / edge list / shifts and the device->host
 copy of energy and forces are inside its timed region.  The working set of a step (several GB) is
 far larger than the 126 MB L2, so no explicit L2 flush is needed between steps.
+
+At one GPU the line also carries
+  `secondary`          the other configurations of the spec on the same device: the 3 000-atom H/O box in
+                       float32 (eager and replayed as a CUDA graph) and float64, and the slab in float64;
+  `reference_kernels`  the reference library's own kernels (oracle/_ref, run in a child process because both
+                       libraries register the same TorchScript class names) next to this library's on the
+                       isolated-operator shapes, and its whole 3 000-atom step;
+  `cpu_baseline`       the float64 CPU restatement on a bounded sample.
 """
 import argparse
 import json
@@ -47,6 +57,11 @@ def parse():
                          "single-GPU 3 000-atom H/O box of the spec (1 GPU only)")
     ap.add_argument("--cpu-sample-atoms", type=int, default=400)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the other configurations (profiling runs)")
+    ap.add_argument("--no-reference-kernels", action="store_true", help="skip the reference library's kernels")
+    ap.add_argument("--reference-sample-atoms", type=int, default=8000,
+                    help="--impl reference: atoms of the sample the reference's kernels run on (they index an "
+                         "N x N table with 32-bit offsets, so at most 8192)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--radial", default="exact", choices=["exact", "spline"],
                     help="exact: Bessel basis + multilayer perceptron per edge (the headline); spline: the reference's "
@@ -63,7 +78,7 @@ def peaks():
     if os.path.isfile(path):
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s)"
 
 
 class ClockSampler:
@@ -188,6 +203,137 @@ def cpu_reference_run(args, steps, warmup):
                       f"float64 torch restatement (oracle/), {steps} timed call(s) of {dt:.2f} s"}, dt
 
 
+def cpu_named_config(name, steps):
+    """The CPU restatement on a named configuration of the spec at its full size: "cfg0" (192 atoms, 64 channels,
+    4 species) or "water3000" (3 000 atoms, 128 channels).  Returns atoms, seconds per call, atom-steps/s."""
+    from cuda_mace_b200 import cg, systems
+    from oracle import model as omodel
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    sysd = systems.make_system(name)
+    pos, species = sysd["positions"], sysd["species"]
+    ei, sh = systems.neighbor_list(pos, sysd["box"], (True, True, True), R_MAX)
+    params = systems.init_params(sysd["channels"], sysd["n_species"], 0 if name == "cfg0" else 1)
+    U = cg.u_matrices()
+    attrs = systems.one_hot(species, sysd["n_species"])
+    tpos, tei, tsh = torch.from_numpy(pos), torch.from_numpy(ei), torch.from_numpy(sh)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        omodel.energy_and_forces(params, U, tpos, attrs, tei, tsh)
+    dt = (time.perf_counter() - t0) / steps
+    n = pos.shape[0]
+    return {"config": name, "atoms": n, "edges": int(ei.shape[1]), "channels": sysd["channels"], "dtype": "f64",
+            "calls": steps, "s_per_call": dt, "atom_steps_per_s": n / dt, "cores": torch.get_num_threads()}
+
+
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libcuda_mace.so")
+
+
+def run_reference_child(mode_args, timeout=600):
+    """python -m oracle.ref_run ... in a child process; returns the parsed JSON it wrote, or {"unavailable": why}."""
+    if not os.path.isfile(REF_LIB):
+        return {"unavailable": "oracle/_ref/libcuda_mace.so is not built (python -m oracle.build_ref needs the "
+                               "reference's sources)"}
+    fd, out = tempfile.mkstemp(suffix=".json")
+    os.close(fd)
+    try:
+        r = subprocess.run([sys.executable, "-m", "oracle.ref_run"] + mode_args + ["--out", out], cwd=ROOT,
+                           capture_output=True, text=True, timeout=timeout)
+        if r.returncode != 0:
+            return {"unavailable": "the reference run failed: " + (r.stderr.strip().splitlines() or ["?"])[-1][:300]}
+        with open(out) as f:
+            return json.load(f)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"the reference run did not finish in {timeout} s"}
+    finally:
+        if os.path.exists(out):
+            os.unlink(out)
+
+
+def reference_kernels_block(iters):
+    """The reference library's kernels and this library's on the same isolated-operator shapes, on this GPU."""
+    from cuda_mace_b200 import opbench
+
+    ref = run_reference_child(["bench", "--iters", str(iters), "--warmup", "10"])
+    if isinstance(ref, dict):
+        return ref
+    dev = torch.device("cuda")
+    opbench.RECORDS.clear()
+    opbench.bench_symcon(torch.float32, iters, dev)
+    opbench.bench_imp(torch.float32, iters, dev, graph="symmetric")
+    opbench.bench_linear(torch.float32, iters, dev)
+    opbench.bench_edge(torch.float32, iters, dev)
+    def key(r):
+        c = r["case"]
+        stem = c.split(" forward")[0].split(" backward")[0]
+        which = " forward+backward" if "forward+backward" in c else " forward" if " forward" in c else \
+            " backward" if " backward" in c else ""
+        return r["op"], stem + which
+
+    ours = {key(r): r for r in opbench.RECORDS}
+    rows = []
+    for r in ref:
+        row = {"op": r["op"], "case": r["case"], "reference_ms": r["ms"]}
+        if "atom_steps_per_s" in r:
+            row["reference_atom_steps_per_s"] = r["atom_steps_per_s"]
+        # "with derivatives" (reference stores them in the forward) pairs with this library's plain forward
+        if "no derivatives" in r["case"]:
+            rows.append(row)
+            continue
+        mine = ours.get(key(r))
+        if mine is not None:
+            row["ours_ms"] = mine["ms"]
+            row["reference_over_ours"] = round(r["ms"] / mine["ms"], 2)
+        rows.append(row)
+    return {"protocol": f"10 warm-up + {iters} timed calls, CUDA events, float32, identical shapes and edge lists "
+                        "(symmetrised random graph: the only kind the reference accepts)",
+            "reference_library": "oracle/_ref/libcuda_mace.so, built from the reference's sources by oracle/build_ref.py, "
+                                 "kernels compiled by NVRTC for this GPU at first launch",
+            "rows": rows}
+
+
+def secondary_block(args, dev, sysd_slab, dom_slab, steps):
+    """The other configurations of the spec on this GPU: device-resident ms per step and atom-steps/s."""
+    from cuda_mace_b200 import cg, domain, evaluator, model, systems
+
+    out = {}
+    U = cg.u_matrices()
+
+    def run(name, sysd, dom, dtype, graph):
+        params = systems.init_params(128, sysd["n_species"], 1)
+        net = model.InvariantMACE(params, U, dtype=dtype, device=dev)
+        ev = evaluator.EnergyForceEvaluator(net, dom, dev)
+        pos = ev.load_domain()
+        if graph:
+            ev.capture(pos)
+        for _ in range(3):
+            ev(pos)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            energy, forces = ev(pos)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / steps
+        n = dom.n_owned
+        out[name] = {"atoms": n, "edges": int(dom.edge_index.shape[1]), "dtype": "f32" if dtype == torch.float32 else "f64",
+                     "cuda_graph": bool(graph), "steps": steps, "ms_per_step": ms, "atom_steps_per_s": n / (ms * 1e-3),
+                     "energy": float(energy)}
+        del ev, net
+        torch.cuda.empty_cache()
+
+    w = systems.make_system("water3000")
+    wdom = domain.partition_slabs(w["positions"], w["species"], w["box"], 1, R_MAX, 0)
+    run("water3000_f32", w, wdom, torch.float32, False)
+    run("water3000_f32_graph", w, wdom, torch.float32, True)
+    run("water3000_f64", w, wdom, torch.float64, False)
+    run("water3000_f64_graph", w, wdom, torch.float64, True)
+    if args.dtype == "f32" and args.workload == "slab":
+        run("slab_f64", sysd_slab, dom_slab, torch.float64, False)
+    return out
+
+
 def main():
     args = parse()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -203,19 +349,41 @@ def main():
                     f"2-layer invariant MACE, r_max {R_MAX} A, energy+forces")
 
     if args.impl == "reference":
-        # the reference has no CPU implementation of its own; the float64 CPU restatement stands in
+        # Rank 0 alone.  The reference is a GPU library without a CPU path, so the arm times ITS OWN KERNELS on this
+        # GPU: the energy+force step re-assembled from its operator classes (oracle/ref_model.py) on a sample of the
+        # workload (same density, species mix and 128-channel model) that its N x N reverse-edge table and 32-bit
+        # offsets can hold; `--steps` / `--warmup` are honoured.  The float64 CPU restatement is timed beside it
+        # (`cpu_baseline`, bounded sample) together with two configurations of the spec at their full size.
         if rank != 0:
             return
-        steps = max(1, min(args.steps, 3))
-        base, dt = cpu_reference_run(args, steps, 1 if args.warmup > 0 else 0)
+        warmup = max(args.warmup, 3)
+        n_ref = min(args.reference_sample_atoms, 8192)
+        ref = run_reference_child(["step", "--atoms", str(n_ref), "--channels", "128", "--species", "4",
+                                   "--iters", str(args.steps), "--warmup", str(warmup)])
+        cpu_steps = max(1, min(args.steps, 3))
+        base, dt = cpu_reference_run(args, cpu_steps, 1)
+        cpu_configs = [cpu_named_config("cfg0", max(1, min(args.steps, 10))), cpu_named_config("water3000", 1)]
+        if "unavailable" in ref:
+            value, ms, dtype, kind = base["value"], dt * 1e3, "f64", "port"
+            sample, steps, launches = base["sample"], cpu_steps, 0
+        else:
+            value, ms, dtype, kind = ref["atom_steps_per_s"], ref["ms_per_step"], "f32", "reference"
+            sample = (f"{ref['atoms']} atoms ({ref['edges']} edges) of the same density, species mix and 128-channel "
+                      "model in a periodic cube; the reference's own kernels on this GPU (float32, 256-knot spline, "
+                      "its TorchScript classes from oracle/_ref/libcuda_mace.so driven by oracle/ref_model.py), "
+                      "inputs resident on the device")
+            steps, launches = ref["steps"], None
         line = {
-            "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "atom-steps/s",
-            "n_gpus": args.gpus, "steps": steps, "warmup": 1 if args.warmup > 0 else 0, "ms_per_step": dt * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": {"workload": workload, "sample": base["sample"]},
+            "impl": "reference", "metric": METRIC, "value": value, "unit": "atom-steps/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": workload, "sample": sample},
+            "reference_kind": kind,
+            "reference_gpu_step": ref,
             "cpu_baseline": base,
-            "e2e": {"value": base["value"], "unit": "atom-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0,
+            "cpu_configs": cpu_configs,
+            "e2e": {"value": value, "unit": "atom-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": launches,
         }
         print(json.dumps(line))
         return
@@ -270,7 +438,6 @@ def main():
     if rank == 0:
         sampler.start()
     launches0 = _abi.launch_count
-    _abi.start_timing()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0.record()
@@ -278,7 +445,6 @@ def main():
         energy, forces = ev(pos)
     t1.record()
     barrier()
-    kernel_ms = _abi.stop_timing()
     launches = _abi.launch_count - launches0
     clocks = sampler.stop() if rank == 0 else None
     ms = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
@@ -286,6 +452,22 @@ def main():
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(ms) / args.steps
     value = n_total / (ms_per_step * 1e-3)
+    if args.graph:
+        launches = None   # a replayed graph launches the recorded kernels without passing through the binding
+
+    # ---- per-kernel pass: the same steps again with CUDA events around every entry-point call -------
+    kernel_steps = 0 if args.graph else min(args.steps, 5)
+    kernel_ms, bracketed_ms = {}, None
+    if kernel_steps:
+        _abi.start_timing()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(kernel_steps):
+            ev(pos)
+        k1.record()
+        kernel_ms = _abi.stop_timing()
+        bracketed_ms = k0.elapsed_time(k1) / kernel_steps
+    barrier()
 
     # ---- end-to-end timing with host buffers -----------------------------------------------------
     e2e_value, h2d, d2h = None, 0, 0
@@ -326,8 +508,8 @@ def main():
     for name, (calls, tot) in sorted(kernel_ms.items()):
         b = algorithmic_bytes(name, s_bytes, N, Ns, E, 128, sysd["n_species"])
         avg = tot / calls
-        per_kernel[name] = {"calls_per_step": calls / args.steps, "avg_ms": avg,
-                            "share_of_step": tot / (ms_per_step * args.steps),
+        per_kernel[name] = {"calls_per_step": calls / kernel_steps, "avg_ms": avg,
+                            "share_of_step": tot / (bracketed_ms * kernel_steps),
                             "achieved_gbs": (b / (avg * 1e-3) / 1e9) if b else None}
         if b and tot > top_ms:
             top, top_ms = name, tot
@@ -353,6 +535,7 @@ def main():
                    "energy": float(energy), "max_abs_force": float(forces.abs().max())},
         "roofline": roofline,
         "kernels": per_kernel,
+        "kernels_pass": {"steps": kernel_steps, "ms_per_step_with_events": bracketed_ms},
         "e2e": {"value": e2e_value, "unit": "atom-steps/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "clocks": clocks,
@@ -361,6 +544,13 @@ def main():
         line["config"]["radial"] = f"cubic spline table, {args.spline_knots} knots (not the headline configuration)"
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"], _ = cpu_reference_run(args, 2, 1)
+    if world == 1 and not args.no_secondary:
+        del ev, net, energy, forces
+        torch.cuda.empty_cache()
+        line["secondary"] = secondary_block(args, dev, sysd, dom, min(args.steps, 10))
+    if world == 1 and not args.no_reference_kernels:
+        torch.cuda.empty_cache()
+        line["reference_kernels"] = reference_kernels_block(50)
     sys.stdout.flush()
     os.dup2(saved_stdout, 1)
     print(json.dumps(line), flush=True)

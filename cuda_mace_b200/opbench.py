@@ -5,7 +5,8 @@
 symcon  SymmetricContraction, N = 4096 atoms, 128 channels, 10 species, forward and forward+backward
 imp     InvariantMessagePassing, N = 8192 receivers, Poisson(30) edges each, 128 channels, forward and backward
 fused   message passing with the last radial layer inside (float32), N receivers with Poisson(52) edges each
-linear  Linear, N = 3000 and N = 64000 nodes, 128 channels
+linear  Linear, N = 3000 and N = 64000 nodes, 128 channels; ElementalLinear, N = 64000, 4 elements
+edge    spherical harmonics and the tabulated (cubic spline) radial weights, E = 157 000 and 3 331 524 edges
 radial  the three hidden radial layers in one kernel (float32), E edges
 nlist   neighbour list of the 64 000-atom slab system on the device (cell-list kernels) and on the host (numpy)
 
@@ -21,8 +22,8 @@ import torch
 from . import cg, ops
 
 
-def _time(fn, iters):
-    for _ in range(3):
+def _time(fn, iters, warmup=3):
+    for _ in range(max(3, warmup)):
         fn()
     torch.cuda.synchronize()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -34,10 +35,14 @@ def _time(fn, iters):
     return t0.elapsed_time(t1) / iters
 
 
+RECORDS = []   # every measurement of this process, for callers that want them as data (bench.py)
+
+
 def _emit(op, what, ms, nbytes, **extra):
     line = {"op": op, "case": what, "ms": round(ms, 4), "algorithmic_bytes": int(nbytes),
             "gb_per_s": round(nbytes / (ms * 1e-3) / 1e9, 1)}
     line.update(extra)
+    RECORDS.append(line)
     print(json.dumps(line), flush=True)
 
 
@@ -67,11 +72,16 @@ def bench_symcon(dtype, iters, dev):
     _emit("symcon", f"N={N} C={C} Z={Z} forward+backward", _time(fwd_bwd, iters), s * (17 + 33) * N * C)
 
 
-def bench_imp(dtype, iters, dev):
+def bench_imp(dtype, iters, dev, graph="poisson"):
+    """graph = "poisson": the configuration of the spec (Poisson(30) receivers, uniform random senders);
+    "symmetric": the symmetrised random graph of the same mean degree in which every node has an edge, the only kind
+    of list the reference's kernels accept, so that both libraries can be timed on identical lists."""
+    from . import systems
+
     gen = torch.Generator().manual_seed(2)
     N, C = 8192, 128
     s = 4 if dtype == torch.float32 else 8
-    send, recv = _graph(N, 30, gen)
+    send, recv = systems.symmetric_graph(2, N, 30) if graph == "symmetric" else _graph(N, 30, gen)
     E = send.numel()
     X = torch.randn(N, C, generator=gen, dtype=torch.float64).to(dtype).to(dev).requires_grad_(True)
     Y = torch.randn(16, E, generator=gen, dtype=torch.float64).to(dtype).to(dev).requires_grad_(True)
@@ -121,7 +131,44 @@ def bench_linear(dtype, iters, dev):
         with torch.no_grad():
             t = _time(lambda: ops.linear_forward(X, W, WT), iters)
         _emit("linear", f"N={N} K=Nout={C}", t, s * (32 * N * C + 4 * C * C), gflops=round(32 * N * C * C / t / 1e6, 1))
+    N, Z = 64000, 4
+    WE = torch.randn(Z, 4, C, C, generator=gen, dtype=torch.float64).to(dtype).to(dev)
+    WET = WE.transpose(-1, -2).contiguous()
+    oh = torch.zeros(N, Z, dtype=dtype, device=dev)
+    oh[torch.arange(N), torch.randint(0, Z, (N,), generator=gen)] = 1.0
+    with torch.no_grad():
+        t = _time(lambda: ops.elemental_linear_forward(X, WE, WET, oh), iters)
+    _emit("elinear", f"N={N} Z={Z} K=Nout={C}", t, s * (32 * N * C + 4 * Z * C * C))
     ops.check_status()
+
+
+def bench_edge(dtype, iters, dev):
+    """Spherical harmonics alone (the reference's operator) and the tabulated radial weights, at the edge counts of
+    the 3 000-atom box and of one 64 000-atom slab."""
+    import math
+
+    s = 4 if dtype == torch.float32 else 8
+    sh = ops.SphericalHarmonics()
+    knots = torch.linspace(1e-12, 6.0, 256, dtype=torch.float64)
+    vals = torch.sin(knots[:, None] * torch.arange(1, 513, dtype=torch.float64) / 100.0)
+    h = float(knots[1] - knots[0])
+    spl = ops.CubicSpline(knots.to(dtype).to(dev), vals.to(dtype).to(dev), h, 5.0)
+    for E in (157000, 3331524):
+        gen = torch.Generator().manual_seed(4)
+        xyz = torch.randn(E, 3, generator=gen).to(dtype).to(dev).requires_grad_(True)
+        GY = torch.randn(16, E, generator=gen).to(dtype).to(dev)
+        Y = sh(xyz)
+        _emit("sh", f"E={E} forward", _time(lambda: sh(xyz), iters), s * E * (3 + 16))
+        _emit("sh", f"E={E} backward (derivatives recomputed)", _time(
+            lambda: torch.autograd.grad(Y, xyz, GY, retain_graph=True), iters), s * E * (3 + 16 + 3))
+        del Y, GY
+        r = (0.3 + 4.7 * torch.rand(E, generator=gen)).to(dtype).to(dev).requires_grad_(True)
+        R = spl(r)
+        GR = torch.randn(E, 512, dtype=dtype, device=dev)
+        _emit("spline", f"E={E} F=512 forward", _time(lambda: spl(r), iters), s * E * (1 + 512))
+        _emit("spline", f"E={E} F=512 backward (derivatives recomputed)", _time(
+            lambda: torch.autograd.grad(R, r, GR, retain_graph=True), iters), s * E * (1 + 512 + 1))
+        del R, GR
 
 
 def bench_radial(dtype, iters, dev, edges):
@@ -164,7 +211,8 @@ def bench_nlist(iters, dev, nodes):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="all", choices=["all", "symcon", "imp", "fused", "linear", "radial", "nlist"])
+    ap.add_argument("--op", default="all", choices=["all", "symcon", "imp", "fused", "linear", "edge", "radial", "nlist"])
+    ap.add_argument("--graph", default="poisson", choices=["poisson", "symmetric"], help="edge list of the imp case")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--nodes", type=int, default=64000, help="receivers of the fused case")
@@ -177,9 +225,11 @@ def main():
     if args.op in ("all", "symcon"):
         bench_symcon(dtype, args.iters, dev)
     if args.op in ("all", "imp"):
-        bench_imp(dtype, args.iters, dev)
+        bench_imp(dtype, args.iters, dev, args.graph)
     if args.op in ("all", "linear"):
         bench_linear(dtype, args.iters, dev)
+    if args.op in ("all", "edge"):
+        bench_edge(dtype, args.iters, dev)
     if args.op in ("all", "radial"):
         bench_radial(dtype, args.iters, dev, args.edges)
     if args.op in ("all", "fused"):

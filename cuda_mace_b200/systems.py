@@ -95,6 +95,27 @@ def neighbor_list(pos, box, pbc, r_cut, n_receivers=None):
     return edge_index, ext_shift[send_ext]
 
 
+def symmetric_graph(seed, n_nodes, mean_degree):
+    """Random undirected graph as a directed, receiver-sorted, duplicate-free, symmetric edge list in which every
+    node has at least one edge (a ring guarantees it): the kind of list the reference's message passing needs
+    (reverse-edge lookup, no edgeless receivers).  Returns int32 torch tensors (sender, receiver)."""
+    rng = np.random.default_rng(seed)
+    n_pairs = max(1, int(n_nodes * mean_degree / 2))
+    a = rng.integers(0, n_nodes, n_pairs)
+    b = rng.integers(0, n_nodes, n_pairs)
+    ring = np.arange(n_nodes)
+    a = np.concatenate([a, ring])
+    b = np.concatenate([b, (ring + 1) % n_nodes])
+    keep = a != b
+    lo, hi = np.minimum(a[keep], b[keep]), np.maximum(a[keep], b[keep])
+    pairs = np.unique(lo.astype(np.int64) * n_nodes + hi)
+    lo, hi = pairs // n_nodes, pairs % n_nodes
+    recv = np.concatenate([lo, hi])
+    send = np.concatenate([hi, lo])
+    order = np.lexsort((send, recv))
+    return torch.from_numpy(send[order].astype(np.int32)), torch.from_numpy(recv[order].astype(np.int32))
+
+
 # --------------------------------------------------------------------------------------
 # systems
 # --------------------------------------------------------------------------------------

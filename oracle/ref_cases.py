@@ -36,23 +36,10 @@ def _gen(seed):
 
 
 def symmetric_graph(seed, n_nodes, mean_degree):
-    """Random undirected graph as a directed, receiver-sorted, duplicate-free, symmetric edge list in which every
-    node has at least one edge (a ring guarantees it).  Returns int32 (sender, receiver)."""
-    rng = np.random.default_rng(seed)
-    n_pairs = max(1, int(n_nodes * mean_degree / 2))
-    a = rng.integers(0, n_nodes, n_pairs)
-    b = rng.integers(0, n_nodes, n_pairs)
-    ring = np.arange(n_nodes)
-    a = np.concatenate([a, ring])
-    b = np.concatenate([b, (ring + 1) % n_nodes])
-    keep = a != b
-    lo, hi = np.minimum(a[keep], b[keep]), np.maximum(a[keep], b[keep])
-    pairs = np.unique(lo.astype(np.int64) * n_nodes + hi)
-    lo, hi = pairs // n_nodes, pairs % n_nodes
-    recv = np.concatenate([lo, hi])
-    send = np.concatenate([hi, lo])
-    order = np.lexsort((send, recv))
-    return torch.from_numpy(send[order].astype(np.int32)), torch.from_numpy(recv[order].astype(np.int32))
+    """See cuda_mace_b200.systems.symmetric_graph (host-side data generation, shared with the benchmarks)."""
+    from cuda_mace_b200 import systems
+
+    return systems.symmetric_graph(seed, n_nodes, mean_degree)
 
 
 def check_graph(sender, receiver, n_nodes, channels):

@@ -7,6 +7,8 @@ TorchScript library register the same class names and cannot share an interprete
         oracle.ref_cases, float32 (and float64 where the reference's templates allow it)
     python -m oracle.ref_run model --atoms 375 --out results.npz
         energy + forces of the re-assembled reference step (oracle.ref_model) on a seeded periodic box
+    python -m oracle.ref_run step --atoms 8000 --iters 20 --warmup 5 --out result.json
+        the same step timed with CUDA events (atom-steps/s of the reference's kernels on this GPU)
     python -m oracle.ref_run bench --out results.json [--iters 100 --warmup 10]
         the timing protocol of the reference's own scripts (warm-up, then timed iterations bracketed by
         synchronisation: tests/symmetric_contraction.py:78-87, tools/model_surgery.py:198-233), with CUDA events
@@ -110,6 +112,8 @@ def model_system(atoms, channels, n_species, seed):
         raise ValueError("box narrower than twice the cutoff: the list would hold duplicate image pairs")
     pos = systems.random_box(atoms, np.full(3, side), 0.9, seed)
     species = np.random.default_rng(seed + 1).integers(0, n_species, atoms)
+    if n_species == 4:          # H : C : N : O = 50 : 30 : 10 : 10, the mix of the slab configuration
+        species = np.random.default_rng(seed + 1).choice(4, size=atoms, p=[0.5, 0.3, 0.1, 0.1])
     if n_species == 2:          # the 1 : 2 oxygen : hydrogen mix of the 3 000-atom configuration
         species = (np.arange(atoms) >= atoms // 3).astype(np.int64)
     ei, sh = systems.neighbor_list(pos, np.full(3, side), (True, True, True), 5.0)
@@ -264,7 +268,7 @@ def run_bench(classes, dev, iters, warmup):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("mode", choices=["parity", "model", "bench"])
+    ap.add_argument("mode", choices=["parity", "model", "step", "bench"])
     ap.add_argument("--size", default="live", choices=["fixture", "live"])
     ap.add_argument("--atoms", type=int, default=375)
     ap.add_argument("--channels", type=int, default=128)
@@ -282,6 +286,14 @@ def main():
     elif a.mode == "model":
         out, _ = run_model(a.atoms, a.channels, a.species, classes, dev)
         np.savez_compressed(a.out, **out)
+    elif a.mode == "step":
+        out, ms = run_model(a.atoms, a.channels, a.species, classes, dev, iters=max(1, a.iters), warmup=a.warmup)
+        rec = dict(atoms=int(out["atoms"]), edges=int(out["edges"]), channels=a.channels, species=a.species,
+                   steps=max(1, a.iters), warmup=a.warmup, ms_per_step=ms, atom_steps_per_s=a.atoms / (ms * 1e-3),
+                   energy=float(out["energy"]))
+        print(json.dumps(rec), flush=True)
+        with open(a.out, "w") as f:
+            json.dump(rec, f)
     else:
         rec = run_bench(classes, dev, a.iters, a.warmup)
         out, ms = run_model(3000, 128, 2, classes, dev, iters=max(10, a.iters // 5), warmup=a.warmup)

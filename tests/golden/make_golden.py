@@ -71,6 +71,17 @@ def main():
                         forces=f.numpy(), n_edges=np.array(ei.shape[1]))
     print("wrote fixtures:", E, "edges;", ei.shape[1], "edges in cfg0; E =", float(e))
 
+    # whole model at full size: the 3 000-atom H/O box (C=128, seed 1), energy + forces (about a minute of CPU)
+    s = systems.make_system("water3000")
+    ei, sh = systems.neighbor_list(s["positions"], s["box"], (True, True, True), 5.0)
+    params = systems.init_params(s["channels"], s["n_species"], 1)
+    e, e_inter, f = omodel.energy_and_forces(params, U, torch.from_numpy(s["positions"]),
+                                             systems.one_hot(s["species"], 2), torch.from_numpy(ei),
+                                             torch.from_numpy(sh))
+    np.savez_compressed(os.path.join(HERE, "water3000_energy_forces.npz"), energy=e.numpy(),
+                        interaction=e_inter.numpy(), forces=f.numpy(), n_edges=np.array(ei.shape[1]))
+    print("wrote water3000 fixture:", ei.shape[1], "edges; E_inter =", float(e_inter))
+
 
 if __name__ == "__main__":
     main()

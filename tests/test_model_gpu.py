@@ -74,21 +74,58 @@ def test_spline_variant_matches_spline_oracle(U):
     assert abs(float(out["interaction_energy"]) - float(z["interaction"])) < 1e-4 * abs(float(z["interaction"]))
 
 
-def test_full_size_properties(U):
-    """3000-atom configuration at full size: no oracle run, size-independent properties instead:
-    forces sum to zero, float32 agrees with float64, rigid translation leaves the energy unchanged."""
-    s, ei, sh, params, m64, data = build("water3000", U, torch.float64)
-    from cuda_mace_b200 import model
+@pytest.mark.parametrize("dtype,tol_e,tol_f", [(torch.float64, 1e-10, 1e-10), (torch.float32, 1e-5, 1e-4)])
+def test_water3000_full_size_matches_oracle_fixture(dtype, tol_e, tol_f, U):
+    """The 3 000-atom H/O configuration at its full size (156 916 edges, 128 channels) against the float64 CPU
+    oracle's energy and forces, committed as tests/golden/water3000_energy_forces.npz (tests/golden/make_golden.py);
+    plus the size-independent properties: forces sum to zero, a rigid translation leaves the energy unchanged."""
+    z = np.load(os.path.join(GOLD, "water3000_energy_forces.npz"))
+    s, ei, sh, params, m, data = build("water3000", U, dtype, seed=1)
+    assert ei.shape[1] == int(z["n_edges"])
+    out = m(data)
+    assert abs(float(out["interaction_energy"]) - float(z["interaction"])) < tol_e * abs(float(z["interaction"]))
+    assert abs(float(out["energy"]) - float(z["energy"])) < tol_e * abs(float(z["energy"]))
+    f = out["forces"]
+    assert rel_err(f, torch.from_numpy(z["forces"])) < tol_f
+    if dtype == torch.float64:
+        assert f.sum(0).abs().max().item() < 1e-9 * f.abs().max().item() * f.shape[0]
+        moved = dict(data, positions=data["positions"] + torch.tensor([0.3, -0.2, 0.1], dtype=torch.float64, device="cuda"))
+        assert abs(float(m(moved)["interaction_energy"]) - float(out["interaction_energy"])) < 1e-10 * abs(float(out["interaction_energy"]))
 
-    out64 = m64(data)
-    f = out64["forces"]
-    assert f.sum(0).abs().max().item() < 1e-9 * f.abs().max().item() * f.shape[0]
-    m32 = model.InvariantMACE(params, U, dtype=torch.float32, device="cuda")
-    out32 = m32(data)
-    assert abs(float(out32["interaction_energy"]) - float(out64["interaction_energy"])) < 1e-5 * abs(float(out64["interaction_energy"]))
-    assert rel_err(out32["forces"], f) < 1e-4
-    moved = dict(data, positions=data["positions"] + torch.tensor([0.3, -0.2, 0.1], dtype=torch.float64, device="cuda"))
-    assert abs(float(m64(moved)["interaction_energy"]) - float(out64["interaction_energy"])) < 1e-10 * abs(float(out64["interaction_energy"]))
+
+def _cluster_around(pos, species, box, centre, radius):
+    """Atoms (with their periodic images) within `radius` of atom `centre`, as an open cluster; the centre is row 0."""
+    d = pos - pos[centre]
+    d -= np.round(d / box) * box
+    keep = np.flatnonzero((d * d).sum(1) < radius * radius)
+    keep = np.concatenate([[centre], keep[keep != centre]])
+    return d[keep] + 50.0, species[keep]
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-10), (torch.float32, 2e-5)])
+def test_slab_64000_node_energies_match_oracle_on_cut_out_clusters(dtype, tol, U):
+    """The 64 000-atom slab at its full size.  A node's interaction energy depends only on the atoms within
+    2 r_max = 10 A of it, so the oracle evaluated on the open cluster cut out around an atom must give that atom
+    the node energy the kernels give it inside the full periodic system.  Three atoms are checked against the
+    oracle; the whole system against the size-independent properties (zero net force, in float64)."""
+    from cuda_mace_b200 import systems
+    from oracle import model as omodel
+
+    s, ei, sh, params, m, data = build("slab", U, dtype, seed=1)
+    out = m(data)
+    e0 = m.atomic_energies.index_select(0, data["species"].long())
+    node_inter = (out["node_energy"] - e0).cpu()
+    pos, species, box = s["positions"], s["species"], np.asarray(s["box"])
+    scale = float(node_inter.abs().max())
+    for centre in (0, 31999, 63999):
+        cpos, cspec = _cluster_around(pos, species, box, centre, 10.0 + 1e-6)
+        cei, csh = systems.neighbor_list(cpos, np.full(3, 200.0), (False, False, False), 5.0)
+        e_nodes = omodel.node_energies(params, U, torch.from_numpy(cpos), systems.one_hot(cspec, 4),
+                                       torch.from_numpy(cei), torch.from_numpy(csh))
+        assert abs(float(node_inter[centre]) - float(e_nodes[0])) < tol * scale, (centre, len(cspec))
+    if dtype == torch.float64:
+        f = out["forces"]
+        assert f.sum(0).abs().max().item() < 1e-9 * f.abs().max().item() * f.shape[0]
 
 
 def test_single_gpu_slab_domain_equals_periodic(U):

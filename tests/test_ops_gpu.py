@@ -37,6 +37,7 @@ def imp_case(seed, N, deg, C, dtype, dev, nsend=None, empty_every=0):
     (33, 3, 96, None, 0),       # three 32-channel chunks
     (50, 5, 32, 80, 3),         # more sender rows than receivers (ghost atoms), isolated receivers
     (5, 600, 128, None, 0),     # more than 512 neighbours per receiver
+    (8192, 30, 128, None, 0),   # the isolated-operator configuration of the benchmark spec at its full size
 ])
 def test_message_passing(dtype, N, deg, C, nsend, empty, dev):
     from cuda_mace_b200 import ops
@@ -143,7 +144,8 @@ def test_elemental_linear(dtype, N, Z, K, dev):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("N,C,Z", [(256, 128, 10), (19, 32, 1), (64, 64, 4)])
+@pytest.mark.parametrize("N,C,Z", [(256, 128, 10), (19, 32, 1), (64, 64, 4),
+                                   (4096, 128, 10)])   # last: the benchmark spec's configuration at full size
 def test_symmetric_contraction(dtype, N, C, Z, dev, U):
     from cuda_mace_b200 import ops
     from oracle import ops as oops
@@ -237,6 +239,10 @@ def test_cubic_spline(dtype, dev):
     (out ** 2).sum().backward()
     assert out.shape == (E, F)
     assert out[r.to(dev) > 5.0].abs().max().item() == 0.0
+    # The table is a random walk, so within an interval the cubic's four terms are each about as large as the
+    # largest table value while most results are much smaller: the evaluation keeps a few ulp of the largest TERM,
+    # not of the result, and the gradient sums 512 such values per edge.  Hence ten times the operator tolerance
+    # here; the smooth table of tests/test_reference_pin.py meets the plain tolerance.
     assert rel_err(out, ref) < TOL[dtype]["out"] * 10
     assert rel_err(rg.grad, ro.grad) < TOL[dtype]["grad"] * 10
 

@@ -6,14 +6,16 @@
 // located on the device from the element group bounds, so there is no host synchronisation and
 // no per-element launch.  This file holds the float64 tensor-core (DMMA) kernel and the shared-memory tiled
 // FMA kernel that serves odd sizes and float32 callers that do not use the tcgen05 path; rows are gathered,
-// so no intermediate re-layout of X is needed.
+// so no intermediate re-layout of X is needed.  The same two kernels with the identity row map are the plain float64
+// product cmace_gemm_f64 (radial multilayer perceptron and node products of the float64 model).
 #include "common.cuh"
 
 namespace cmace {
 
 constexpr int TILE_M = 64, TILE_N = 64, KSTEP = 16, LIN_THREADS = 256;
 
-template <typename T>
+// PLAIN: one dense product out[M, Nout] = scale * X[M, K] @ W[K, Nout] (nnodes = M rows, no l blocks, no elements).
+template <typename T, bool PLAIN>
 __global__ void __launch_bounds__(LIN_THREADS)
     linear_tile_kernel(const T *__restrict__ X, const T *__restrict__ W,
                        const int32_t *__restrict__ node_order, const int32_t *__restrict__ elem_start,
@@ -22,27 +24,31 @@ __global__ void __launch_bounds__(LIN_THREADS)
   __shared__ T Bs[KSTEP][TILE_N];
   __shared__ int64_t row_of[TILE_M];
 
-  const int l = blockIdx.y;
+  const int l = PLAIN ? 0 : blockIdx.y;
   const int nl = 2 * l + 1;
   const int n0 = blockIdx.z * TILE_N;
 
   // which (element, tile) this CTA owns
   int z = 0;
   int64_t tile = blockIdx.x, seg_begin = 0, seg_count = 0;
-  for (; z < nelements; z++) {
-    seg_begin = elem_start ? elem_start[z] : 0;
-    seg_count = elem_start ? (int64_t)elem_start[z + 1] - seg_begin : nnodes;
-    const int64_t tiles = (seg_count * nl + TILE_M - 1) / TILE_M;
-    if (tile < tiles) break;
-    tile -= tiles;
+  if (!PLAIN) {
+    for (; z < nelements; z++) {
+      seg_begin = elem_start ? elem_start[z] : 0;
+      seg_count = elem_start ? (int64_t)elem_start[z + 1] - seg_begin : nnodes;
+      const int64_t tiles = (seg_count * nl + TILE_M - 1) / TILE_M;
+      if (tile < tiles) break;
+      tile -= tiles;
+    }
+    if (z >= nelements) return;
   }
-  if (z >= nelements) return;
 
   const int tid = threadIdx.x;
   if (tid < TILE_M) {
     const int64_t rl = tile * TILE_M + tid;
     int64_t grow = -1;
-    if (rl < seg_count * nl) {
+    if (PLAIN) {
+      if (rl < nnodes) grow = rl;
+    } else if (rl < seg_count * nl) {
       const int64_t slot = seg_begin + rl / nl;
       const int64_t node = node_order ? (int64_t)node_order[slot] : slot;
       grow = node * 16 + l * l + (rl % nl);
@@ -51,7 +57,7 @@ __global__ void __launch_bounds__(LIN_THREADS)
   }
   __syncthreads();
 
-  const T *Wz = W + ((int64_t)(z * 4 + l) * K) * Nout;
+  const T *Wz = PLAIN ? W : W + ((int64_t)(z * 4 + l) * K) * Nout;
   const int ty = tid / 16, tx = tid % 16;
   T acc[4][4];
 #pragma unroll
@@ -121,6 +127,7 @@ __device__ __forceinline__ void cp_async_16_zfill(void *dst, const void *src, bo
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
 }
 
+template <bool PLAIN>
 __global__ void __launch_bounds__(DM_THREADS, 1)
     linear_dmma_kernel(const double *__restrict__ X, const double *__restrict__ W,
                        const int32_t *__restrict__ node_order, const int32_t *__restrict__ elem_start,
@@ -128,26 +135,30 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
   extern __shared__ __align__(16) double dm_smem[];
   __shared__ int64_t row_of[DM_TILE];
 
-  const int l = blockIdx.y;
+  const int l = PLAIN ? 0 : blockIdx.y;
   const int nl = 2 * l + 1;
   const int n0 = blockIdx.z * DM_TILE;
 
   int z = 0;
   int64_t tile = blockIdx.x, seg_begin = 0, seg_count = 0;
-  for (; z < nelements; z++) {
-    seg_begin = elem_start ? elem_start[z] : 0;
-    seg_count = elem_start ? (int64_t)elem_start[z + 1] - seg_begin : nnodes;
-    const int64_t tiles = (seg_count * nl + DM_TILE - 1) / DM_TILE;
-    if (tile < tiles) break;
-    tile -= tiles;
+  if (!PLAIN) {
+    for (; z < nelements; z++) {
+      seg_begin = elem_start ? elem_start[z] : 0;
+      seg_count = elem_start ? (int64_t)elem_start[z + 1] - seg_begin : nnodes;
+      const int64_t tiles = (seg_count * nl + DM_TILE - 1) / DM_TILE;
+      if (tile < tiles) break;
+      tile -= tiles;
+    }
+    if (z >= nelements) return;
   }
-  if (z >= nelements) return;
 
   const int tid = threadIdx.x;
   if (tid < DM_TILE) {
     const int64_t rl = tile * DM_TILE + tid;
     int64_t grow = -1;
-    if (rl < seg_count * nl) {
+    if (PLAIN) {
+      if (rl < nnodes) grow = rl;
+    } else if (rl < seg_count * nl) {
       const int64_t slot = seg_begin + rl / nl;
       const int64_t node = node_order ? (int64_t)node_order[slot] : slot;
       grow = node * 16 + l * l + (rl % nl);
@@ -156,7 +167,7 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
   }
   __syncthreads();
 
-  const double *Wz = W + ((int64_t)(z * 4 + l) * K) * Nout;
+  const double *Wz = PLAIN ? W : W + ((int64_t)(z * 4 + l) * K) * Nout;
   // copy assignments: 1024 16-byte chunks per operand and K slice, two per thread
   int64_t a_src[2];
   int a_dst[2], a_k[2], b_dst[2], b_k[2], b_c[2];
@@ -242,16 +253,45 @@ static int linear_dmma(const double *X, const double *W, const int32_t *node_ord
                        cmace_stream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(linear_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(linear_dmma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM_BYTES) != cudaSuccess)
       return fail(CMACE_ERR_CUDA, "cmace_linear_f64: cannot reserve shared memory");
     attr_set = true;
   }
   const int64_t max_tiles = (nnodes * 7 + DM_TILE - 1) / DM_TILE + nelements;
   if (max_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear: too many rows");
   dim3 grid((unsigned)max_tiles, 4, (unsigned)((Nout + DM_TILE - 1) / DM_TILE));
-  linear_dmma_kernel<<<grid, DM_THREADS, DM_SMEM_BYTES, (cudaStream_t)stream>>>(
+  linear_dmma_kernel<false><<<grid, DM_THREADS, DM_SMEM_BYTES, (cudaStream_t)stream>>>(
       X, W, node_order, elem_start, nelements, nnodes, K, Nout, scale, out);
   return check_launch("cmace_linear_f64");
+}
+
+// out[M, N] = scale * A[M, K] @ B[K, N], float64: the DMMA tile loop with the identity row map; the FMA tile kernel
+// when the 16-byte copies of the tensor-core path cannot be aligned (odd K or N).
+static int gemm_f64(const double *A, const double *B, int64_t M, int K, int N, double scale, double *out,
+                    cmace_stream_t stream) {
+  if (M < 0 || K < 1 || N < 1) return fail(CMACE_ERR_ARG, "cmace_gemm_f64: bad size");
+  if (M == 0) return CMACE_OK;
+  if (!A || !B || !out) return fail(CMACE_ERR_ARG, "cmace_gemm_f64: null pointer");
+  if (K % 2 == 0 && N % 2 == 0 && aligned16(A) && aligned16(B) && aligned16(out)) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(linear_dmma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM_BYTES) != cudaSuccess)
+        return fail(CMACE_ERR_CUDA, "cmace_gemm_f64: cannot reserve shared memory");
+      attr_set = true;
+    }
+    const int64_t tiles = (M + DM_TILE - 1) / DM_TILE;
+    if (tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm_f64: too many rows");
+    dim3 grid((unsigned)tiles, 1, (unsigned)((N + DM_TILE - 1) / DM_TILE));
+    linear_dmma_kernel<true><<<grid, DM_THREADS, DM_SMEM_BYTES, (cudaStream_t)stream>>>(A, B, nullptr, nullptr, 1, M, K, N,
+                                                                                         scale, out);
+    return check_launch("cmace_gemm_f64");
+  }
+  const int64_t tiles = (M + TILE_M - 1) / TILE_M;
+  if (tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm_f64: too many rows");
+  dim3 grid((unsigned)tiles, 1, (unsigned)((N + TILE_N - 1) / TILE_N));
+  linear_tile_kernel<double, true><<<grid, LIN_THREADS, 0, (cudaStream_t)stream>>>(A, B, nullptr, nullptr, 1, M, K, N,
+                                                                                   scale, out);
+  return check_launch("cmace_gemm_f64");
 }
 
 template <typename T>
@@ -271,7 +311,7 @@ static int linear(const T *X, const T *W, const int32_t *node_order, const int32
   const int64_t max_tiles = (nnodes * 7 + TILE_M - 1) / TILE_M + nelements;
   if (max_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear: too many rows");
   dim3 grid((unsigned)max_tiles, 4, (unsigned)((Nout + TILE_N - 1) / TILE_N));
-  linear_tile_kernel<T><<<grid, LIN_THREADS, 0, (cudaStream_t)stream>>>(
+  linear_tile_kernel<T, false><<<grid, LIN_THREADS, 0, (cudaStream_t)stream>>>(
       X, W, node_order, elem_start, nelements, nnodes, K, Nout, (T)scale, out);
   return check_launch("cmace_linear");
 }
@@ -290,5 +330,9 @@ int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order
                      int nelements, int64_t nnodes, int K, int Nout, double scale, double *out,
                      cmace_stream_t stream) {
   return linear<double>(X, W, node_order, elem_start, nelements, nnodes, K, Nout, scale, out, stream);
+}
+int cmace_gemm_f64(const double *A, const double *B, int64_t M, int K, int N, double scale, double *out,
+                   cmace_stream_t stream) {
+  return gemm_f64(A, B, M, K, N, scale, out, stream);
 }
 }

@@ -100,6 +100,7 @@ class InvariantMACE(torch.nn.Module):
                 W_skip = P["W_skip"].double() / math.sqrt(Z)
                 L.linear = ops.ElementalLinear(torch.einsum("lab,zlbc->zlac", W_lin, W_skip).to(**dd))
                 L.register_buffer("W_readout", (P["W_readout"] / math.sqrt(C)).to(**d64))
+                L.register_buffer("W_readout_T", L.W_readout.t().contiguous())
             else:
                 L.linear = ops.Linear(P["W_lin"].to(**dd), scale=1.0 / float(P["avg_num_neighbors"]))
                 # W_sc [C, Z, C]: as one [C, Z*C] matrix, column block z is the matrix of element z
@@ -107,6 +108,8 @@ class InvariantMACE(torch.nn.Module):
                 L.register_buffer("W_sc_T", L.W_sc.t().contiguous())
                 L.register_buffer("W_readout1", (P["W_readout1"] / math.sqrt(C)).to(**d64))
                 L.register_buffer("W_readout2", (P["W_readout2"] / math.sqrt(P["W_readout2"].shape[0])).to(**d64))
+                L.register_buffer("W_readout1_T", L.W_readout1.t().contiguous())
+                L.register_buffer("W_readout2_T", L.W_readout2.t().contiguous())
             L.contraction = ops.SymmetricContraction(U3, U2, U1, P["W3"].to(dtype), P["W2"].to(dtype),
                                                      P["W1"].to(dtype)).to(device)
             L.register_buffer("W_prod", (P["W_prod"] / math.sqrt(C)).to(**dd))
@@ -142,7 +145,7 @@ class InvariantMACE(torch.nn.Module):
             h = ops.radial_hidden(bessel, Ws[:-1], [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial - 1)])
             return ops.matmul3x(h, Ws[-1], getattr(L, f"W_radial{L.n_radial - 1}_T"))
         for i, W in enumerate(Ws):
-            h = ops.matmul3x(h, W, getattr(L, f"W_radial{i}_T")) if on_tc else h @ W
+            h = self._mm(h, W, getattr(L, f"W_radial{i}_T"))
             if i + 1 < L.n_radial:
                 h = torch.nn.functional.silu(h)
         return h
@@ -207,16 +210,21 @@ class InvariantMACE(torch.nn.Module):
                 h = h + sc
             h64 = h.double()
             if t == 0:
-                es.append((h64 @ L.W_readout)[:, 0])
+                es.append(self._mm(h64, L.W_readout, L.W_readout_T)[:, 0])
             else:
-                es.append((_silu_n(h64 @ L.W_readout1) @ L.W_readout2)[:, 0])
+                hid = _silu_n(self._mm(h64, L.W_readout1, L.W_readout1_T))
+                es.append(self._mm(hid, L.W_readout2, L.W_readout2_T)[:, 0])
         return self.scale * (es[0] + es[1]) + self.shift
 
     @staticmethod
     def _mm(x, W, W_T):
-        """x @ W for a constant weight: on the tensor cores (3-term TF32 split) in float32, torch.matmul otherwise."""
+        """x @ W for a constant weight on this library's kernels: tcgen05 with a 3-term TF32 split in float32, the
+        FP64 tensor cores (DMMA) in float64; torch.matmul only for float32 shapes the tensor-core kernel does not
+        take and for CPU tensors (the oracle-side domain tests)."""
         if ops.tensor_core_ok(x.dtype, W.shape[0], W.shape[1]):
             return ops.matmul3x(x, W, W_T)
+        if x.is_cuda and x.dtype == torch.float64:
+            return ops.matmul_f64(x, W, W_T)
         return x @ W
 
     def forward(self, data, training=False, compute_force=True, topology=None):

@@ -247,6 +247,38 @@ def matmul3x(A, W, W_T=None):
     return _Matmul3xFunction.apply(A, W, W_T)
 
 
+class _MatmulF64Function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, A, W, W_T):
+        ctx.save_for_backward(W_T)
+        return _gemm_f64(A, W)
+
+    @staticmethod
+    def backward(ctx, G):
+        (W_T,) = ctx.saved_tensors
+        return _gemm_f64(G, W_T), None, None
+
+
+def _gemm_f64(A, B):
+    A = A.contiguous()
+    M, K = A.shape
+    N = B.shape[1]
+    out = torch.empty(M, N, dtype=torch.float64, device=A.device)
+    _abi.call("cmace_gemm_f64", _ptr(A), _ptr(B), M, K, N, 1.0, _ptr(out), _stream(), tag=f"M={M},K={K},N={N}")
+    return out
+
+
+def matmul_f64(A, W, W_T=None):
+    """A [M,K] @ W [K,N] for a constant float64 weight W (no weight gradient) on the FP64 tensor cores."""
+    _check_cuda(A, W)
+    if A.dtype != torch.float64 or W.dtype != torch.float64:
+        raise TypeError("matmul_f64 needs float64 operands")
+    W = W.contiguous()
+    if W_T is None:
+        W_T = W.t().contiguous()
+    return _MatmulF64Function.apply(A, W, W_T)
+
+
 def tensor_core_ok(dtype, K, N):
     return USE_TENSOR_CORES and dtype == torch.float32 and K % 8 == 0 and N % 4 == 0
 

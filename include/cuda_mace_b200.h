@@ -218,6 +218,13 @@ int cmace_linear_f64(const double *X, const double *W, const int32_t *node_order
                      const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
                      double scale, double *out, cmace_stream_t stream);
 
+/* Plain float64 product out[M,N] = scale * A[M,K] @ B[K,N] on the FP64 tensor cores (the tile loop of
+ * cmace_linear_f64 with the identity row map; FMA tile kernel for odd K or N).  Serves the radial multilayer
+ * perceptron and the node products [N,C] x [C,C] of the float64 model, which the reference leaves to
+ * torch.matmul (models/InvariantMACE.py:41-53 linear_matmul) or tabulates in float32 (:226-240). */
+int cmace_gemm_f64(const double *A, const double *B, int64_t M, int K, int N, double scale, double *out,
+                   cmace_stream_t stream);
+
 /* ---- float32 tensor-core path (tcgen05, kind::tf32 with a 3-term hi/lo split, TMEM accumulator) -----
  * The reference runs Linear / ElementalLinear on wmma TF32 with the same 3-term error compensation
  * (cuda/src/linear_impl.cu:85-101).  Weights are packed once into the shared-memory image the tensor

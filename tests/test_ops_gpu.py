@@ -304,6 +304,24 @@ def test_tensor_core_gemm_has_float32_accuracy(M, K, N, dev):
     assert e_fwd < 6e-7 * (1 + K / 64) and e_bwd < 6e-7 * (1 + N / 64)
 
 
+@pytest.mark.parametrize("M,K,N", [(1000, 8, 64), (517, 64, 512), (300, 512, 64), (129, 128, 1), (64, 3, 5),
+                                   (128, 128, 128), (1, 16, 2)])
+def test_float64_product_on_the_tensor_cores(M, K, N, dev):
+    """cmace_gemm_f64 (DMMA tile loop for even K and N, FMA tiles otherwise) against a float64 host product, value
+    and gradient with respect to A."""
+    from cuda_mace_b200 import ops
+
+    g = torch.Generator().manual_seed(M + K + N)
+    A = torch.randn(M, K, generator=g, dtype=torch.float64)
+    W = torch.randn(K, N, generator=g, dtype=torch.float64)
+    G = torch.randn(M, N, generator=g, dtype=torch.float64)
+    Ad = A.to(dev).requires_grad_(True)
+    out = ops.matmul_f64(Ad, W.to(dev))
+    (gA,) = torch.autograd.grad(out, Ad, G.to(dev))
+    assert rel_err(out, A @ W) < 1e-13
+    assert rel_err(gA, G @ W.t()) < 1e-13
+
+
 def test_tensor_core_and_fma_linear_agree(dev):
     from cuda_mace_b200 import ops
     from oracle import ops as oops

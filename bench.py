@@ -67,6 +67,9 @@ def parse():
                     help="exact: Bessel basis + multilayer perceptron per edge (the headline); spline: the reference's "
                          "tabulated radial weights (cubic spline, --spline-knots knots), a secondary figure")
     ap.add_argument("--spline-knots", type=int, default=256)
+    ap.add_argument("--materialise-gradr", action="store_true",
+                    help="float32: write the radial-weight gradient [E,4,C] and multiply it afterwards (the path "
+                         "before radial_message_passing), for A/B timing")
     ap.add_argument("--graph", action="store_true",
                     help="1 GPU: replay the step as a CUDA graph in the device-resident leg (no per-kernel timings, "
                          "no roofline object); useful for small systems, which are launch-bound")
@@ -138,6 +141,8 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
         dims = dict(x.split("=") for x in name[name.index("[") + 1:-1].split(","))
         rows, k, n = int(dims.get("M", E)), int(dims["K"]), int(dims["N"])   # no M: a product over the edges
         return 4 * (rows * k + rows * n + k * n)
+    if name == "cmace_imp_bwd_edge_f32[no gradR]":   # the edge pass of radial_message_passing: R in, no gradR out
+        return s * (4 * E * C + 2 * 16 * E + Ns * C + 16 * N * C) + 8 * E
     base = name[:-4]
     return {
         "cmace_imp_fwd": s * (4 * E * C + 16 * E + Ns * C + 16 * N * C) + 8 * E,
@@ -151,6 +156,8 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
         "cmace_radial_hidden_fwd": 4 * E * (8 + 64 + 3 * 64),
         "cmace_radial_hidden_bwd": 4 * E * (64 + 3 * 64 + 8),
         "cmace_imp_radial_fused_fwd": 4 * (E * 64 + 16 * E + Ns * C + 16 * N * C + 4 * E * C) + 8 * E,
+        # grad h3 from operands formed on the fly: X, G, Y, the edge lists and the weights in, [E,64] out
+        "cmace_gemm3x_gradr": 4 * (E * 64 + 16 * E + Ns * C + 16 * N * C + 64 * 4 * C) + 8 * E,
         # tabulated radial weights (secondary configuration): r in, R [E,4C] out / gradR in, grad r out; table in L2
         "cmace_spline_fwd": s * (E + 4 * E * C),
         "cmace_spline_bwd": s * (2 * E + 4 * E * C),
@@ -396,8 +403,10 @@ def main():
     os.dup2(2, 1)
     import torch.distributed as dist
 
-    from cuda_mace_b200 import _abi, cg, domain, evaluator, model, systems
+    from cuda_mace_b200 import _abi, cg, domain, evaluator, model, ops, systems
 
+    if args.materialise_gradr:
+        ops.RADIAL_GRADIENT_ON_THE_FLY = False
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:

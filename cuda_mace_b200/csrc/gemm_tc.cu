@@ -68,17 +68,10 @@ constexpr int GT_PREFETCH = 2;                      // K blocks of global loads 
 constexpr int GT_EP_STRIDE = 20;                    // floats per row of an epilogue transpose buffer (16 + padding)
 constexpr int GT_EP_BYTES = 8 * 32 * GT_EP_STRIDE * 4;  // one buffer per epilogue warp, 20 KB in all
 constexpr int GT_EP_TMA_BYTES = 8 * 32 * 128;       // PLAIN with TMA stores: 32 rows x 128 bytes per epilogue warp
-#ifdef CMACE_GEMM_DEBUG
-#define GT_DBG(g, bit) (((g).debug & (bit)) != 0)
-#define GT_PROF(g, slot, t0) do { if (((g).debug & 4096) && blockIdx.x == 0 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long *>((g).status) + (slot), (unsigned long long)(clock64() - (t0))); } while (0)
-#define GT_NOW() clock64()
-#else
-#define GT_PROF(g, slot, t0) do { } while (0)
-#define GT_NOW() 0
-#define GT_DBG(g, bit) false
-#endif
 
-enum { GT_MODE_PLAIN = 0, GT_MODE_LINEAR = 1 };
+// GRADR: the A operand is never in memory.  Row e, column l*C + c of A is the radial-weight gradient of the message
+// passing, X[sender(e), c] * sum_{m in l} Y[m, e] * G[receiver(e), m, c]; the producer warps form it on the fly.
+enum { GT_MODE_PLAIN = 0, GT_MODE_LINEAR = 1, GT_MODE_GRADR = 2 };
 
 struct GemmArgs {
   const float *A;
@@ -98,7 +91,10 @@ struct GemmArgs {
   int b_resident;               // PLAIN: bytes of this CTA's B images kept in shared memory for the whole kernel, or 0
   int a_lo_tmem;                // PLAIN: 1 when the residual image of A lives in tensor memory (kernel variant TS)
   int ep_tma;                   // PLAIN: 1 when the epilogue stores tiles with TMA from a staging buffer
-  int debug;                    // knock-out switches, only honoured in -DCMACE_GEMM_DEBUG builds
+  // GRADR: X [Ns, C] sender features, G [Nr, 16, C] gradient of the messages, Y [16, M] harmonics, edge lists [M]
+  const float *gx, *gg, *gy;
+  const int32_t *sender, *receiver;
+  int C;
   int a_act;                    // 1: apply SiLU to A while loading it
   const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
 };
@@ -171,7 +167,7 @@ struct TileWalker {
     ntile = 0;
     rt_step = 0;
     nt_step = 0;
-    if (MODE == GT_MODE_PLAIN) {
+    if (MODE != GT_MODE_LINEAR) {
       rt = blockIdx.x / (uint32_t)n_tiles;
       ntile = (int)(blockIdx.x - (uint32_t)rt * (uint32_t)n_tiles);
       rt_step = gridDim.x / (uint32_t)n_tiles;
@@ -183,7 +179,7 @@ struct TileWalker {
   __device__ __forceinline__ bool next(Tile &T) {
     if (started) {
       t += gridDim.x;
-      if (MODE == GT_MODE_PLAIN) {
+      if (MODE != GT_MODE_LINEAR) {
         rt += rt_step;
         ntile += nt_step;
         if (ntile >= n_tiles) {
@@ -195,7 +191,7 @@ struct TileWalker {
     started = true;
     T.valid = false;
     if (t >= total) return false;
-    if (MODE == GT_MODE_PLAIN) {
+    if (MODE != GT_MODE_LINEAR) {
       T.row0 = rt * GT_TILE_M;
       if (T.row0 >= M) return false;   // padded index space of the resident-B mode: row tiles only grow
       T.seg_begin = 0;
@@ -232,7 +228,7 @@ template <int MODE>
 __device__ __forceinline__ int64_t global_row(const GemmArgs &g, const Tile &T, int r) {
   const int64_t lr = T.row0 + r;
   if (lr >= T.seg_rows) return -1;
-  if (MODE == GT_MODE_PLAIN) return lr;
+  if (MODE != GT_MODE_LINEAR) return lr;
   // rows of one (element, l) problem fit 32 bits (checked on the host); constant divisors compile to a multiplication
   const uint32_t lr32 = (uint32_t)lr;
   uint32_t q;
@@ -257,11 +253,7 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 // Alo*Bhi product reads its A operand from there.  Shared-memory bandwidth is what the roles of this kernel compete
 // for; this takes the image's 16 KB store and its 16 KB read by the tensor core out of every pipeline item.  Needs
 // room in tensor memory next to the accumulators: two accumulators of 2 npad columns + 32 columns per ring slot.
-// WIDE (implies TS; K = 64 with resident B images): a pipeline item is the whole K extent of a tile (two K blocks), and the
-// three split terms accumulate into the same columns, which leaves room for the ring of residual images beside two
-// 128-column accumulators.  Per item the roles synchronise once instead of twice, the MMA thread issues 24
-// instructions back to back, and the epilogue reads half as many columns.
-template <bool ACT, int MODE, bool TS = false, bool WIDE = false>
+template <bool ACT, int MODE, bool TS = false>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap,
                        const __grid_constant__ CUtensorMap tmap_out) {
@@ -285,8 +277,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   const uint32_t GT_STAGE_BYTES = (uint32_t)g.stage_bytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long t_kernel0 = GT_NOW();
-  (void)t_kernel0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GT_STAGES; s++) {
@@ -311,24 +301,22 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   const int k_blocks = g.k_blocks;
   const uint32_t b_image = (uint32_t)g.npad * 128u;  // bytes of one B image
   const uint32_t b_off = TS ? GT_A_SLAB : 2 * GT_A_SLAB;          // the stage's B block follows its A image(s)
-  // tensor-memory columns between the accumulators; TS: ring of residual images behind them, 32 (WIDE: 64) columns a slot
-  const uint32_t acc_stride = WIDE ? (uint32_t)g.npad : TS ? 2u * (uint32_t)g.npad : 256u;
-  const uint32_t lo_ring = tmem_base + (WIDE ? 2u : 4u) * (uint32_t)g.npad;
-  const int items = WIDE ? k_blocks / 2 : k_blocks;               // pipeline items per tile
+  // tensor-memory columns between the accumulators; TS: ring of residual images behind them, 32 columns a slot
+  const uint32_t acc_stride = TS ? 2u * (uint32_t)g.npad : 256u;
+  const uint32_t lo_ring = tmem_base + 4u * (uint32_t)g.npad;
+  const int items = k_blocks;                                     // pipeline items per tile
 
   if (MODE == GT_MODE_PLAIN && TS && warp < GT_PRODUCER_WARPS) {
     // ================================ converters, residual image to tensor memory ================================
     // A thread owns one row of the tile (the tensor-memory lane its warp may access) and 16 of the K block's 32
     // columns: four 16-byte shared-memory loads (conflict-free: the 128-byte swizzle puts the same logical chunk of
     // eight consecutive rows into eight different bank groups), three ALU operations per float, one tcgen05.st.
-    // (WIDE: the warp's half is one of the item's two K blocks, eight loads and one 32-column store.)
     const int q = warp & 3, hf = warp >> 2;
     const int r = q * 32 + lane;
-    uint32_t soff[WIDE ? 8 : 4];
+    uint32_t soff[4];
 #pragma unroll
-    for (int c = 0; c < (WIDE ? 8 : 4); c++)
-      soff[c] = WIDE ? (uint32_t)(hf * GT_A_SLAB) + (uint32_t)sw128_offset(r, c) : (uint32_t)sw128_offset(r, 4 * hf + c);
-    const uint32_t t_lo = lo_ring + ((uint32_t)(q * 32) << 16) + (WIDE ? 32u : 16u) * (uint32_t)hf;
+    for (int c = 0; c < 4; c++) soff[c] = (uint32_t)sw128_offset(r, 4 * hf + c);
+    const uint32_t t_lo = lo_ring + ((uint32_t)(q * 32) << 16) + 16u * (uint32_t)hf;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -337,20 +325,17 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     while (ok && tiles.next(T)) {
       for (int kb = 0; kb < items; kb++) {
         uint32_t got = 1;
-        const long long tw = GT_NOW();
         if (lane == 0) got = mbar_wait(tma_full + 8 * stage, phase) ? 1u : 0u;
         got = __shfl_sync(0xffffffffu, got, 0);
-        if (warp == 0) GT_PROF(g, 1, tw);
-        const long long tc = GT_NOW();
         if (!got) {
           report(g, 1);
           ok = false;
           break;
         }
         const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-        uint32_t lo[WIDE ? 32 : 16];
+        uint32_t lo[16];
 #pragma unroll
-        for (int c = 0; c < (WIDE ? 8 : 4); c++) {
+        for (int c = 0; c < 4; c++) {
           float4 a;
           asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                        : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
@@ -361,13 +346,11 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           lo[4 * c + 2] = __float_as_uint(to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u)));
           lo[4 * c + 3] = __float_as_uint(to_tf32(a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u)));
         }
-        if constexpr (WIDE) tmem_st32(t_lo + 64u * (uint32_t)stage, lo);
-        else tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
+        tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar + 8 * stage);
-        if (warp == 0) GT_PROF(g, 2, tc);
         if (++stage == GT_STAGES) {
           stage = 0;
           phase ^= 1;
@@ -395,11 +378,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     while (ok && tiles.next(T)) {
       for (int kb = 0; kb < k_blocks; kb++) {
         uint32_t got = 1;
-        const long long tw = GT_NOW();
         if (lane == 0) got = mbar_wait(tma_full + 8 * stage, phase) ? 1u : 0u;
         got = __shfl_sync(0xffffffffu, got, 0);
-        if (warp == 0) GT_PROF(g, 1, tw);
-        const long long tc = GT_NOW();
         if (!got) {
           report(g, 1);
           ok = false;
@@ -434,14 +414,110 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar + 8 * stage);
-        if (warp == 0) GT_PROF(g, 2, tc);
         if (++stage == GT_STAGES) {
           stage = 0;
           phase ^= 1;
         }
       }
     }
-  } else if (MODE != GT_MODE_PLAIN && warp < GT_PRODUCER_WARPS) {
+  } else if (MODE == GT_MODE_GRADR && warp < GT_PRODUCER_WARPS) {
+    // ================================ producers, operand formed on the fly ================================
+    // Thread p owns the 16-byte chunk p % 8 of the rows p / 8 + 32 i (i < 4) of every K block, as in the LINEAR
+    // producers.  K block (l, cb) covers the columns l*C + 32 cb .. + 31 of A; the items of a tile run cb-outer,
+    // l-inner (the order of a sum does not matter to the accumulator, the producer only has to copy the matching
+    // B block), so the sender's features x = X[s, 32 cb + 4 chunk .. + 3] stay in registers for four items.  Per item
+    // and row: q = sum_{m in l} Y[m, e] * G[r, m, 32 cb + 4 chunk .. + 3] (2l + 1 fused multiply-adds on float4),
+    // a = x * q, split into hi / lo and stored.  The rows of a tile are consecutive edges of the receiver-sorted
+    // list, so the G pieces of an item belong to three or four receivers and are served by L1 after their first use;
+    // X is gathered from L2 once per tile and column block.
+    const int p = threadIdx.x;
+    const int chunk = p & 7;
+    const int rbase = p >> 3;
+    const int C = g.C, ncb = C >> 5;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    TileWalker<MODE> tiles(g, tab);
+    Tile T;
+    while (ok && tiles.next(T)) {
+      int64_t e[GT_ROWS_PER_THREAD];
+      const float *xrow[GT_ROWS_PER_THREAD], *grow[GT_ROWS_PER_THREAD];
+#pragma unroll
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
+        e[i] = T.row0 + rbase + GT_ROW_STEP * i;
+        const bool in = e[i] < g.M;
+        const int64_t ee = in ? e[i] : 0;
+        xrow[i] = g.gx + (int64_t)__ldg(g.sender + ee) * C + 4 * chunk;
+        grow[i] = g.gg + (int64_t)__ldg(g.receiver + ee) * 16 * C + 4 * chunk;
+        if (!in) e[i] = -1;
+      }
+      for (int cb = 0; ok && cb < ncb; cb++) {
+        float4 x[GT_ROWS_PER_THREAD];
+#pragma unroll
+        for (int i = 0; i < GT_ROWS_PER_THREAD; i++)
+          x[i] = e[i] >= 0 ? __ldg(reinterpret_cast<const float4 *>(xrow[i] + 32 * cb)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int l = 0; l < 4; l++) {
+          float4 a[GT_ROWS_PER_THREAD];
+#pragma unroll
+          for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
+            float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (e[i] >= 0) {
+#pragma unroll
+              for (int m = l * l; m < (l + 1) * (l + 1); m++) {
+                const float y = __ldg(g.gy + (int64_t)m * g.M + e[i]);
+                const float4 gv = __ldg(reinterpret_cast<const float4 *>(grow[i] + m * C + 32 * cb));
+                q.x = fmaf(y, gv.x, q.x);
+                q.y = fmaf(y, gv.y, q.y);
+                q.z = fmaf(y, gv.z, q.z);
+                q.w = fmaf(y, gv.w, q.w);
+              }
+            }
+            a[i] = make_float4(x[i].x * q.x, x[i].y * q.y, x[i].z * q.z, x[i].w * q.w);
+          }
+          // the slot is free once the MMAs that read it have completed
+          uint32_t got = 1;
+          if (lane == 0) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) {
+            report(g, 1);
+            ok = false;
+            break;
+          }
+          const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+          if (p == 0) {
+            const int kb = l * ncb + cb;
+            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) + (int64_t)kb * (2 * (int64_t)b_image);
+            mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
+            bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
+          }
+#pragma unroll
+          for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
+            const float4 v = a[i];
+            float4 lo;
+            // the raw value serves as the hi image (the tensor core ignores the low 13 mantissa bits)
+            lo.x = to_tf32(v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u));
+            lo.y = to_tf32(v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u));
+            lo.z = to_tf32(v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u));
+            lo.w = to_tf32(v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u));
+            const uint32_t off = (uint32_t)sw128_offset(rbase + GT_ROW_STEP * i, chunk);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                         : "memory");
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + GT_A_SLAB + off), "f"(lo.x), "f"(lo.y),
+                         "f"(lo.z), "f"(lo.w)
+                         : "memory");
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+          if (++stage == GT_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (MODE == GT_MODE_LINEAR && warp < GT_PRODUCER_WARPS) {
     // ================================ producers ================================
     // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
     // GT_PREFETCH items ahead of the conversion in a register ring, so that enough bytes are in flight
@@ -472,7 +548,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (head.grow[i] >= 0 && k0 < g.K && !GT_DBG(g, 1))
+        if (head.grow[i] >= 0 && k0 < g.K)
           v[i] = __ldg(reinterpret_cast<const float4 *>(g.A + head.grow[i] * g.K + k0));
       }
       const int64_t bblock = (int64_t)(head.T.mat * g.n_tiles + head.T.ntile) * k_blocks + head.kb;
@@ -485,24 +561,19 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     auto commit = [&](int64_t bblock, const float4 (&v)[GT_ROWS_PER_THREAD]) -> bool {
       // lane 0 polls the barrier for the warp
       uint32_t got = 1;
-      const long long tw = GT_NOW();
       if (lane == 0) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
       got = __shfl_sync(0xffffffffu, got, 0);
-      if (warp == 0) GT_PROF(g, 1, tw);
-      const long long tc = GT_NOW();
       if (!got) {
         report(g, 1);
         return false;
       }
       const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-      if (p == 0 && GT_DBG(g, 8)) mbar_arrive(full_bar + 8 * stage);
-      if (p == 0 && !GT_DBG(g, 8)) {
+      if (p == 0) {
         const unsigned char *bsrc =
             reinterpret_cast<const unsigned char *>(g.packed) + bblock * (2 * (int64_t)b_image);
         mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
         bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
       }
-      if (!GT_DBG(g, 16))
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
         const int r = rbase + GT_ROW_STEP * i;
@@ -528,7 +599,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(full_bar + 8 * stage);
-      if (warp == 0) GT_PROF(g, 2, tc);
       if (++stage == GT_STAGES) {
         stage = 0;
         phase ^= 1;
@@ -579,24 +649,12 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
                                     ((int64_t)(T.mat * g.n_tiles + T.ntile) * k_blocks) * (2 * (int64_t)b_image);
         for (int kb = 0; kb < items; kb++) {
-          const long long tl = GT_NOW();
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1)) {
             report(g, 5);
             ok = false;
             break;
           }
-          GT_PROF(g, 10, tl);
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-          if (WIDE) {   // both K blocks of the tile, B is resident
-            mbar_arrive_expect_tx(tma_full + 8 * stage, 2u * GT_A_SLAB);
-            tma_load_2d(sA, &tmap, 2 * kb * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
-            tma_load_2d(sA + GT_A_SLAB, &tmap, (2 * kb + 1) * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
-            if (++stage == GT_STAGES) {
-              stage = 0;
-              phase ^= 1;
-            }
-            continue;
-          }
           mbar_arrive_expect_tx(tma_full + 8 * stage, g.b_resident ? (uint32_t)GT_A_SLAB : GT_A_SLAB + 2 * b_image);
           tma_load_2d(sA, &tmap, kb * GT_KBLOCK, (int)T.row0, tma_full + 8 * stage);
           if (!g.b_resident)
@@ -638,43 +696,20 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       // one MMA gives Ahi*Bhi in columns [0, npad) and Ahi*Blo in columns [npad, 2 npad)
       const uint32_t idesc2 = umma_idesc_tf32(GT_TILE_M, 2 * g.npad);
       const uint32_t idesc1 = umma_idesc_tf32(GT_TILE_M, nmma);
-      const long long ta = GT_NOW();
       if (!mbar_wait(acc_empty + 8 * acc, acc_phase[acc] ^ 1)) {
         report(g, 2);
         break;
       }
-      GT_PROF(g, 3, ta);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * acc_stride;
       for (int kb = 0; kb < items; kb++) {
-        const long long tf = GT_NOW();
-        if (!GT_DBG(g, 1024) && !mbar_wait(full_bar + 8 * stage, phase)) {
+        if (!mbar_wait(full_bar + 8 * stage, phase)) {
           report(g, 3);
           ok = false;
           break;
         }
-        GT_PROF(g, 4, tf);
-        const long long ti = GT_NOW();
-        if (!GT_DBG(g, 512)) tc_fence_after();
-        if (WIDE) {
-          // two K blocks, four K steps each, three terms into the same columns
-          const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-          const uint32_t a_lo_t = lo_ring + 64u * (uint32_t)stage;
-#pragma unroll
-          for (int kbi = 0; kbi < 2; kbi++) {
-            const uint64_t a_hi0 = umma_desc_sw128(sA + kbi * GT_A_SLAB);
-            const uint64_t b_hi0 = umma_desc_sw128(smem_first + (uint32_t)(2 * kb + kbi) * 2u * b_image);
-            const uint64_t b_lo0 = umma_desc_sw128(smem_first + (uint32_t)(2 * kb + kbi) * 2u * b_image + b_image);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              umma_tf32(d_tmem, a_hi0 + (uint64_t)(2 * j), b_hi0 + (uint64_t)(2 * j), idesc1, (kb | kbi | j) != 0);
-              umma_tf32_acc(d_tmem, a_hi0 + (uint64_t)(2 * j), b_lo0 + (uint64_t)(2 * j), idesc1);
-              umma_tf32_ts_acc(d_tmem, a_lo_t + 32u * kbi + 8u * j, b_hi0 + (uint64_t)(2 * j), idesc1);
-            }
-          }
-          umma_commit(empty_bar + 8 * stage);
-          if (kb == items - 1) umma_commit(acc_full + 8 * acc);
-        } else {
+        tc_fence_after();
+        {
           // descriptors of K step j differ from those of step 0 by j * 32 bytes = 2 address units
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
           const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
@@ -682,8 +717,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
               umma_desc_sw128(g.b_resident ? smem_first + (uint32_t)kb * 2u * b_image : sA + b_off);
           int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
           ksteps = ksteps > 4 ? 4 : ksteps;
-          if (GT_DBG(g, 2)) ksteps = 0;
-          const long long tm0 = GT_NOW();
           // the issuing thread shares its scheduler with busy warps, so every instruction between two
           // MMAs costs issue latency: descriptors are formed first, then the MMAs go back to back
           uint64_t ah[4], al[4], bh[4];
@@ -711,18 +744,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
               else umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
             }
           }
-          GT_PROF(g, 8, tm0);
-          const long long tm1 = GT_NOW();
-          if (GT_DBG(g, 128)) {
-            mbar_arrive(empty_bar + 8 * stage);
-            if (kb == k_blocks - 1) mbar_arrive(acc_full + 8 * acc);
-          } else {
-            umma_commit(empty_bar + 8 * stage);
-            if (kb == k_blocks - 1) umma_commit(acc_full + 8 * acc);
-          }
-          GT_PROF(g, 9, tm1);
+          umma_commit(empty_bar + 8 * stage);
+          if (kb == k_blocks - 1) umma_commit(acc_full + 8 * acc);
         }
-        GT_PROF(g, 5, ti);
         if (++stage == GT_STAGES) {
           stage = 0;
           phase ^= 1;
@@ -752,17 +776,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       int ncols = g.N - n0;
       ncols = ncols > 128 ? 128 : ncols;
       uint32_t got = 1;
-      const long long te = GT_NOW();
       if (lane == 0) got = mbar_wait(acc_full + 8 * acc, acc_phase[acc]) ? 1u : 0u;
-      if (q == 0 && half == 0) GT_PROF(g, 6, te);
-      const long long tb = GT_NOW();
       if (!__shfl_sync(0xffffffffu, got, 0)) {
         report(g, 4);
         break;
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * acc_stride + ((uint32_t)(q * 32) << 16);
-      if (MODE == GT_MODE_PLAIN && !ACT && g.ep_tma) {
+      if (MODE != GT_MODE_LINEAR && !ACT && g.ep_tma) {
         // Tile store by TMA.  Global stores from registers cost the load/store data pipe one pass per 32-byte sector
         // whatever their shape (64 KB per tile = 2048 passes, the pipe measured 70 % busy on [E,64]x[64,512]); here
         // a warp writes its 32 rows x 32 columns into a swizzled 4 KB staging buffer (eight conflict-free 16-byte
@@ -776,12 +797,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           for (int h16 = 0; h16 < 2; h16++) {
             uint32_t v[16], w[16];
             tmem_ld16_nowait(taddr + (uint32_t)(c0 + 16 * h16), v);
-            if constexpr (WIDE) {
-#pragma unroll
-              for (int i = 0; i < 16; i++) w[i] = 0u;
-            } else {
-              tmem_ld16_nowait(taddr + (uint32_t)(g.npad + c0 + 16 * h16), w);
-            }
+            tmem_ld16_nowait(taddr + (uint32_t)(g.npad + c0 + 16 * h16), w);
             tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 4; c++) {
@@ -797,10 +813,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           fence_proxy_async();
           __syncwarp();
           // a box that starts inside the matrix: the engine clips what hangs over, a start outside is never issued
-          if (lane == 0 && T.row0 + q * 32 < g.M && !GT_DBG(g, 4))
+          if (lane == 0 && T.row0 + q * 32 < g.M)
             tma_store_2d(&tmap_out, n0 + c0, (int)T.row0 + q * 32, stg);
         }
-      } else if (MODE == GT_MODE_PLAIN) {
+      } else if (MODE != GT_MODE_LINEAR) {
         // Straight from tensor memory to global memory, no shared-memory transpose: the 16x256b load shape hands
         // thread t two rows (t/4 and t/4 + 8 of a 16-row half) and, per 8-column block, the two columns
         // 2(t%4), 2(t%4)+1 -- four neighbouring lanes hold 32 contiguous bytes of a row, so an 8-byte store per
@@ -813,12 +829,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             uint32_t v[16], w[16];
             const uint32_t ta = taddr + ((uint32_t)(16 * hr) << 16) + (uint32_t)c0;
             tmem_ld_16x256b_x4(ta, v);                 // Ahi*Bhi + Alo*Bhi
-            if constexpr (WIDE) {
-#pragma unroll
-              for (int i = 0; i < 16; i++) w[i] = 0u;  // all three terms are in v
-            } else {
-              tmem_ld_16x256b_x4(ta + g.npad, w);      // Ahi*Blo
-            }
+            tmem_ld_16x256b_x4(ta + g.npad, w);        // Ahi*Blo
             tmem_ld_wait();
             const int64_t gra = __shfl_sync(0xffffffffu, grow, 16 * hr + (lane >> 2));
             const int64_t grb = __shfl_sync(0xffffffffu, grow, 16 * hr + 8 + (lane >> 2));
@@ -847,7 +858,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             float *pb = g.out + grb * g.N + n0 + cbase;
 #pragma unroll
             for (int m = 0; m < 2; m++) {
-              const bool col_ok = cbase + 8 * m < ncols && !GT_DBG(g, 4);
+              const bool col_ok = cbase + 8 * m < ncols;
               if (ACT && g.ep_z != nullptr) {
                 if (gra >= 0 && col_ok) {
                   const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (pa - g.out) + 8 * m));
@@ -901,7 +912,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             for (int it = 0; it < 4; it++) {
               const int rr = it * 8 + (lane >> 2);
               float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 3) * 4);
-              if (rowptr[it] != nullptr && col_ok && !GT_DBG(g, 4)) {
+              if (rowptr[it] != nullptr && col_ok) {
                 if (ACT && g.ep_z != nullptr) {
                   const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + cc));
                   o.x *= silu_n_grad(z.x);
@@ -919,17 +930,15 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8 * acc);
-      if (q == 0 && half == 0) GT_PROF(g, 7, tb);
       acc_phase[acc] ^= 1;
       acc ^= 1;
     }
     // the copy engine still reads this warp's staging buffer and writes its tile: wait before the CTA retires
-    if (MODE == GT_MODE_PLAIN && !ACT && g.ep_tma && lane == 0) tma_store_wait_all();
+    if (MODE != GT_MODE_LINEAR && !ACT && g.ep_tma && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) GT_PROF(g, 0, t_kernel0);
   if (warp == GT_PRODUCER_WARPS) tmem_dealloc(tmem_base, GT_TMEM_COLS);
 }
 
@@ -1033,37 +1042,24 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (num_sms <= 0) num_sms = 148;
   }
-#ifdef CMACE_GEMM_DEBUG
-  g.debug = getenv("CMACE_GEMM_DEBUG") ? atoi(getenv("CMACE_GEMM_DEBUG")) : 0;
-#endif
   // PLAIN row map with few K blocks: every CTA keeps the B images of one column tile in shared memory and only
   // streams A, instead of fetching the same B block from L2 again for every 128-row tile
   const int b_all = g.k_blocks * 2 * g.npad * 128;
   g.b_resident = (g.mode == GT_MODE_PLAIN && b_all <= 64 * 1024 && num_sms >= g.n_tiles) ? b_all : 0;
   const bool act = g.a_act != 0 || g.ep_z != nullptr;
   // residual image of A in tensor memory when at least four ring slots fit next to the two accumulators
-  static const bool ts_off = getenv("CMACE_GEMM_TS") && atoi(getenv("CMACE_GEMM_TS")) == 0;
   const int ts_slots = (GT_TMEM_COLS - 4 * g.npad) / 32;
-  g.a_lo_tmem = (g.mode == GT_MODE_PLAIN && !act && ts_slots >= 4 && !ts_off) ? 1 : 0;
-  // whole-K items when K is exactly two K blocks and B is resident; at least two ring slots of 64 columns
-  // (measured 1-9 % slower than two items per tile on the [E,64]x[64,512] and [E,64]x[64,64] products, so it is opt-in)
-  static const bool wide_off = !(getenv("CMACE_GEMM_WIDE") && atoi(getenv("CMACE_GEMM_WIDE")) == 1);
-  const int wide_slots = (GT_TMEM_COLS - 2 * g.npad) / 64;
-  const bool wide = g.mode == GT_MODE_PLAIN && !act && !ts_off && !wide_off && g.b_resident && g.K == 2 * GT_KBLOCK &&
-                    wide_slots >= 2;
-  if (wide) g.a_lo_tmem = 1;
-  g.stage_bytes = wide ? 2 * GT_A_SLAB : (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
+  g.a_lo_tmem = (g.mode == GT_MODE_PLAIN && !act && ts_slots >= 4) ? 1 : 0;
+  g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   // PLAIN: tile stores by TMA from a 4 KB staging buffer per epilogue warp (N >= 32: the box is 32 columns wide);
   // LINEAR: the transpose buffers of its epilogue
-  static const bool ep_tma_off = getenv("CMACE_GEMM_EP_TMA") && atoi(getenv("CMACE_GEMM_EP_TMA")) == 0;
-  g.ep_tma = (g.mode == GT_MODE_PLAIN && !act && g.N >= 32 && !ep_tma_off) ? 1 : 0;
-  const int ep_bytes = g.mode == GT_MODE_PLAIN ? (g.ep_tma ? GT_EP_TMA_BYTES : 0) : GT_EP_BYTES;
+  g.ep_tma = (g.mode != GT_MODE_LINEAR && !act && g.N >= 32) ? 1 : 0;
+  const int ep_bytes = g.mode != GT_MODE_LINEAR ? (g.ep_tma ? GT_EP_TMA_BYTES : 0) : GT_EP_BYTES;
   // the LINEAR variant holds its problem table in static shared memory
   const int budget = GT_SMEM_BUDGET - (g.mode == GT_MODE_LINEAR ? (int)sizeof(ProblemTable) + 1024 : 0);
   g.stages = (budget - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
-  if (g.a_lo_tmem && !wide && g.stages > ts_slots) g.stages = ts_slots;
-  if (wide && g.stages > wide_slots) g.stages = wide_slots;
+  if (g.a_lo_tmem && g.stages > ts_slots) g.stages = ts_slots;
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
   const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024;
   CUtensorMap tmap, tmap_out;
@@ -1076,8 +1072,8 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     if (int rc = encode_out_tensor_map(&tmap_out, g.out, g.M, g.N, what)) return rc;
   }
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
+              : g.mode == GT_MODE_GRADR ? gemm3x_tf32_kernel<false, GT_MODE_GRADR>
               : act                    ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN>
-              : wide                   ? gemm3x_tf32_kernel<false, GT_MODE_PLAIN, true, true>
               : g.a_lo_tmem            ? gemm3x_tf32_kernel<false, GT_MODE_PLAIN, true>
                                        : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1135,6 +1131,29 @@ int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int 
   g.n_tiles = p.n_tiles; g.k_blocks = p.k_blocks; g.npad = p.npad;
   g.total_tiles = ((M + GT_TILE_M - 1) / GT_TILE_M) * p.n_tiles;
   return gemm_launch(g, "cmace_gemm3x", (cudaStream_t)stream);
+}
+
+int cmace_gemm3x_gradr_f32(const float *X, const float *G, const float *Y, const int32_t *sender,
+                           const int32_t *receiver, const float *packed, int64_t nedges, int channels, int N,
+                           float *out, int32_t *status, cmace_stream_t stream) {
+  if (nedges < 0 || N < 32 || N > 128 || N % 4 != 0)
+    return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm3x_gradr: the hidden width must be a multiple of 4 in 32..128");
+  if (channels < 32 || channels > 128 || channels % 32 != 0)
+    return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm3x_gradr: channels must be 32, 64, 96 or 128");
+  if (nedges == 0) return CMACE_OK;
+  if (!X || !G || !Y || !sender || !receiver || !packed || !out)
+    return fail(CMACE_ERR_ARG, "cmace_gemm3x_gradr: null pointer");
+  if (!aligned16(X) || !aligned16(G) || !aligned16(packed) || !aligned16(out))
+    return fail(CMACE_ERR_ARG, "cmace_gemm3x_gradr: pointers must be 16-byte aligned");
+  const int K = 4 * channels;
+  const PackGeom p = pack_geom(N, K);
+  GemmArgs g{};
+  g.packed = packed; g.out = out; g.status = status;
+  g.gx = X; g.gg = G; g.gy = Y; g.sender = sender; g.receiver = receiver; g.C = channels;
+  g.M = nedges; g.K = K; g.N = N; g.nelements = 1; g.mode = GT_MODE_GRADR; g.scale = 1.0f;
+  g.n_tiles = p.n_tiles; g.k_blocks = p.k_blocks; g.npad = p.npad;
+  g.total_tiles = (nedges + GT_TILE_M - 1) / GT_TILE_M;
+  return gemm_launch(g, "cmace_gemm3x_gradr", (cudaStream_t)stream);
 }
 
 int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node_order, const int32_t *elem_start,

@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
           t[v] = fma(u[l][v], r[l][v], t[v]);
           gr[v] = x[v] * u[l][v];
         }
-        store_vec_stream<T, VEC>(gradR + (ee * 4 + l) * C + c0, gr);
+        if (gradR != nullptr) store_vec_stream<T, VEC>(gradR + (ee * 4 + l) * C + c0, gr);
       }
       if (Tout != nullptr) store_vec<T, VEC>(Tout + ee * C + c0, t);
       const T tot = warp_reduce16(p, lane);
@@ -209,7 +209,7 @@ constexpr int BS_SLOTS = 4;
 constexpr int BS_C = 128;
 constexpr int BS_R_BYTES = 4 * BS_C * 4;
 constexpr int BS_SLOT_BYTES = BS_R_BYTES + BS_C * 4;
-constexpr long long BS_TIMEOUT_CYCLES = 4000000000LL;
+constexpr long long BS_TIMEOUT_CYCLES = 400000000LL;   // bound of every wait, about 0.2 s
 
 struct EdgeCursor {
   int64_t node, e, e1;
@@ -317,7 +317,24 @@ __global__ void __launch_bounds__(BS_WARPS * 32, 1)
         if (ok || clock64() - t0 > BS_TIMEOUT_CYCLES) break;
       }
       if (!__all_sync(0xffffffffu, ok != 0)) {
+        // Give up on this warp's receivers, but not before the copies it still has in flight have landed: they
+        // target this CTA's shared memory, which must stay allocated until they complete.  Slots ccount + 1 ..
+        // icount - 1 are outstanding; each gets one more bounded wait.
         if (lane == 0 && stalled) atomicExch(stalled, 1);
+        for (uint32_t k = ccount + 1; k < icount; k++) {
+          const uint32_t kbar = bar0 + 8 * (k % BS_SLOTS), kpar = (k / BS_SLOTS) & 1u;
+          uint32_t done = 0;
+          const long long t1 = clock64();
+          do {
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done)
+                : "r"(kbar), "r"(kpar)
+                : "memory");
+          } while (!done && clock64() - t1 < BS_TIMEOUT_CYCLES);
+        }
         break;
       }
     }
@@ -361,7 +378,7 @@ __global__ void __launch_bounds__(BS_WARPS * 32, 1)
         t[v] = fmaf(u[l][v], r[l][v], t[v]);
         gr[v] = x[v] * u[l][v];
       }
-      store_vec_stream<float, 4>(gradR + (e * 4 + l) * BS_C + c0, gr);
+      if (gradR != nullptr) store_vec_stream<float, 4>(gradR + (e * 4 + l) * BS_C + c0, gr);
     }
     // every value read from the slot has been consumed by now: the next copy may go into it
     __syncwarp();
@@ -474,15 +491,6 @@ static void launch_bwd_edge(const T *X, const T *Y, const T *R, const T *G, cons
                                                                      nnodes, nedges, C, gradR, gy, Tout);
 }
 
-// the staged edge pass can be switched off with CMACE_IMP_STAGED=0 (falls back to the register-prefetch kernel)
-static bool staged_edge_pass_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char *v = getenv("CMACE_IMP_STAGED");
-    on = (v == nullptr || atoi(v) != 0) ? 1 : 0;
-  }
-  return on != 0;
-}
 static __device__ int g_staged_stall;   // set when a bounded wait of the staged edge pass gave up
 static int *staged_stall_flag() {
   static int *per_device[64] = {nullptr};
@@ -502,9 +510,9 @@ static int imp_bwd_edge(const T *X, const T *Y, const T *R, const T *G, const in
   int rc = check_common<T>(X, R, G, nnodes, nedges, C, "cmace_imp_bwd_edge");
   if (rc) return rc;
   if (nnodes == 0 || nedges == 0) return CMACE_OK;
-  if (!X || !Y || !R || !G || !sender || !row_ptr || !gradR || !gradY)
+  if (!X || !Y || !R || !G || !sender || !row_ptr || !gradY)
     return fail(CMACE_ERR_ARG, "cmace_imp_bwd_edge: null pointer");
-  if (!aligned16(gradR) || (Tout && !aligned16(Tout)))
+  if ((gradR && !aligned16(gradR)) || (Tout && !aligned16(Tout)))
     return fail(CMACE_ERR_ARG, "cmace_imp_bwd_edge: outputs must be 16-byte aligned");
   const int vec = pick_vec<T>(C);
   const int nchunks = C / (32 * vec);
@@ -513,7 +521,7 @@ static int imp_bwd_edge(const T *X, const T *Y, const T *R, const T *G, const in
   T *gy = nchunks > 1 ? partial : gradY;
   cudaStream_t st = (cudaStream_t)stream;
   if constexpr (sizeof(T) == 4) {
-    if (C == BS_C && staged_edge_pass_enabled() && aligned16(R) && aligned16(X) && aligned16(G)) {
+    if (C == BS_C && aligned16(R) && aligned16(X) && aligned16(G)) {
       static int num_sms = 0;
       if (num_sms == 0) {
         int dev = 0;

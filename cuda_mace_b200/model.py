@@ -161,6 +161,13 @@ class InvariantMACE(torch.nn.Module):
             hidden = ops.radial_hidden(bessel, Ws[:-1], [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial - 1)])
             return ops.fused_radial_message_passing(up, Y, hidden, Ws[-1], getattr(L, f"W_radial{L.n_radial - 1}_T"),
                                                     topology)
+        if (self.radial == "exact" and ops.RADIAL_GRADIENT_ON_THE_FLY and ops.radial_hidden_ok(up.dtype, Ws[:-1])
+                and ops.radial_message_passing_ok(up.dtype, C, Ws[-1].shape[0])
+                and all(ops.tensor_core_ok(up.dtype, W.shape[0], W.shape[1]) for W in Ws)):
+            # float32 default: hidden layers in one kernel; last layer as a product whose gradient array is never
+            # written (the backward forms the radial-weight gradient inside the tensor-core kernel that consumes it)
+            hidden = ops.radial_hidden(bessel, Ws[:-1], [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial - 1)])
+            return ops.radial_message_passing(up, Y, hidden, Ws[-1], getattr(L, f"W_radial{L.n_radial - 1}_T"), topology)
         R = self._radial_weights(L, bessel, lengths).view(-1, 4, C)
         return self.tp(up, Y, R, send, recv, n_owned, topology=topology)
 

@@ -87,6 +87,9 @@ FUSED_RADIAL_ACTIVATION = False
 # Measured at 64 000 atoms (E = 3.33 M, C = 128): 3.75 ms against 2.25 + 1.23 ms for the GEMM followed by the
 # plain forward, so the model does not use it by default; fused_radial_message_passing() always does.
 FUSED_RADIAL_MESSAGE_PASSING = False
+# The backward of the last radial layer + message passing without a gradR [E,4,C] array (radial_message_passing):
+# the model's float32 default.  False selects the separate product / message-passing operators.
+RADIAL_GRADIENT_ON_THE_FLY = True
 
 
 def _status_tensor(device):
@@ -424,6 +427,71 @@ class _IMPFunction(torch.autograd.Function):
             _abi.call("cmace_imp_bwd_node_" + _suffix(X), _ptr(T), _ptr(perm), _ptr(send_ptr), topo.nsenders, C,
                       _ptr(gradX), _stream())
         return gradX, gradY, gradR, None
+
+
+class _RadialIMPFunction(torch.autograd.Function):
+    """Message passing on radial weights R = H @ W (H the last hidden activations of the radial perceptron, W its
+    last layer) with a backward that never materialises gradR [E,4,C]: the edge pass is called without a gradR
+    output (it still gives gradY and the sender contributions T), and grad H = gradR @ W^T comes from the
+    tensor-core kernel whose producer warps form the rows of gradR on the fly (cmace_gemm3x_gradr_f32).  The forward
+    is the plain product followed by cmace_imp_fwd_f32; R is kept for the backward's edge pass."""
+
+    @staticmethod
+    def forward(ctx, X, Y, H, W, W_T, topo):
+        X, Y, H = X.contiguous(), Y.contiguous(), H.contiguous()
+        N, C, E, K = topo.nnodes, X.shape[1], topo.nedges, H.shape[1]
+        if X.shape[0] != topo.nsenders or Y.shape != (16, E) or H.shape[0] != E or W.shape != (K, 4 * C):
+            raise RuntimeError(f"shape mismatch: X {tuple(X.shape)}, Y {tuple(Y.shape)}, H {tuple(H.shape)}, "
+                               f"W {tuple(W.shape)} for {N} nodes and {E} edges")
+        R = _gemm3x(H, W_T)
+        out = torch.empty(N, 16, C, dtype=torch.float32, device=X.device)
+        _abi.call("cmace_imp_fwd_f32", _ptr(X), _ptr(Y), _ptr(R), _ptr(topo.sender), _ptr(topo.row_ptr), N, E, C,
+                  _ptr(out), _stream())
+        ctx.save_for_backward(X, Y, R, W)
+        ctx.topo = topo
+        return out
+
+    @staticmethod
+    def backward(ctx, G):
+        X, Y, R, W = ctx.saved_tensors
+        topo = ctx.topo
+        G = G.contiguous()
+        N, C, E, K = topo.nnodes, X.shape[1], topo.nedges, W.shape[0]
+        need_x = ctx.needs_input_grad[0]
+        gradY = torch.empty_like(Y)
+        T = torch.empty(E, C, dtype=X.dtype, device=X.device) if need_x else None
+        nscratch = _abi.call("cmace_imp_bwd_scratch_elems", E, C, 0)
+        scratch = torch.empty(nscratch, dtype=X.dtype, device=X.device) if nscratch > 0 else None
+        _abi.call("cmace_imp_bwd_edge_f32", _ptr(X), _ptr(Y), _ptr(R), _ptr(G), _ptr(topo.sender), _ptr(topo.row_ptr),
+                  N, E, C, 0, _ptr(gradY), _ptr(T), _ptr(scratch), _stream(), tag="no gradR")
+        gradX = None
+        if need_x:
+            perm, send_ptr = topo.sender_order()
+            gradX = torch.empty(topo.nsenders, C, dtype=X.dtype, device=X.device)
+            _abi.call("cmace_imp_bwd_node_f32", _ptr(T), _ptr(perm), _ptr(send_ptr), topo.nsenders, C, _ptr(gradX),
+                      _stream())
+        gradH = None
+        if ctx.needs_input_grad[2]:
+            gradH = torch.empty(E, K, dtype=torch.float32, device=X.device)
+            _abi.call("cmace_gemm3x_gradr_f32", _ptr(X), _ptr(G), _ptr(Y), _ptr(topo.sender), _ptr(topo.receiver),
+                      _ptr(_pack(W)), E, C, K, _ptr(gradH), _ptr(_status_tensor(X.device)), _stream())
+        return gradX, gradY, gradH, None, None, None
+
+
+def radial_message_passing_ok(dtype, C, K):
+    """True when radial_message_passing applies (float32, 32/64/96/128 channels, hidden width 32..128)."""
+    return USE_TENSOR_CORES and dtype == torch.float32 and C in (32, 64, 96, 128) and 32 <= K <= 128 and K % 8 == 0
+
+
+def radial_message_passing(X, Y, H, W, W_T, topology):
+    """out[i,lm,c] = sum_e X[sender(e),c] Y[lm,e] (H @ W)[e, l(lm)*C + c], differentiable with respect to X, Y and H.
+    X [Ns,C], Y [16,E], H [E,K], W [K,4C] constant float32 (no weight gradient), W_T its contiguous transpose.  Same
+    values as InvariantMessagePassingTP applied to H @ W; the backward moves 2 x 4C floats per edge less through
+    memory because the gradient of the radial weights is consumed where it is formed."""
+    _check_cuda(X, Y, H, W, W_T)
+    if not radial_message_passing_ok(X.dtype, X.shape[1], H.shape[1]):
+        raise RuntimeError("radial_message_passing needs float32, 32/64/96/128 channels and a hidden width in 32..128")
+    return _RadialIMPFunction.apply(X, Y, H, W, W_T, topology)
 
 
 def _pack_fused_radial(W_T, C):

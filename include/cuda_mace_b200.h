@@ -151,7 +151,8 @@ int cmace_spline_bwd_f64(const double *r, const double *r_knots, const double *c
  * kernel impl.cu:74-165): out[i,lm,c] = sum_{e in row i} X[sender[e],c] * Y[lm,e] * R[e,l(lm),c].
  * Every row of out is written (zeros for receivers without edges).
  * cmace_imp_bwd_edge_* + cmace_imp_bwd_node_* replace jit_backward_message_passing
- * (wrapper :157-284, kernels impl.cu:167-399).  The edge pass writes gradR [E,4,C], gradY [16,E]
+ * (wrapper :157-284, kernels impl.cu:167-399).  The edge pass writes gradY [16,E], gradR [E,4,C] unless
+ * gradR == NULL (a caller that forms the radial-weight gradient on the fly, cmace_gemm3x_gradr_f32),
  * and, when T != NULL, the per-edge sender contribution T [E,C]; the node pass sums T over each
  * sender's group into gradX [N,C].  A warp covers 32*VEC channels (VEC = 4, 2 or 1 scalars per
  * lane, the widest that divides C/32 within 16 bytes); when C needs several such chunks (e.g.
@@ -165,10 +166,9 @@ int cmace_imp_fwd_f64(const double *X, const double *Y, const double *R, const i
                       const int32_t *row_ptr, int64_t nnodes, int64_t nedges, int channels,
                       double *out, cmace_stream_t stream);
 int64_t cmace_imp_bwd_scratch_elems(int64_t nedges, int channels, int is_f64);
-/* float32 with 128 channels runs the edge pass with the R rows staged through shared memory by bulk copies
- * (CMACE_IMP_STAGED=0 in the environment selects the register-prefetch kernel).  Its waits on the copies are
- * bounded; cmace_imp_staged_stalled() synchronises, returns 1 if one of them gave up since the last call (the
- * results of that launch are then incomplete) and clears the flag. */
+/* float32 with 128 channels runs the edge pass with the R rows staged through shared memory by bulk copies.
+ * Its waits on the copies are bounded (about 0.2 s); cmace_imp_staged_stalled() synchronises, returns 1 if one
+ * of them gave up since the last call (the results of that launch are then incomplete) and clears the flag. */
 int cmace_imp_staged_stalled(void);
 int cmace_imp_bwd_edge_f32(const float *X, const float *Y, const float *R, const float *G,
                            const int32_t *sender, const int32_t *row_ptr, int64_t nnodes,
@@ -247,6 +247,18 @@ int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int 
 int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node_order,
                         const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
                         double scale, float *out, int32_t *status, cmace_stream_t stream);
+
+/* Gradient of the last hidden radial activations without a gradR array (no counterpart in the reference, whose
+ * backward writes gradR [E,4,C] for its spline kernel, invariant_message_passing_impl.cu:283-291):
+ *   out[e, :] = sum_{l,c} gradR[e,l,c] * W[:, l*C + c],   gradR[e,l,c] = X[sender[e],c] * sum_{m in l} Y[m,e] * G[receiver[e],m,c]
+ * i.e. cmace_gemm3x_f32 applied to the radial-weight gradient of cmace_imp_bwd_edge_f32, whose rows are formed in
+ * the producer warps of the tensor-core kernel instead of being read from memory (call the edge pass with
+ * gradR = NULL for gradY and T).  X [Ns,C], G [Nr,16,C], Y [16,E], sender / receiver [E] sorted by receiver,
+ * C in {32,64,96,128}; packed = cmace_gemm_pack_weights_f32 of Bt = W [N, 4C] (the last radial layer, N its input
+ * width, 32 <= N <= 128, a multiple of 4); out [E, N]. */
+int cmace_gemm3x_gradr_f32(const float *X, const float *G, const float *Y, const int32_t *sender,
+                           const int32_t *receiver, const float *packed, int64_t nedges, int channels, int N,
+                           float *out, int32_t *status, cmace_stream_t stream);
 
 /* ---- hidden layers of the radial multilayer perceptron in one kernel (float32) ---------------------
  * basis [E, nb] -> h3 = silu(silu(silu(basis W1) W2) W3) [E, 64], nb in {8, 16, 24, 32}, hidden width 64: the

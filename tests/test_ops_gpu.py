@@ -475,6 +475,52 @@ def test_message_passing_with_the_last_radial_layer_inside(N, deg, C, K, nsend, 
     assert rel_err(Hg.grad, Ho.grad) < 1e-4
 
 
+@pytest.mark.parametrize("N,deg,C,K,nsend", [(300, 30, 128, 64, None), (64, 5, 32, 32, None), (200, 52, 64, 64, 260),
+                                             (50, 200, 96, 64, None), (3, 1, 128, 64, None), (1000, 40, 128, 64, None)])
+def test_message_passing_whose_backward_forms_the_radial_gradient_on_the_fly(N, deg, C, K, nsend, dev):
+    """radial_message_passing: out = message passing on R = H @ W; its backward gives grad H without a gradR array
+    (rows of gradR are formed inside the tensor-core kernel that multiplies them with W^T).  Against the oracle's
+    message passing on the float64 product: output and the gradients with respect to X, Y and H; edge counts that
+    are not a multiple of the 128-row tile, ghost senders, a receiver without edges."""
+    from cuda_mace_b200 import ops
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(200 + N)
+    Ns = N if nsend is None else nsend
+    degs = torch.poisson(torch.full((N,), float(deg)), generator=g).long()
+    degs[N // 2] = 0  # a receiver without edges
+    recv = torch.repeat_interleave(torch.arange(N), degs)
+    E = int(recv.numel())
+    send = torch.randint(0, Ns, (E,), generator=g)
+    X = torch.randn(Ns, C, generator=g, dtype=torch.float64).float().double()
+    Y = torch.randn(16, E, generator=g, dtype=torch.float64).float().double()
+    H = torch.randn(E, K, generator=g, dtype=torch.float64).float().double()
+    W = (torch.randn(K, 4 * C, generator=g, dtype=torch.float64) / K ** 0.5).float().double()
+    Xo, Yo, Ho = (t.clone().requires_grad_(True) for t in (X, Y, H))
+    ref = oops.invariant_message_passing(Xo, Yo, (Ho @ W).view(E, 4, C), send, recv, N)
+    Gr = torch.randn(N, 16, C, generator=g, dtype=torch.float64).float()
+    (ref * Gr.double()).sum().backward()
+
+    Xg, Yg, Hg = (t.float().to(dev).requires_grad_(True) for t in (X, Y, H))
+    Wg = W.float().to(dev)
+    topo = ops.EdgeTopology(send.int().to(dev), recv.int().to(dev), N, Ns)
+    out = ops.radial_message_passing(Xg, Yg, Hg, Wg, Wg.t().contiguous(), topo)
+    assert rel_err(out, ref) < 1e-5
+    assert float(out.detach()[N // 2].abs().max()) == 0.0
+    out.backward(Gr.to(dev))
+    ops.check_status()
+    assert rel_err(Xg.grad, Xo.grad) < 1e-4
+    assert rel_err(Yg.grad, Yo.grad) < 1e-4
+    assert rel_err(Hg.grad, Ho.grad) < 1e-4
+    # and the same numbers as the path that writes gradR and multiplies it afterwards
+    Xh, Yh, Hh = (t.float().to(dev).requires_grad_(True) for t in (X, Y, H))
+    R = ops.matmul3x(Hh, Wg, Wg.t().contiguous()).view(E, 4, C)
+    out2 = ops.InvariantMessagePassingTP()(Xh, Yh, R, topo.sender, topo.receiver, N, topology=topo)
+    out2.backward(Gr.to(dev))
+    assert rel_err(out2, out) < 1e-6
+    assert rel_err(Hh.grad, Hg.grad) < 1e-5
+
+
 def _edge_keys(edge_index, shift_index):
     """One sortable integer per edge: (receiver, sender, shift index triple)."""
     ei = edge_index.long().cpu()

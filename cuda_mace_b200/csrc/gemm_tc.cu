@@ -95,6 +95,7 @@ struct GemmArgs {
   const float *gx, *gg, *gy;
   const int32_t *sender, *receiver;
   int C;
+  int g_stage_bytes;            // GRADR: shared memory behind the ring and the epilogue buffers for staged G rows
   int a_act;                    // 1: apply SiLU to A while loading it
   const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
 };
@@ -253,12 +254,13 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 // Alo*Bhi product reads its A operand from there.  Shared-memory bandwidth is what the roles of this kernel compete
 // for; this takes the image's 16 KB store and its 16 KB read by the tensor core out of every pipeline item.  Needs
 // room in tensor memory next to the accumulators: two accumulators of 2 npad columns + 32 columns per ring slot.
-template <bool ACT, int MODE, bool TS = false>
+// CC: compile-time channel count of the GRADR producers (0: read it from the arguments)
+template <bool ACT, int MODE, bool TS = false, int CC = 0>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap,
                        const __grid_constant__ CUtensorMap tmap_out) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 5];
+  __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 9];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int32_t tab_words[MODE == GT_MODE_LINEAR ? sizeof(ProblemTable) / 4 : 1];
   const ProblemTable *tab = reinterpret_cast<const ProblemTable *>(tab_words);
@@ -273,6 +275,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   const uint32_t acc_empty = smem_u32(&bars[2 * GT_MAX_STAGES + 2]);
   const uint32_t tma_full = smem_u32(&bars[2 * GT_MAX_STAGES + 4]);   // + 8*s, PLAIN: A tile and B block landed
   const uint32_t b_full = smem_u32(&bars[3 * GT_MAX_STAGES + 4]);     // PLAIN with resident B: images landed
+  const uint32_t g_full = smem_u32(&bars[3 * GT_MAX_STAGES + 5]);     // + 8*buf, GRADR: staged G rows of a tile landed
+  const uint32_t g_empty = smem_u32(&bars[3 * GT_MAX_STAGES + 7]);    // + 8*buf, GRADR: every producer warp is done with them
   const int GT_STAGES = g.stages;
   const uint32_t GT_STAGE_BYTES = (uint32_t)g.stage_bytes;
 
@@ -290,6 +294,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       mbar_init(acc_empty + 8 * a, GT_EPILOGUE_WARPS);  // one arrival per epilogue warp
     }
     mbar_init(b_full, 1);
+    for (int b2 = 0; b2 < 2; b2++) {
+      mbar_init(g_full + 8 * b2, 1);                      // the loader's expect_tx arrival (+ the copy's bytes)
+      mbar_init(g_empty + 8 * b2, GT_PRODUCER_WARPS);     // one arrival per producer warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == GT_PRODUCER_WARPS) tmem_alloc(smem_u32(&tmem_base_slot), GT_TMEM_COLS);
@@ -422,64 +430,131 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     }
   } else if (MODE == GT_MODE_GRADR && warp < GT_PRODUCER_WARPS) {
     // ================================ producers, operand formed on the fly ================================
-    // Thread p owns the 16-byte chunk p % 8 of the rows p / 8 + 32 i (i < 4) of every K block, as in the LINEAR
-    // producers.  K block (l, cb) covers the columns l*C + 32 cb .. + 31 of A; the items of a tile run cb-outer,
-    // l-inner (the order of a sum does not matter to the accumulator, the producer only has to copy the matching
-    // B block), so the sender's features x = X[s, 32 cb + 4 chunk .. + 3] stay in registers for four items.  Per item
-    // and row: q = sum_{m in l} Y[m, e] * G[r, m, 32 cb + 4 chunk .. + 3] (2l + 1 fused multiply-adds on float4),
-    // a = x * q, split into hi / lo and stored.  The rows of a tile are consecutive edges of the receiver-sorted
-    // list, so the G pieces of an item belong to three or four receivers and are served by L1 after their first use;
-    // X is gathered from L2 once per tile and column block.
+    // (always the TS variant: raw values are the hi image in shared memory, the residual image goes to tensor memory)
+    // A thread owns one row of the tile = one edge e (the tensor-memory lane its warp may write) and 16 of a K
+    // block's 32 columns.  K block (l, cb) covers the columns l*C + 32 cb .. + 31 of A; the items of a tile run
+    // cb-outer, l-inner (the order of a sum does not matter to the accumulator, the producer only has to fetch the
+    // matching B block), so the sender's features x = X[s, 32 cb + 16 hf .. + 15] stay in registers for four items
+    // and the next column block's are already on their way.  Per item: q = sum_{m in l} Y[m, e] * G[r, m, same
+    // columns], a = x * q.  Y[0..15, e] lives in registers for the whole tile.  The rows of a tile are consecutive
+    // edges of the receiver-sorted list, so their receivers form a short contiguous range: the loader warp copies
+    // the G rows of that range (8 KB per receiver at C = 128, one contiguous piece) into one of two shared-memory
+    // buffers a tile ahead, and the inner loop reads them from there (warp-wide broadcasts); receivers beyond
+    // the staged range, when a tile spans many low-degree receivers, are read from global memory.
+    // The hand-over of an item (wait for the tensor-memory store, fences, arrival) is delayed until the next
+    // item's operand has been computed, so that the store's latency is covered by arithmetic.
+    const int q4 = warp & 3, hf = warp >> 2;
+    const int r = q4 * 32 + lane;
     const int p = threadIdx.x;
-    const int chunk = p & 7;
-    const int rbase = p >> 3;
-    const int C = g.C, ncb = C >> 5;
-    int stage = 0;
+    const int C = CC ? CC : g.C, ncb = C >> 5;
+    const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES + GT_EP_TMA_BYTES;
+    const uint32_t g_half = (uint32_t)g.g_stage_bytes / 2u;
+    const int max_staged = (int)(g_half / (uint32_t)(16 * C * 4));
+    uint32_t soff[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) soff[c] = (uint32_t)sw128_offset(r, 4 * hf + c);
+    const uint32_t t_lo = lo_ring + ((uint32_t)(q4 * 32) << 16) + 16u * (uint32_t)hf;
+    int stage = 0, pending_stage = -1;
     uint32_t phase = 0;
     bool ok = true;
+    auto hand_over = [&]() {
+      if (pending_stage < 0) return;
+      tmem_st_wait();
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar + 8 * pending_stage);
+      pending_stage = -1;
+    };
     TileWalker<MODE> tiles(g, tab);
     Tile T;
-    while (ok && tiles.next(T)) {
-      int64_t e[GT_ROWS_PER_THREAD];
-      const float *xrow[GT_ROWS_PER_THREAD], *grow[GT_ROWS_PER_THREAD];
+    for (int t = 0; ok && tiles.next(T); t++) {
+      const int buf = t & 1;
+      const int64_t e_last = T.row0 + GT_TILE_M - 1 < g.M ? T.row0 + GT_TILE_M - 1 : g.M - 1;
+      const int r_first = __ldg(g.receiver + T.row0);
+      const int r_count = __ldg(g.receiver + e_last) - r_first + 1;
+      const int nstaged = r_count < max_staged ? r_count : max_staged;
+      const int64_t e = T.row0 + r;
+      const bool in = e < g.M;
+      const int64_t ee = in ? e : T.row0;
+      const int my_recv = __ldg(g.receiver + ee);
+      const float *xrow = g.gx + (int64_t)__ldg(g.sender + ee) * C + 16 * hf;
+      float y[16];
 #pragma unroll
-      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
-        e[i] = T.row0 + rbase + GT_ROW_STEP * i;
-        const bool in = e[i] < g.M;
-        const int64_t ee = in ? e[i] : 0;
-        xrow[i] = g.gx + (int64_t)__ldg(g.sender + ee) * C + 4 * chunk;
-        grow[i] = g.gg + (int64_t)__ldg(g.receiver + ee) * 16 * C + 4 * chunk;
-        if (!in) e[i] = -1;
+      for (int m = 0; m < 16; m++) y[m] = in ? __ldg(g.gy + (int64_t)m * g.M + ee) : 0.f;
+      const bool staged = my_recv - r_first < nstaged;
+      const bool warp_staged = __all_sync(0xffffffffu, staged);
+      const uint32_t gs = g_stage0 + buf * g_half + (uint32_t)((my_recv - r_first) * 16 * C + 16 * hf) * 4u;
+      const float *gg = g.gg + (int64_t)my_recv * 16 * C + 16 * hf;
+      {
+        uint32_t got = 1;
+        if (lane == 0) got = mbar_wait(g_full + 8 * buf, (uint32_t)(t >> 1) & 1u) ? 1u : 0u;
+        if (!__shfl_sync(0xffffffffu, got, 0)) {
+          report(g, 8);
+          ok = false;
+          break;
+        }
       }
-      for (int cb = 0; ok && cb < ncb; cb++) {
-        float4 x[GT_ROWS_PER_THREAD];
+      // Arithmetic on register pairs: fma.rn.f32x2 / mul.rn.f32x2 / sub.rn.f32x2 handle two floats per instruction,
+      // and the inner loop of this role is bound by instruction issue (eight warps feed the tensor core).
+      unsigned long long xn2[8];
+      {
+        const ulonglong2 *xp = reinterpret_cast<const ulonglong2 *>(xrow);
 #pragma unroll
-        for (int i = 0; i < GT_ROWS_PER_THREAD; i++)
-          x[i] = e[i] >= 0 ? __ldg(reinterpret_cast<const float4 *>(xrow[i] + 32 * cb)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c < 4; c++) {
+          const ulonglong2 v = __ldg(xp + c);
+          xn2[2 * c] = v.x;
+          xn2[2 * c + 1] = v.y;
+        }
+      }
+#pragma unroll 1
+      for (int cb = 0; ok && cb < ncb; cb++) {
+        unsigned long long x2[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) x2[c] = xn2[c];
+        if (cb + 1 < ncb) {
+          const ulonglong2 *xp = reinterpret_cast<const ulonglong2 *>(xrow + 32 * (cb + 1));
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            const ulonglong2 v = __ldg(xp + c);
+            xn2[2 * c] = v.x;
+            xn2[2 * c + 1] = v.y;
+          }
+        }
 #pragma unroll
         for (int l = 0; l < 4; l++) {
-          float4 a[GT_ROWS_PER_THREAD];
+          unsigned long long a2[8];
 #pragma unroll
-          for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
-            float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (e[i] >= 0) {
+          for (int c = 0; c < 8; c++) a2[c] = 0ull;
 #pragma unroll
-              for (int m = l * l; m < (l + 1) * (l + 1); m++) {
-                const float y = __ldg(g.gy + (int64_t)m * g.M + e[i]);
-                const float4 gv = __ldg(reinterpret_cast<const float4 *>(grow[i] + m * C + 32 * cb));
-                q.x = fmaf(y, gv.x, q.x);
-                q.y = fmaf(y, gv.y, q.y);
-                q.z = fmaf(y, gv.z, q.z);
-                q.w = fmaf(y, gv.w, q.w);
+          for (int m = l * l; m < (l + 1) * (l + 1); m++) {
+            unsigned long long yy;
+            asm("mov.b64 %0, {%1, %1};" : "=l"(yy) : "f"(y[m]));
+            unsigned long long gv[8];
+            if (warp_staged) {
+              const uint32_t ga = gs + (uint32_t)(m * C + 32 * cb) * 4u;
+#pragma unroll
+              for (int c = 0; c < 4; c++)
+                asm("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(gv[2 * c]), "=l"(gv[2 * c + 1]) : "r"(ga + 16u * c));
+            } else {
+              const ulonglong2 *gp = reinterpret_cast<const ulonglong2 *>(gg + m * C + 32 * cb);
+#pragma unroll
+              for (int c = 0; c < 4; c++) {
+                const ulonglong2 v = __ldg(gp + c);
+                gv[2 * c] = v.x;
+                gv[2 * c + 1] = v.y;
               }
             }
-            a[i] = make_float4(x[i].x * q.x, x[i].y * q.y, x[i].z * q.z, x[i].w * q.w);
+#pragma unroll
+            for (int c = 0; c < 8; c++) asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a2[c]) : "l"(yy), "l"(gv[c]));
           }
-          // the slot is free once the MMAs that read it have completed
+#pragma unroll
+          for (int c = 0; c < 8; c++) asm("mul.rn.f32x2 %0, %0, %1;" : "+l"(a2[c]) : "l"(x2[c]));
+          hand_over();   // the previous item
+          // the slot (shared-memory image and tensor-memory columns) is free once the MMAs that read it completed
           uint32_t got = 1;
           if (lane == 0) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
-          got = __shfl_sync(0xffffffffu, got, 0);
-          if (!got) {
+          if (!__shfl_sync(0xffffffffu, got, 0)) {
             report(g, 1);
             ok = false;
             break;
@@ -489,34 +564,36 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             const int kb = l * ncb + cb;
             const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) + (int64_t)kb * (2 * (int64_t)b_image);
             mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
-            bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
+            bulk_copy_g2s(sA + GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
           }
+          // hi image: the raw values (the tensor core ignores the low 13 mantissa bits of its operands);
+          // residual image: a - trunc(a), exact in float32 and at most 2^-10 |a|; it is read with the same truncation,
+          // which leaves an error below 2^-20 |a| per element
+          uint32_t lo[16];
 #pragma unroll
-          for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
-            const float4 v = a[i];
-            float4 lo;
-            // the raw value serves as the hi image (the tensor core ignores the low 13 mantissa bits)
-            lo.x = to_tf32(v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u));
-            lo.y = to_tf32(v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u));
-            lo.z = to_tf32(v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u));
-            lo.w = to_tf32(v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u));
-            const uint32_t off = (uint32_t)sw128_offset(rbase + GT_ROW_STEP * i, chunk);
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                         : "memory");
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + GT_A_SLAB + off), "f"(lo.x), "f"(lo.y),
-                         "f"(lo.z), "f"(lo.w)
-                         : "memory");
+          for (int c = 0; c < 4; c++) {
+            asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(sA + soff[c]), "l"(a2[2 * c]), "l"(a2[2 * c + 1]) : "memory");
+#pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+              unsigned long long d;
+              const unsigned long long tr = a2[2 * c + h2] & 0xFFFFE000FFFFE000ull;
+              asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a2[2 * c + h2]), "l"(tr));
+              asm("mov.b64 {%0, %1}, %2;" : "=r"(lo[4 * c + 2 * h2]), "=r"(lo[4 * c + 2 * h2 + 1]) : "l"(d));
+            }
           }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+          tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
+          pending_stage = stage;
           if (++stage == GT_STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
       }
+      // this warp no longer reads the tile's G rows: the loader may overwrite the buffer
+      __syncwarp();
+      if (lane == 0) mbar_arrive(g_empty + 8 * buf);
     }
+    hand_over();
   } else if (MODE == GT_MODE_LINEAR && warp < GT_PRODUCER_WARPS) {
     // ================================ producers ================================
     // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
@@ -630,6 +707,33 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // stage's barrier: the TMA tile load of A (128 rows x 32 columns, 128-byte swizzle, zeros outside the
     // matrix) into the hi image, and the bulk copy of the matching pre-packed B block.  Nothing waits in
     // registers for HBM; the ring depth sets the bytes in flight.
+    if (MODE == GT_MODE_GRADR && lane == 0) {
+      // one bulk copy per tile: the G rows of the tile's receiver range (contiguous) into the buffer the producers
+      // released two tiles ago
+      const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES + GT_EP_TMA_BYTES;
+      const uint32_t g_half = (uint32_t)g.g_stage_bytes / 2u;
+      const int per_receiver = 16 * g.C * 4;
+      const int max_staged = (int)(g_half / (uint32_t)per_receiver);
+      TileWalker<MODE> tiles(g, tab);
+      Tile T;
+      for (int t = 0; tiles.next(T); t++) {
+        const int buf = t & 1;
+        if (t >= 2 && !mbar_wait(g_empty + 8 * buf, ((uint32_t)(t >> 1) & 1u) ^ 1u)) {
+          report(g, 7);
+          break;
+        }
+        const int64_t e_last = T.row0 + GT_TILE_M - 1 < g.M ? T.row0 + GT_TILE_M - 1 : g.M - 1;
+        const int r_first = __ldg(g.receiver + T.row0);
+        const int r_count = __ldg(g.receiver + e_last) - r_first + 1;
+        const uint32_t bytes = (uint32_t)((r_count < max_staged ? r_count : max_staged) * per_receiver);
+        const unsigned char *src = reinterpret_cast<const unsigned char *>(g.gg + (int64_t)r_first * 16 * g.C);
+        mbar_arrive_expect_tx(g_full + 8 * buf, bytes);
+        for (uint32_t off = 0; off < bytes; off += 8192u) {
+          const uint32_t n = bytes - off < 8192u ? bytes - off : 8192u;
+          bulk_copy_g2s(g_stage0 + buf * g_half + off, src + off, n, g_full + 8 * buf);
+        }
+      }
+    }
     if (MODE == GT_MODE_PLAIN && lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -1049,7 +1153,8 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   const bool act = g.a_act != 0 || g.ep_z != nullptr;
   // residual image of A in tensor memory when at least four ring slots fit next to the two accumulators
   const int ts_slots = (GT_TMEM_COLS - 4 * g.npad) / 32;
-  g.a_lo_tmem = (g.mode == GT_MODE_PLAIN && !act && ts_slots >= 4) ? 1 : 0;
+  g.a_lo_tmem = ((g.mode == GT_MODE_PLAIN && !act && ts_slots >= 4) || g.mode == GT_MODE_GRADR) ? 1 : 0;
+  if (g.mode == GT_MODE_GRADR && ts_slots < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
   g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   // PLAIN: tile stores by TMA from a 4 KB staging buffer per epilogue warp (N >= 32: the box is 32 columns wide);
   // LINEAR: the transpose buffers of its epilogue
@@ -1060,8 +1165,17 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   g.stages = (budget - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
   if (g.a_lo_tmem && g.stages > ts_slots) g.stages = ts_slots;
+  g.g_stage_bytes = 0;
+  if (g.mode == GT_MODE_GRADR) {
+    // three ring slots are enough here (the producers compute, nothing waits for HBM); what is left of shared
+    // memory holds the G rows of a tile's receivers, twice (the next tile's are copied while this one is consumed)
+    const int per_receiver = 16 * g.C * 4;
+    if (g.stages > 3) g.stages = 3;
+    g.g_stage_bytes = ((budget - ep_bytes - 1024 - g.stages * g.stage_bytes) / (2 * per_receiver)) * 2 * per_receiver;
+    if (g.g_stage_bytes < 0) g.g_stage_bytes = 0;
+  }
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
-  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024;
+  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024 + (size_t)g.g_stage_bytes;
   CUtensorMap tmap, tmap_out;
   memset(&tmap, 0, sizeof(tmap));
   memset(&tmap_out, 0, sizeof(tmap_out));
@@ -1072,7 +1186,8 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     if (int rc = encode_out_tensor_map(&tmap_out, g.out, g.M, g.N, what)) return rc;
   }
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
-              : g.mode == GT_MODE_GRADR ? gemm3x_tf32_kernel<false, GT_MODE_GRADR>
+              : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<false, GT_MODE_GRADR, true, 128>
+                                                       : gemm3x_tf32_kernel<false, GT_MODE_GRADR, true>)
               : act                    ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN>
               : g.a_lo_tmem            ? gemm3x_tf32_kernel<false, GT_MODE_PLAIN, true>
                                        : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>;

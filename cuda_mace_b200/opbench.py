@@ -5,6 +5,7 @@
 symcon  SymmetricContraction, N = 4096 atoms, 128 channels, 10 species, forward and forward+backward
 imp     InvariantMessagePassing, N = 8192 receivers, Poisson(30) edges each, 128 channels, forward and backward
 fused   message passing with the last radial layer inside (float32), N receivers with Poisson(52) edges each
+gradr   gradient of the last hidden radial layer from operands formed inside the tensor-core kernel (float32)
 linear  Linear, N = 3000 and N = 64000 nodes, 128 channels; ElementalLinear, N = 64000, 4 elements
 edge    spherical harmonics and the tabulated (cubic spline) radial weights, E = 157 000 and 3 331 524 edges
 radial  the three hidden radial layers in one kernel (float32), E edges
@@ -120,6 +121,26 @@ def bench_fused(dtype, iters, dev, nodes):
     _emit("fused", f"N={N} E={E} C={C} K={K} forward only", t, 4 * (E * K + 16 * E + N * C + 16 * N * C) + 8 * E)
 
 
+def bench_gradr(dtype, iters, dev, nodes):
+    """Backward of the last radial layer + message passing without a gradR array: the tensor-core product whose
+    A operand is formed on the fly, and the edge pass that no longer writes gradR; Poisson(52) receivers."""
+    if dtype != torch.float32:
+        return
+    gen = torch.Generator().manual_seed(5)
+    N, C, K = nodes, 128, 64
+    send, recv = _graph(N, 52, gen)
+    E = send.numel()
+    X = torch.randn(N, C, generator=gen).to(dev)
+    Y = torch.randn(16, E, generator=gen).to(dev)
+    G = torch.randn(N, 16, C, generator=gen).to(dev)
+    W = (torch.randn(K, 4 * C, generator=gen) / 8).to(dev)
+    topo = ops.EdgeTopology(send.to(dev), recv.to(dev), N, N)
+    t = _time(lambda: ops.radial_gradient_product(X, G, Y, W, topo), iters)
+    ops.check_status()
+    _emit("gradr", f"N={N} E={E} C={C} K={K} grad H from operands formed on the fly", t,
+          4 * (E * K + 16 * E + N * C + 16 * N * C + K * 4 * C) + 8 * E, gflops=round(3 * 2 * E * 4 * C * K / t / 1e6, 1))
+
+
 def bench_linear(dtype, iters, dev):
     gen = torch.Generator().manual_seed(3)
     C = 128
@@ -211,7 +232,7 @@ def bench_nlist(iters, dev, nodes):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="all", choices=["all", "symcon", "imp", "fused", "linear", "edge", "radial", "nlist"])
+    ap.add_argument("--op", default="all", choices=["all", "symcon", "imp", "fused", "gradr", "linear", "edge", "radial", "nlist"])
     ap.add_argument("--graph", default="poisson", choices=["poisson", "symmetric"], help="edge list of the imp case")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--iters", type=int, default=20)
@@ -232,6 +253,8 @@ def main():
         bench_edge(dtype, args.iters, dev)
     if args.op in ("all", "radial"):
         bench_radial(dtype, args.iters, dev, args.edges)
+    if args.op in ("all", "gradr"):
+        bench_gradr(dtype, args.iters, dev, args.nodes)
     if args.op in ("all", "fused"):
         bench_fused(dtype, args.iters, dev, args.nodes)
     if args.op in ("all", "nlist"):

@@ -470,12 +470,18 @@ class _RadialIMPFunction(torch.autograd.Function):
             gradX = torch.empty(topo.nsenders, C, dtype=X.dtype, device=X.device)
             _abi.call("cmace_imp_bwd_node_f32", _ptr(T), _ptr(perm), _ptr(send_ptr), topo.nsenders, C, _ptr(gradX),
                       _stream())
-        gradH = None
-        if ctx.needs_input_grad[2]:
-            gradH = torch.empty(E, K, dtype=torch.float32, device=X.device)
-            _abi.call("cmace_gemm3x_gradr_f32", _ptr(X), _ptr(G), _ptr(Y), _ptr(topo.sender), _ptr(topo.receiver),
-                      _ptr(_pack(W)), E, C, K, _ptr(gradH), _ptr(_status_tensor(X.device)), _stream())
+        gradH = radial_gradient_product(X, G, Y, W, topo) if ctx.needs_input_grad[2] else None
         return gradX, gradY, gradH, None, None, None
+
+
+def radial_gradient_product(X, G, Y, W, topo):
+    """grad H [E,K] = gradR @ W^T with gradR[e,l,c] = X[sender(e),c] * sum_{m in l} Y[m,e] * G[receiver(e),m,c] formed
+    inside the tensor-core kernel (never written).  X [Ns,C], G [N,16,C], Y [16,E], W [K,4C], float32."""
+    E, C, K = topo.nedges, X.shape[1], W.shape[0]
+    gradH = torch.empty(E, K, dtype=torch.float32, device=X.device)
+    _abi.call("cmace_gemm3x_gradr_f32", _ptr(X), _ptr(G), _ptr(Y), _ptr(topo.sender), _ptr(topo.receiver),
+              _ptr(_pack(W)), E, C, K, _ptr(gradH), _ptr(_status_tensor(X.device)), _stream())
+    return gradH
 
 
 def radial_message_passing_ok(dtype, C, K):

@@ -51,8 +51,9 @@ SIGNATURES = {
     "cmace_gemm_f64": [_P, _P, _L, _I, _I, _D, _P, _P],
     "cmace_gemm_packed_floats": [_I, _I, _I],
     "cmace_gemm_pack_weights_f32": [_P, _I, _I, _I, _P, _P],
-    "cmace_gemm3x_f32": [_P, _P, _L, _I, _I, _D, _I, _P, _P, _P, _P],
+    "cmace_gemm3x_f32": [_P, _P, _L, _I, _I, _D, _P, _P, _P],
     "cmace_linear_tc_f32": [_P, _P, _P, _P, _I, _L, _I, _I, _D, _P, _P, _P],
+    "cmace_bounded_wait_probe": [_P, _I, _D, _P],
     "cmace_gemm3x_gradr_f32": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _P, _P, _P],
     "cmace_radial_hidden_saved_floats": [_L],
     "cmace_radial_hidden_fwd_f32": [_P, _I, _P, _P, _P, _L, _P, _P, _P, _P],
@@ -103,7 +104,7 @@ KERNEL_LAUNCHES = {
     "cmace_edge_vectors_fwd": 1, "cmace_edge_vectors_bwd": 1,
     "cmace_spline_fwd": 1, "cmace_spline_bwd": 1, "cmace_imp_fwd": 1, "cmace_imp_bwd_edge": 1, "cmace_imp_bwd_edge_f64_noalloc": 2,
     "cmace_imp_bwd_node": 1, "cmace_linear": 1, "cmace_symcon_fwd": 1, "cmace_symcon_bwd": 1,
-    "cmace_gemm_pack_weights": 1, "cmace_gemm3x": 1, "cmace_gemm": 1, "cmace_gemm3x_gradr": 1, "cmace_linear_tc": 1,
+    "cmace_gemm_pack_weights": 1, "cmace_gemm3x": 1, "cmace_gemm": 1, "cmace_gemm3x_gradr": 1, "cmace_bounded_wait_probe": 1, "cmace_linear_tc": 1,
     "cmace_radial_hidden_fwd": 1, "cmace_radial_hidden_bwd": 1, "cmace_imp_radial_fused_fwd": 1,
     "cmace_nl_cell_ids": 1, "cmace_nl_count": 1, "cmace_exclusive_scan_i32": 1, "cmace_nl_fill": 1,
 }

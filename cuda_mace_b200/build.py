@@ -1,4 +1,4 @@
-"""Builds the C-ABI library (and the host-compiled math check library) in-tree with nvcc.
+"""Builds the C-ABI library in-tree with nvcc, and the TorchScript classes on top of it with g++.
 
     python -m cuda_mace_b200.build [--force] [-v]
 
@@ -17,7 +17,6 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(LIB_DIR, "libcuda_mace_b200.so")
-HOSTCHECK_PATH = os.path.join(LIB_DIR, "libcmace_hostcheck.so")
 TORCH_LIB_PATH = os.path.join(LIB_DIR, "libcuda_mace_b200_torch.so")
 
 NVCC_FLAGS = [
@@ -67,14 +66,6 @@ def build(force=False, verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    # host-compiled copy of the per-edge math, used by the CPU tests of the kernel formulas
-    hc_src = os.path.join(CSRC, "hostcheck.cpp")
-    if os.path.exists(hc_src) and (force or not os.path.exists(HOSTCHECK_PATH)
-                                   or os.path.getmtime(HOSTCHECK_PATH) < max(os.path.getmtime(hc_src), hdr_time)):
-        r = subprocess.run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", HOSTCHECK_PATH, hc_src],
-                           capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"g++ failed for hostcheck.cpp:\n{r.stdout}\n{r.stderr}")
     build_torch_classes(force)
     return LIB_PATH
 

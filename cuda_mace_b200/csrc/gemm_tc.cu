@@ -27,8 +27,8 @@
 //              after the last K block of a tile, to the accumulator's "full" barrier.
 //   warps 9-16 epilogue: tcgen05.ld of the accumulator, add the two column ranges, scale, store, release the
 //              accumulator.  PLAIN: a warp writes its 32 rows x 32 columns into a swizzled 4 KB staging buffer
-//              and one thread stores it by TMA (the engine clips what lies outside the matrix); with the
-//              activation-fused variant or N < 32, 16x256b loads stored straight from registers.  LINEAR:
+//              and one thread stores it by TMA (the engine clips what lies outside the matrix); with
+//              N < 32, 16x256b loads stored straight from registers.  LINEAR:
 //              32x32b loads (a thread holds one row, 16 columns at a time), transposed through a per-warp
 //              shared-memory buffer, stored as 64-byte row pieces.
 // Accumulators are double buffered in tensor memory (2 x 256 columns), so the epilogue of tile t
@@ -96,8 +96,6 @@ struct GemmArgs {
   const int32_t *sender, *receiver;
   int C;
   int g_stage_bytes;            // GRADR: shared memory behind the ring and the epilogue buffers for staged G rows
-  int a_act;                    // 1: apply SiLU to A while loading it
-  const float *ep_z;            // when set: out = scale * acc * silu'(ep_z[row, col]), ep_z laid out like out
 };
 
 // ---- tile bookkeeping ----------------------------------------------------------------------------
@@ -248,14 +246,12 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
   if (g.status) atomicCAS(g.status, 0, code);
 }
 
-// ACT: the activation switches (a_act, ep_z) are compiled in only for the variant that uses them, the plain
-// variant measured 14 % faster without the extra code in its producer and epilogue loops
 // TS: the residual image lo = tf32(a - trunc(a)) of A goes to tensor memory instead of shared memory and the
 // Alo*Bhi product reads its A operand from there.  Shared-memory bandwidth is what the roles of this kernel compete
 // for; this takes the image's 16 KB store and its 16 KB read by the tensor core out of every pipeline item.  Needs
 // room in tensor memory next to the accumulators: two accumulators of 2 npad columns + 32 columns per ring slot.
 // CC: compile-time channel count of the GRADR producers (0: read it from the arguments)
-template <bool ACT, int MODE, bool TS = false, int CC = 0>
+template <int MODE, bool TS = false, int CC = 0>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap,
                        const __grid_constant__ CUtensorMap tmap_out) {
@@ -401,16 +397,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                        : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
                        : "r"(sA + soff[i])
                        : "memory");
-          if (ACT && g.a_act) {
-            // the activated values replace the raw ones in the hi image
-            a.x = silu_n(a.x);
-            a.y = silu_n(a.y);
-            a.z = silu_n(a.z);
-            a.w = silu_n(a.w);
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + soff[i]), "f"(a.x), "f"(a.y), "f"(a.z),
-                         "f"(a.w)
-                         : "memory");
-          }
           lo.x = to_tf32(a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u));
           lo.y = to_tf32(a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u));
           lo.z = to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u));
@@ -655,12 +641,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
         const int r = rbase + GT_ROW_STEP * i;
         float4 a = v[i], hi, lo;
-        if (ACT && g.a_act) {
-          a.x = silu_n(a.x);
-          a.y = silu_n(a.y);
-          a.z = silu_n(a.z);
-          a.w = silu_n(a.w);
-        }
         hi.x = to_tf32(a.x); lo.x = to_tf32(a.x - hi.x);
         hi.y = to_tf32(a.y); lo.y = to_tf32(a.y - hi.y);
         hi.z = to_tf32(a.z); lo.z = to_tf32(a.z - hi.z);
@@ -887,7 +867,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * acc_stride + ((uint32_t)(q * 32) << 16);
-      if (MODE != GT_MODE_LINEAR && !ACT && g.ep_tma) {
+      if (MODE != GT_MODE_LINEAR && g.ep_tma) {
         // Tile store by TMA.  Global stores from registers cost the load/store data pipe one pass per 32-byte sector
         // whatever their shape (64 KB per tile = 2048 passes, the pipe measured 70 % busy on [E,64]x[64,512]); here
         // a warp writes its 32 rows x 32 columns into a swizzled 4 KB staging buffer (eight conflict-free 16-byte
@@ -963,22 +943,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 #pragma unroll
             for (int m = 0; m < 2; m++) {
               const bool col_ok = cbase + 8 * m < ncols;
-              if (ACT && g.ep_z != nullptr) {
-                if (gra >= 0 && col_ok) {
-                  const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (pa - g.out) + 8 * m));
-                  oa[m].x *= silu_n_grad(z.x);
-                  oa[m].y *= silu_n_grad(z.y);
-                  oa[m].z *= silu_n_grad(z.z);
-                  oa[m].w *= silu_n_grad(z.w);
-                }
-                if (grb >= 0 && col_ok) {
-                  const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (pb - g.out) + 8 * m));
-                  ob[m].x *= silu_n_grad(z.x);
-                  ob[m].y *= silu_n_grad(z.y);
-                  ob[m].z *= silu_n_grad(z.z);
-                  ob[m].w *= silu_n_grad(z.w);
-                }
-              }
               if (gra >= 0 && col_ok) *reinterpret_cast<float4 *>(pa + 8 * m) = oa[m];
               if (grb >= 0 && col_ok) *reinterpret_cast<float4 *>(pb + 8 * m) = ob[m];
             }
@@ -1017,13 +981,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
               const int rr = it * 8 + (lane >> 2);
               float4 o = *reinterpret_cast<const float4 *>(ep_buf + rr * GT_EP_STRIDE + (lane & 3) * 4);
               if (rowptr[it] != nullptr && col_ok) {
-                if (ACT && g.ep_z != nullptr) {
-                  const float4 z = __ldg(reinterpret_cast<const float4 *>(g.ep_z + (rowptr[it] - g.out) + cc));
-                  o.x *= silu_n_grad(z.x);
-                  o.y *= silu_n_grad(z.y);
-                  o.z *= silu_n_grad(z.z);
-                  o.w *= silu_n_grad(z.w);
-                }
                 *reinterpret_cast<float4 *>(rowptr[it] + cc) = o;
               }
             }
@@ -1038,12 +995,34 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       acc ^= 1;
     }
     // the copy engine still reads this warp's staging buffer and writes its tile: wait before the CTA retires
-    if (MODE != GT_MODE_LINEAR && !ACT && g.ep_tma && lane == 0) tma_store_wait_all();
+    if (MODE != GT_MODE_LINEAR && g.ep_tma && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == GT_PRODUCER_WARPS) tmem_dealloc(tmem_base, GT_TMEM_COLS);
+}
+
+// ---- a wait that runs out ---------------------------------------------------------------------------
+// One warp waits, with the same bounded wait every role of the kernels above uses, on an mbarrier that nothing ever
+// completes; when the wait gives up the kernel records `code` in *status and returns normally.  This is how the
+// time-out path is exercised on a GPU without hanging or faulting it (tests, health checks).
+__global__ void bounded_wait_probe_kernel(int32_t *status, int code, long long limit_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  uint32_t got = 1;
+  if (threadIdx.x == 0) {
+    got = mbar_try_wait(b, 0) ? 1u : 0u;
+    const long long t0 = clock64();
+    while (!got && clock64() - t0 < limit_cycles) got = mbar_try_wait(b, 0) ? 1u : 0u;
+  }
+  got = __shfl_sync(0xffffffffu, got, 0);
+  if (!got && threadIdx.x == 0 && status) atomicCAS(status, 0, code);
 }
 
 // ---- weight packing ---------------------------------------------------------------------------------
@@ -1150,15 +1129,14 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   // streams A, instead of fetching the same B block from L2 again for every 128-row tile
   const int b_all = g.k_blocks * 2 * g.npad * 128;
   g.b_resident = (g.mode == GT_MODE_PLAIN && b_all <= 64 * 1024 && num_sms >= g.n_tiles) ? b_all : 0;
-  const bool act = g.a_act != 0 || g.ep_z != nullptr;
   // residual image of A in tensor memory when at least four ring slots fit next to the two accumulators
   const int ts_slots = (GT_TMEM_COLS - 4 * g.npad) / 32;
-  g.a_lo_tmem = ((g.mode == GT_MODE_PLAIN && !act && ts_slots >= 4) || g.mode == GT_MODE_GRADR) ? 1 : 0;
+  g.a_lo_tmem = ((g.mode == GT_MODE_PLAIN && ts_slots >= 4) || g.mode == GT_MODE_GRADR) ? 1 : 0;
   if (g.mode == GT_MODE_GRADR && ts_slots < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
   g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   // PLAIN: tile stores by TMA from a 4 KB staging buffer per epilogue warp (N >= 32: the box is 32 columns wide);
   // LINEAR: the transpose buffers of its epilogue
-  g.ep_tma = (g.mode != GT_MODE_LINEAR && !act && g.N >= 32) ? 1 : 0;
+  g.ep_tma = (g.mode != GT_MODE_LINEAR && g.N >= 32) ? 1 : 0;
   const int ep_bytes = g.mode != GT_MODE_LINEAR ? (g.ep_tma ? GT_EP_TMA_BYTES : 0) : GT_EP_BYTES;
   // the LINEAR variant holds its problem table in static shared memory
   const int budget = GT_SMEM_BUDGET - (g.mode == GT_MODE_LINEAR ? (int)sizeof(ProblemTable) + 1024 : 0);
@@ -1185,12 +1163,11 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (g.ep_tma) {
     if (int rc = encode_out_tensor_map(&tmap_out, g.out, g.M, g.N, what)) return rc;
   }
-  auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<false, GT_MODE_LINEAR>
-              : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<false, GT_MODE_GRADR, true, 128>
-                                                       : gemm3x_tf32_kernel<false, GT_MODE_GRADR, true>)
-              : act                    ? gemm3x_tf32_kernel<true, GT_MODE_PLAIN>
-              : g.a_lo_tmem            ? gemm3x_tf32_kernel<false, GT_MODE_PLAIN, true>
-                                       : gemm3x_tf32_kernel<false, GT_MODE_PLAIN>;
+  auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<GT_MODE_LINEAR>
+              : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<GT_MODE_GRADR, true, 128>
+                                                       : gemm3x_tf32_kernel<GT_MODE_GRADR, true>)
+              : g.a_lo_tmem            ? gemm3x_tf32_kernel<GT_MODE_PLAIN, true>
+                                       : gemm3x_tf32_kernel<GT_MODE_PLAIN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   if (g.total_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many tiles", what);
@@ -1229,23 +1206,34 @@ int cmace_gemm_pack_weights_f32(const float *Bt, int nmat, int N, int K, float *
   return check_launch("cmace_gemm_pack_weights");
 }
 
-int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale, int a_act,
-                     const float *ep_z, float *out, int32_t *status, cmace_stream_t stream) {
+int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale, float *out,
+                     int32_t *status, cmace_stream_t stream) {
   if (M < 0 || K < 1 || N < 1) return fail(CMACE_ERR_ARG, "cmace_gemm3x: bad size");
   if (K % 8 != 0 || N % 4 != 0)
     return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm3x: K must be a multiple of 8 and N a multiple of 4");
   if (M == 0) return CMACE_OK;
   if (!A || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_gemm3x: null pointer");
-  if (!aligned16(A) || !aligned16(packed) || !aligned16(out) || !aligned16(ep_z))
+  if (!aligned16(A) || !aligned16(packed) || !aligned16(out))
     return fail(CMACE_ERR_ARG, "cmace_gemm3x: pointers must be 16-byte aligned");
   const PackGeom p = pack_geom(N, K);
   GemmArgs g{};
   g.A = A; g.packed = packed; g.out = out; g.status = status;
-  g.a_act = a_act ? 1 : 0; g.ep_z = ep_z;
   g.M = M; g.K = K; g.N = N; g.nelements = 1; g.mode = GT_MODE_PLAIN; g.scale = (float)scale;
   g.n_tiles = p.n_tiles; g.k_blocks = p.k_blocks; g.npad = p.npad;
   g.total_tiles = ((M + GT_TILE_M - 1) / GT_TILE_M) * p.n_tiles;
   return gemm_launch(g, "cmace_gemm3x", (cudaStream_t)stream);
+}
+
+int cmace_bounded_wait_probe(int32_t *status, int code, double limit_seconds, cmace_stream_t stream) {
+  if (!status || code == 0) return fail(CMACE_ERR_ARG, "cmace_bounded_wait_probe: status pointer and a non-zero code needed");
+  if (!(limit_seconds > 0.0) || limit_seconds > 1.0)
+    return fail(CMACE_ERR_ARG, "cmace_bounded_wait_probe: the limit must lie in (0, 1] seconds");
+  int dev = 0, khz = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+  if (khz <= 0) khz = 1965000;
+  bounded_wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, code, (long long)(limit_seconds * 1e3 * khz));
+  return check_launch("cmace_bounded_wait_probe");
 }
 
 int cmace_gemm3x_gradr_f32(const float *X, const float *G, const float *Y, const int32_t *sender,

@@ -195,11 +195,6 @@ __device__ __forceinline__ float to_tf32(float x) {
 __device__ __forceinline__ float sigmoid_fast(float x) {
   return __fdividef(1.0f, 1.0f + exp2f(-1.4426950408889634f * x));
 }
-__device__ __forceinline__ float silu_n(float x) { return x * sigmoid_fast(x); }
-__device__ __forceinline__ float silu_n_grad(float x) {
-  const float s = sigmoid_fast(x);
-  return s * fmaf(x, 1.0f - s, 1.0f);
-}
 
 // byte offset of the 16-byte chunk c (0..7) of row r inside a swizzled image
 __device__ __host__ __forceinline__ int sw128_offset(int r, int c) {

@@ -17,6 +17,8 @@
 #include <torch/custom_class.h>
 #include <torch/script.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -29,6 +31,13 @@ using torch::autograd::AutogradContext;
 using torch::autograd::variable_list;
 
 namespace {
+
+// NVTX range around every autograd forward / backward, named after the operator (the reference pushes a range
+// "cuda_mace" with a colour per operator, include/utils.h:9-21): filters for ncu / nsys, no cost when no tool listens.
+struct Range {
+  explicit Range(const char *name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+};
 
 void check(int rc, const char *what) { TORCH_CHECK(rc == 0, what, " failed (", rc, "): ", cmace_last_error()); }
 
@@ -108,6 +117,7 @@ class IMPAutograd : public torch::autograd::Function<IMPAutograd> {
  public:
   static Tensor forward(AutogradContext *ctx, Tensor X, Tensor Y, Tensor radial, Tensor sender_list,
                         Tensor receiver_list, int64_t nnodes) {
+    Range nvtx("cuda_mace_b200::message_passing::forward");
     check_cuda(X, "X");
     c10::cuda::CUDAGuard guard(X.device());
     X = X.contiguous();
@@ -135,6 +145,7 @@ class IMPAutograd : public torch::autograd::Function<IMPAutograd> {
   }
 
   static variable_list backward(AutogradContext *ctx, variable_list grads) {
+    Range nvtx("cuda_mace_b200::message_passing::backward");
     auto saved = ctx->get_saved_variables();
     Tensor X = saved[0], Y = saved[1], radial = saved[2];
     Topology topo;
@@ -242,6 +253,7 @@ class LinearAutograd : public torch::autograd::Function<LinearAutograd> {
  public:
   static Tensor forward(AutogradContext *ctx, Tensor X, Tensor W, Tensor W_T, Tensor node_order, Tensor elem_start,
                         int64_t nelements) {
+    Range nvtx("cuda_mace_b200::linear::forward");
     check_cuda(X, "X");
     c10::cuda::CUDAGuard guard(X.device());
     const double scale = 1.0 / std::sqrt((double)X.size(2));  // the path weight of linear_impl.cu:33
@@ -251,6 +263,7 @@ class LinearAutograd : public torch::autograd::Function<LinearAutograd> {
     return linear_call(X, W, W_T, node_order, elem_start, nelements, scale);
   }
   static variable_list backward(AutogradContext *ctx, variable_list grads) {
+    Range nvtx("cuda_mace_b200::linear::backward");
     auto saved = ctx->get_saved_variables();
     c10::cuda::CUDAGuard guard(grads[0].device());
     Tensor dX = linear_call(grads[0], saved[1], saved[0], saved[2], saved[3], ctx->saved_data["nelements"].toInt(),
@@ -309,6 +322,7 @@ class SymConAutograd : public torch::autograd::Function<SymConAutograd> {
  public:
   static Tensor forward(AutogradContext *ctx, Tensor X, Tensor atom_types, Tensor W3, Tensor W2, Tensor W1,
                         c10::intrusive_ptr<PlanBox> box) {
+    Range nvtx("cuda_mace_b200::symmetric_contraction::forward");
     c10::cuda::CUDAGuard guard(X.device());
     X = X.contiguous();
     const int64_t N = X.size(0), C = X.size(2), Z = W3.size(0);
@@ -329,6 +343,7 @@ class SymConAutograd : public torch::autograd::Function<SymConAutograd> {
     return out;
   }
   static variable_list backward(AutogradContext *ctx, variable_list grads) {
+    Range nvtx("cuda_mace_b200::symmetric_contraction::backward");
     auto s = ctx->get_saved_variables();
     Tensor X = s[0], atom_types = s[1], W3 = s[2], W2 = s[3], W1 = s[4];
     c10::cuda::CUDAGuard guard(X.device());
@@ -355,6 +370,7 @@ class SymConAutograd : public torch::autograd::Function<SymConAutograd> {
 class SphAutograd : public torch::autograd::Function<SphAutograd> {
  public:
   static Tensor forward(AutogradContext *ctx, Tensor xyz) {
+    Range nvtx("cuda_mace_b200::spherical_harmonics::forward");
     check_cuda(xyz, "xyz");
     c10::cuda::CUDAGuard guard(xyz.device());
     xyz = xyz.contiguous();
@@ -369,6 +385,7 @@ class SphAutograd : public torch::autograd::Function<SphAutograd> {
     return Y;
   }
   static variable_list backward(AutogradContext *ctx, variable_list grads) {
+    Range nvtx("cuda_mace_b200::spherical_harmonics::backward");
     Tensor xyz = ctx->get_saved_variables()[0];
     c10::cuda::CUDAGuard guard(xyz.device());
     Tensor gY = grads[0].contiguous();
@@ -388,6 +405,7 @@ class SphAutograd : public torch::autograd::Function<SphAutograd> {
 class SplineAutograd : public torch::autograd::Function<SplineAutograd> {
  public:
   static Tensor forward(AutogradContext *ctx, Tensor r, Tensor r_knots, Tensor coeffs, double r_width, double r_max) {
+    Range nvtx("cuda_mace_b200::cubic_spline::forward");
     check_cuda(r, "r");
     c10::cuda::CUDAGuard guard(r.device());
     r = r.contiguous();
@@ -410,6 +428,7 @@ class SplineAutograd : public torch::autograd::Function<SplineAutograd> {
     return R;
   }
   static variable_list backward(AutogradContext *ctx, variable_list grads) {
+    Range nvtx("cuda_mace_b200::cubic_spline::backward");
     auto s = ctx->get_saved_variables();
     Tensor r = s[0], r_knots = s[1], coeffs = s[2];
     c10::cuda::CUDAGuard guard(r.device());

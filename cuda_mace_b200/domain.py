@@ -113,6 +113,29 @@ class HaloPlan:
             self._ghost_shift[dtype] = torch.as_tensor(self.dom.ghost_shift, dtype=dtype).to(self.device)
         return self._ghost_shift[dtype]
 
+    def verify(self):
+        """Host-side check, once per decomposition: every rank's send counts must equal what its neighbours expect
+        to receive (a wrong halo size would otherwise surface as a truncated or hanging receive).  Collective over
+        the group; raises ValueError on every rank when any pair disagrees."""
+        d = self.dom
+        if d.nranks == 1:
+            return self
+        mine = torch.tensor([self.send_down.numel(), self.send_up.numel(), d.recv_down[1], d.recv_up[1]],
+                            dtype=torch.int64, device=self.device)
+        every = [torch.zeros_like(mine) for _ in range(d.nranks)]
+        dist.all_gather(every, mine, group=self.group)
+        counts = torch.stack(every).cpu().tolist()
+        bad = []
+        for r in range(d.nranks):
+            down, up = (r - 1) % d.nranks, (r + 1) % d.nranks
+            if counts[r][1] != counts[up][2]:
+                bad.append(f"rank {r} sends {counts[r][1]} rows up, rank {up} expects {counts[up][2]}")
+            if counts[r][0] != counts[down][3]:
+                bad.append(f"rank {r} sends {counts[r][0]} rows down, rank {down} expects {counts[down][3]}")
+        if bad:
+            raise ValueError("halo plan mismatch: " + "; ".join(bad))
+        return self
+
     def _exchange(self, out_down, out_up, in_from_down, in_from_up):
         """Sends out_down / out_up to the lower / upper neighbour and receives their counterparts.
         Both neighbours may be the same rank (two ranks): messages are matched by posting order, the

@@ -22,7 +22,7 @@ class EnergyForceEvaluator:
         self.model = model
         self.dom = dom
         self.device = torch.device(device)
-        self.plan = _domain.HaloPlan(dom, self.device, group)
+        self.plan = _domain.HaloPlan(dom, self.device, group).verify()
         self.species = None
         self.edge_index = None
         self.shifts = None

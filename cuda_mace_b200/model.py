@@ -137,8 +137,6 @@ class InvariantMACE(torch.nn.Module):
             return L.spline(lengths)
         Ws = [getattr(L, f"W_radial{i}") for i in range(L.n_radial)]
         on_tc = all(ops.tensor_core_ok(bessel.dtype, W.shape[0], W.shape[1]) for W in Ws)
-        if on_tc and ops.FUSED_RADIAL_ACTIVATION:
-            return ops.radial_mlp(bessel, Ws, [getattr(L, f"W_radial{i}_T") for i in range(L.n_radial)])
         h = bessel
         if on_tc and ops.radial_hidden_ok(bessel.dtype, Ws[:-1]):
             # all hidden layers and their activations in one kernel, then the last, linear layer

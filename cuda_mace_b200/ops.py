@@ -79,13 +79,9 @@ class _RefCache:
 _status = {}          # device index -> int32[1] written by kernels whose bounded waits time out
 _packed_cache = _RefCache(32)
 USE_TENSOR_CORES = True   # float32 Linear / ElementalLinear / matmul3x go through tcgen05 when shapes allow
-# Folding the perceptron's activation into the GEMM's loads and epilogues removes the elementwise passes
-# but lengthens the producer and epilogue warps, which bound that kernel: measured 41.3 ms per step with
-# it against 39.9 ms without on the 64 000-atom benchmark, so it is off by default.
-FUSED_RADIAL_ACTIVATION = False
-# Last radial layer formed inside the message-passing forward (R is written once and never read back there).
-# Measured at 64 000 atoms (E = 3.33 M, C = 128): 3.75 ms against 2.25 + 1.23 ms for the GEMM followed by the
-# plain forward, so the model does not use it by default; fused_radial_message_passing() always does.
+# Last radial layer formed inside the message-passing forward (R is only written when a backward will follow).
+# Measured at 64 000 atoms (E = 3.33 M, C = 128): 3.4 ms (3.7 ms with R written) against 1.6 + 1.25 ms for the product
+# followed by the plain forward, so the model does not use it by default; fused_radial_message_passing() always does.
 FUSED_RADIAL_MESSAGE_PASSING = False
 # The backward of the last radial layer + message passing without a gradR [E,4,C] array (radial_message_passing):
 # the model's float32 default.  False selects the separate product / message-passing operators.
@@ -110,6 +106,13 @@ def check_status():
             raise RuntimeError(f"cuda_mace_b200: a tensor-core kernel on cuda:{idx} gave up waiting (code {code})")
 
 
+def probe_bounded_wait(device, code=77, limit_seconds=0.05):
+    """Launches the library's wait-that-runs-out probe on `device`: after `limit_seconds` the kernel records `code`
+    in the status word that check_status() reads.  Exercises the time-out reporting without hanging the GPU."""
+    _abi.call("cmace_bounded_wait_probe", _ptr(_status_tensor(torch.device(device))), int(code), float(limit_seconds),
+              _stream())
+
+
 def _pack(Bt):
     """Packs Bt [nmat, N, K] (or [N, K]) float32, K contiguous, into the tensor-core weight image (cached)."""
     key = _RefCache.key(Bt)
@@ -124,57 +127,15 @@ def _pack(Bt):
     return _packed_cache.put(key, (Bt,), packed)
 
 
-def _gemm3x(A, Bt, scale=1.0, act_a=False, ep_z=None):
-    """act(A) [M,K] @ B with Bt = B^T [N,K], optionally times silu'(ep_z) elementwise; float32."""
+def _gemm3x(A, Bt, scale=1.0):
+    """A [M,K] @ B with Bt = B^T [N,K]; float32 on the tensor cores (3-term TF32 split)."""
     A = A.contiguous()
     M, K = A.shape
     N = Bt.shape[0]
-    if ep_z is not None:
-        ep_z = ep_z.contiguous()
-        if ep_z.shape != (M, N):
-            raise RuntimeError("ep_z must have the output's shape")
     out = torch.empty(M, N, dtype=torch.float32, device=A.device)
-    _abi.call("cmace_gemm3x_f32", _ptr(A), _ptr(_pack(Bt)), M, K, N, float(scale), 1 if act_a else 0, _ptr(ep_z),
-              _ptr(out), _ptr(_status_tensor(A.device)), _stream(), tag=f"M={M},K={K},N={N}")
+    _abi.call("cmace_gemm3x_f32", _ptr(A), _ptr(_pack(Bt)), M, K, N, float(scale), _ptr(out),
+              _ptr(_status_tensor(A.device)), _stream(), tag=f"M={M},K={K},N={N}")
     return out
-
-
-class _RadialMLPFunction(torch.autograd.Function):
-    """bessel [E,nb] -> radial weights [E,F] through layers W (pre-scaled by 1/sqrt(fan_in)) with the
-    normalised SiLU between them.  Forward keeps the pre-activations; backward is the mirrored GEMM
-    chain with the activation derivative applied in each GEMM's epilogue."""
-
-    @staticmethod
-    def forward(ctx, bessel, n_layers, *weights):
-        W, WT = weights[:n_layers], weights[n_layers:]
-        zs = []
-        h = bessel
-        for i in range(n_layers):
-            h = _gemm3x(h, WT[i], act_a=(i > 0))
-            if i + 1 < n_layers:
-                zs.append(h)
-        ctx.save_for_backward(*zs, *W)
-        ctx.n_layers = n_layers
-        return h
-
-    @staticmethod
-    def backward(ctx, gR):
-        n = ctx.n_layers
-        saved = ctx.saved_tensors
-        zs, W = saved[: n - 1], saved[n - 1:]
-        g = gR.contiguous()
-        for i in range(n - 1, -1, -1):
-            g = _gemm3x(g, W[i], ep_z=zs[i - 1] if i > 0 else None)
-        return (g, None) + (None,) * (2 * n)
-
-
-def radial_mlp(bessel, weights, weights_t):
-    """Radial multilayer perceptron on the tensor cores (float32): h <- silu(h) @ W_i with no
-    activation before the first and after the last layer.  weights[i] [in,out] already carry the
-    1/sqrt(fan_in) of e3nn's FullyConnectedNet and, from the second layer on, the second-moment
-    constant of its normalised SiLU; weights_t[i] are their contiguous transposes."""
-    _check_cuda(bessel)
-    return _RadialMLPFunction.apply(bessel, len(weights), *weights, *weights_t)
 
 
 class _RadialHiddenFunction(torch.autograd.Function):

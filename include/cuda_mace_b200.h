@@ -233,17 +233,12 @@ int cmace_gemm_f64(const double *A, const double *B, int64_t M, int K, int N, do
  * cmace_linear_tc_f32 has the contract of cmace_linear_f32 (Nout <= 128); cmace_gemm3x_f32 is the plain
  * out[M,N] = scale * A[M,K] @ B used for the radial multilayer perceptron (which upstream MACE evaluates
  * with torch and the reference replaces by its spline table, models/InvariantMACE.py:226-240).
- * a_act = 1 applies the perceptron's activation (SiLU; e3nn's second-moment constant is folded into the next
- * layer's weights) to A while it is loaded;
- * ep_z != NULL multiplies the result elementwise by that activation's derivative at ep_z [M,N]; with
- * these two switches the whole perceptron, forward and backward, is a chain of GEMM calls without any
- * separate elementwise pass.
  * status: optional device int32, set non-zero if a bounded wait inside the kernel timed out. */
 int64_t cmace_gemm_packed_floats(int nmat, int N, int K);
 int cmace_gemm_pack_weights_f32(const float *Bt, int nmat, int N, int K, float *packed,
                                 cmace_stream_t stream);
 int cmace_gemm3x_f32(const float *A, const float *packed, int64_t M, int K, int N, double scale,
-                     int a_act, const float *ep_z, float *out, int32_t *status, cmace_stream_t stream);
+                     float *out, int32_t *status, cmace_stream_t stream);
 int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node_order,
                         const int32_t *elem_start, int nelements, int64_t nnodes, int K, int Nout,
                         double scale, float *out, int32_t *status, cmace_stream_t stream);
@@ -256,6 +251,12 @@ int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node
  * gradR = NULL for gradY and T).  X [Ns,C], G [Nr,16,C], Y [16,E], sender / receiver [E] sorted by receiver,
  * C in {32,64,96,128}; packed = cmace_gemm_pack_weights_f32 of Bt = W [N, 4C] (the last radial layer, N its input
  * width, 32 <= N <= 128, a multiple of 4); out [E, N]. */
+/* No counterpart in the reference.  Launches one warp that waits, with the bounded wait the tensor-core kernels
+ * use, on a barrier nothing completes; after limit_seconds (0 < limit <= 1) the kernel writes `code` (non-zero)
+ * into *status (if it still holds 0) and returns.  The context stays usable: this is how a caller (or a test)
+ * exercises the time-out reporting without hanging or faulting the GPU. */
+int cmace_bounded_wait_probe(int32_t *status, int code, double limit_seconds, cmace_stream_t stream);
+
 int cmace_gemm3x_gradr_f32(const float *X, const float *G, const float *Y, const int32_t *sender,
                            const int32_t *receiver, const float *packed, int64_t nedges, int channels, int N,
                            float *out, int32_t *status, cmace_stream_t stream);

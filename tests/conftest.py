@@ -17,9 +17,26 @@ def built_library():
     """The C-ABI library must exist for every test (CPU tests check its exports); build on demand."""
     from cuda_mace_b200 import build
 
-    if not (os.path.isfile(build.LIB_PATH) and os.path.isfile(build.HOSTCHECK_PATH)):
+    if not os.path.isfile(build.LIB_PATH):
         build.build()
     return build.LIB_PATH
+
+
+@pytest.fixture(scope="session")
+def hostcheck_library():
+    """The per-edge formulas of the kernels (csrc/edge_math.cuh, csrc/symcon_plan.hpp) compiled for the host by g++:
+    test infrastructure, built next to its source under tests/hostcheck/ and never part of the product's lib/."""
+    import subprocess
+
+    here = os.path.join(ROOT, "tests", "hostcheck")
+    src, out = os.path.join(here, "hostcheck.cpp"), os.path.join(here, "libcmace_hostcheck.so")
+    csrc = os.path.join(ROOT, "cuda_mace_b200", "csrc")
+    newest = max(os.path.getmtime(os.path.join(csrc, f)) for f in os.listdir(csrc) if f.endswith((".cuh", ".hpp", ".inc")))
+    if not os.path.isfile(out) or os.path.getmtime(out) < max(os.path.getmtime(src), newest):
+        r = subprocess.run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-I" + csrc, "-o", out, src],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    return out
 
 
 @pytest.fixture(scope="session")

@@ -3,7 +3,7 @@
 // device entry points (xyz [E,3], Y [16,E], B [E,nb]).
 #include <cstdint>
 
-#include "edge_math.cuh"
+#include "edge_math.cuh"   // found through -I cuda_mace_b200/csrc (tests/conftest.py builds this file)
 
 using namespace cmace;
 

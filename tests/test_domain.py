@@ -90,3 +90,62 @@ def test_single_rank_is_plain_periodic():
     pos, species, box, _ = make_case()
     d = domain.partition_slabs(pos, species, box, 1, 5.0, 0)
     assert d.n_local == d.n_owned == pos.shape[0] and len(d.send_up) == 0
+
+
+# ---- failure detection on the host (no GPU involved, nothing is made to fault) -------------------------------------
+def _failing_worker(rank, world, port, out_dir, mode):
+    import datetime
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    pos, species, box, params = make_case()
+    dom = domain.partition_slabs(pos, species, box, world, 5.0, rank)
+    outcome = "ok"
+    t0 = time.time()
+    try:
+        if mode == "wrong_halo" and rank == 1:
+            dom.recv_up = (dom.recv_up[0], dom.recv_up[1] + 3)     # this rank expects three rows too many
+        plan = domain.HaloPlan(dom, "cpu")
+        if mode == "wrong_halo":
+            plan.verify()
+        if mode == "rank_dies" and rank == 1:
+            os._exit(3)                                            # leaves between steps, nothing in flight
+        x = torch.from_numpy(dom.positions[: dom.n_owned])
+        domain.halo_exchange(x, plan)
+    except Exception as exc:  # noqa: BLE001 - the test records whatever the survivor sees
+        outcome = type(exc).__name__ + ": " + str(exc)[:200]
+    with open(os.path.join(out_dir, f"outcome{rank}.txt"), "w") as f:
+        f.write(f"{time.time() - t0:.1f}\n{outcome}")
+    os._exit(0)
+
+
+def _run_failing(world, mode, tmp_path):
+    ctx = mp.get_context("spawn")
+    port = free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, str(tmp_path), mode)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+        assert not p.is_alive(), "a rank hung instead of ending with an error"
+    return procs
+
+
+def test_mismatched_halo_sizes_are_caught_on_the_host(tmp_path):
+    """One rank expects a different ghost count than its neighbour sends: HaloPlan.verify() (run once per
+    decomposition by the evaluator) raises on every rank before any exchange is posted."""
+    _run_failing(2, "wrong_halo", tmp_path)
+    for r in range(2):
+        seconds, outcome = open(tmp_path / f"outcome{r}.txt").read().split("\n", 1)
+        assert outcome.startswith("ValueError: halo plan mismatch"), outcome
+
+
+def test_a_rank_that_leaves_ends_the_neighbours_exchange_with_an_error(tmp_path):
+    """Rank 1 exits between steps; rank 0's next halo exchange ends with an exception within the process-group
+    timeout instead of waiting forever."""
+    procs = _run_failing(2, "rank_dies", tmp_path)
+    assert procs[1].exitcode == 3
+    seconds, outcome = open(tmp_path / "outcome0.txt").read().split("\n", 1)
+    assert outcome != "ok" and float(seconds) < 60.0, outcome

@@ -6,7 +6,6 @@ import numpy as np
 import pytest
 import torch
 
-from cuda_mace_b200 import build
 from oracle import model as omodel
 from oracle import ops as oops
 from oracle.sh import real_sh_l3
@@ -17,8 +16,8 @@ def P(a):
 
 
 @pytest.fixture(scope="module")
-def hc(built_library):
-    return ctypes.CDLL(build.HOSTCHECK_PATH)
+def hc(hostcheck_library):
+    return ctypes.CDLL(hostcheck_library)
 
 
 def edges(seed, n):

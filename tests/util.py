@@ -33,7 +33,3 @@ def unit_vectors(seed, n, dtype=torch.float64):
     g = torch.Generator().manual_seed(seed)
     v = torch.randn(n, 3, generator=g, dtype=torch.float64)
     return (v / v.norm(dim=-1, keepdim=True)).to(dtype)
-
-
-def cuda_params(params, device="cuda"):
-    return params

@@ -168,18 +168,36 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
     }.get(base)
 
 
-# DRAM traffic per edge (dram__bytes_read.sum + dram__bytes_write.sum of one launch / edges) from the ncu captures of
-# the 8 000-atom case summarised under profiles/ (E = 417 248 there); the traffic of every edge kernel grows in
-# proportion to E, so a full launch moves this many bytes times its own E.
+# DRAM traffic per edge (dram__bytes_read.sum + dram__bytes_write.sum of one launch / edges) from the ncu capture of
+# the 8 000-atom case summarised in profiles/step_kernels_small_case_f32.txt (E = 417 248 there); the traffic of every
+# edge kernel grows in proportion to E, so a full launch moves this many bytes times its own E.
+_SRC = "profiles/step_kernels_small_case_f32.txt"
 NCU_TRAFFIC_PER_EDGE = {
-    # staged kernel, mean of a step's two launches: 1016 + 1050 MB with the T array, 1008 + 840 MB without
-    "cmace_imp_bwd_edge_f32": (4691.0, "profiles/imp_kernels_small_case_f32.txt"),
-    "cmace_imp_fwd_f32": (2170.0, "profiles/imp_kernels_small_case_f32.txt"),
-    "cmace_gemm3x_f32[K=512,N=64]": (2285.0, "profiles/gemm3x_tf32_small_case_f32.txt"),
-    "cmace_gemm3x_f32[K=64,N=512]": (2176.0, "profiles/gemm3x_tf32_small_case_f32.txt"),
-    "cmace_radial_hidden_fwd_f32": (925.0, "profiles/radial_hidden_small_case_f32.txt"),
-    "cmace_radial_hidden_bwd_f32": (1057.0, "profiles/radial_hidden_small_case_f32.txt"),
+    "cmace_imp_bwd_edge_f32[no gradR]": (2675.0, _SRC),   # mean of a step's two launches (with / without the T array)
+    "cmace_imp_fwd_f32": (2170.0, _SRC),
+    "cmace_gemm3x_gradr_f32": (403.0, _SRC),
+    "cmace_gemm3x_f32[K=64,N=512]": (2162.0, _SRC),
+    "cmace_radial_hidden_fwd_f32": (925.0, _SRC),
+    "cmace_radial_hidden_bwd_f32": (1126.0, _SRC),
 }
+
+
+def tensor_flops(name, E, C):
+    """Tensor-core flops one launch executes, for the kernels whose binding roof is the tensor pipe: the product of
+    the radial-weight gradient with the last radial layer runs three TF32 terms of 2 * E * 4C * 64 flops each."""
+    if name == "cmace_gemm3x_gradr_f32":
+        return 3 * 2 * E * 4 * C * 64
+    return None
+
+
+def tf32_peak():
+    """Dense TF32 peak = half the measured dense bf16 rate (MEASURED_PEAKS.json bf16_tflops, the burst figure of a kernel
+    timed alone); TF32 runs at half the bf16 rate on this tensor core."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]) / 2.0, "half of the measured bf16 burst rate (MEASURED_PEAKS.json bf16_tflops)"
+    return 1590.0 / 2.0, "fallback (half of 1.59 PFLOP/s bf16)"
 
 
 def cpu_reference_run(args, steps, warmup):
@@ -524,15 +542,30 @@ def main():
             top, top_ms = name, tot
     roofline = None
     if top:
-        ach = per_kernel[top]["achieved_gbs"]
         per_edge = NCU_TRAFFIC_PER_EDGE.get(top)
-        roofline = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
-                    "frac": ach / peak, "traffic": per_edge[0] * E if per_edge else None,
-                    "traffic_source": (f"ncu capture of a smaller case scaled by edges, {per_edge[1]}"
-                                       if per_edge else None),
-                    "peak_source": peak_src,
-                    "algorithmic_bytes_per_launch": algorithmic_bytes(top, s_bytes, N, Ns, E, 128, sysd["n_species"]),
-                    "avg_launch_ms": per_kernel[top]["avg_ms"]}
+        traffic = per_edge[0] * E if per_edge else None
+        traffic_src = f"ncu capture of a smaller case scaled by edges, {per_edge[1]}" if per_edge else None
+        flops = tensor_flops(top, E, 128)
+        if flops:
+            # not HBM-bound (its operands are formed on chip): the tensor pipe is the roof that binds it
+            tpeak, tsrc = tf32_peak()
+            ach = flops / (per_kernel[top]["avg_ms"] * 1e-3) / 1e12
+            roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": tpeak, "unit": "TFLOP/s",
+                        "frac": ach / tpeak, "traffic": traffic, "traffic_source": traffic_src, "peak_source": tsrc,
+                        "algorithmic_flops_per_launch": flops, "avg_launch_ms": per_kernel[top]["avg_ms"],
+                        "hbm_gbs_of_algorithmic_bytes": per_kernel[top]["achieved_gbs"]}
+        else:
+            ach = per_kernel[top]["achieved_gbs"]
+            roofline = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
+                        "frac": ach / peak, "traffic": traffic, "traffic_source": traffic_src, "peak_source": peak_src,
+                        "algorithmic_bytes_per_launch": algorithmic_bytes(top, s_bytes, N, Ns, E, 128, sysd["n_species"]),
+                        "avg_launch_ms": per_kernel[top]["avg_ms"]}
+        # the largest HBM-bound kernel beside it, for the fraction of the copy peak the streaming kernels reach
+        hbm = [(v["share_of_step"], k) for k, v in per_kernel.items() if v["achieved_gbs"] and not tensor_flops(k, E, 128)]
+        if hbm:
+            k = max(hbm)[1]
+            roofline["largest_hbm_bound_kernel"] = {"kernel": k, "achieved": per_kernel[k]["achieved_gbs"], "peak": peak,
+                                                    "unit": "GB/s", "frac": per_kernel[k]["achieved_gbs"] / peak}
 
     line = {
         "metric": METRIC, "value": value, "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,

@@ -116,10 +116,18 @@ __global__ void __launch_bounds__(LIN_THREADS)
 // spreads the rows of each half-warp over all 32 banks.  Fragment layout of mma.m8n8k4.f64: A[lane/4][lane%4],
 // B[lane%4][lane/4], C[lane/4][2*(lane%4) + {0,1}].
 // The operator is bound by the FP64 tensor rate at K = Nout = 128 (16 flop/B against a machine balance of ~6).
+// TN: columns of the output tile, 128 or 64 (the radial perceptron's hidden layers are 64 wide: a 128-column tile would
+// spend half of its instructions on padding); the 16 warps form a 4 x 4 grid of 32 x TN/4 pieces in both cases.
 constexpr int DM_TILE = 128, DM_K = 16, DM_THREADS = 512, DM_STAGES = 3;
-constexpr int DM_AS = DM_K + 4, DM_BS = DM_TILE + 4;          // row strides in doubles
-constexpr int DM_STAGE_DOUBLES = DM_TILE * DM_AS + DM_K * DM_BS;
-constexpr int DM_SMEM_BYTES = DM_STAGES * DM_STAGE_DOUBLES * 8;
+constexpr int DM_AS = DM_K + 4;                                // row stride of the A slice in doubles
+template <int TN>
+struct DmGeom {
+  static constexpr int BS = TN + 4;                            // row stride of the B slice in doubles
+  static constexpr int STAGE_DOUBLES = DM_TILE * DM_AS + DM_K * BS;
+  static constexpr int SMEM_BYTES = DM_STAGES * STAGE_DOUBLES * 8;
+  static constexpr int B_COPIES = DM_K * TN / 2 / DM_THREADS;  // 16-byte chunks of a B slice per thread
+  static constexpr int NJ = TN / 32;                           // 8-column MMA tiles per warp
+};
 
 __device__ __forceinline__ void cp_async_16_zfill(void *dst, const void *src, bool valid) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -127,7 +135,7 @@ __device__ __forceinline__ void cp_async_16_zfill(void *dst, const void *src, bo
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
 }
 
-template <bool PLAIN>
+template <bool PLAIN, int TN>
 __global__ void __launch_bounds__(DM_THREADS, 1)
     linear_dmma_kernel(const double *__restrict__ X, const double *__restrict__ W,
                        const int32_t *__restrict__ node_order, const int32_t *__restrict__ elem_start,
@@ -137,7 +145,9 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
 
   const int l = PLAIN ? 0 : blockIdx.y;
   const int nl = 2 * l + 1;
-  const int n0 = blockIdx.z * DM_TILE;
+  using Geo = DmGeom<TN>;
+  constexpr int DM_BS = Geo::BS, DM_STAGE_DOUBLES = Geo::STAGE_DOUBLES;
+  const int n0 = blockIdx.z * TN;
 
   int z = 0;
   int64_t tile = blockIdx.x, seg_begin = 0, seg_count = 0;
@@ -170,7 +180,7 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
   const double *Wz = PLAIN ? W : W + ((int64_t)(z * 4 + l) * K) * Nout;
   // copy assignments: 1024 16-byte chunks per operand and K slice, two per thread
   int64_t a_src[2];
-  int a_dst[2], a_k[2], b_dst[2], b_k[2], b_c[2];
+  int a_dst[2], a_k[2], b_dst[Geo::B_COPIES], b_k[Geo::B_COPIES], b_c[Geo::B_COPIES];
 #pragma unroll
   for (int i = 0; i < 2; i++) {
     const int c = tid + DM_THREADS * i;
@@ -178,7 +188,11 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
     a_src[i] = row_of[ar] >= 0 ? row_of[ar] * K + ach * 2 : -1;
     a_k[i] = ach * 2;
     a_dst[i] = ar * DM_AS + ach * 2;
-    const int bk = c >> 6, bch = c & 63;             // B: 16 K rows x 64 chunks
+  }
+#pragma unroll
+  for (int i = 0; i < Geo::B_COPIES; i++) {
+    const int c = tid + DM_THREADS * i;
+    const int bk = c / (TN / 2), bch = c % (TN / 2);   // B: 16 K rows x TN/2 chunks
     b_k[i] = bk;
     b_c[i] = n0 + bch * 2;
     b_dst[i] = DM_TILE * DM_AS + bk * DM_BS + bch * 2;
@@ -190,19 +204,23 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
     for (int i = 0; i < 2; i++) {
       const bool av = a_src[i] >= 0 && k0 + a_k[i] < K;
       cp_async_16_zfill(st + a_dst[i], av ? X + a_src[i] + k0 : X, av);
+    }
+#pragma unroll
+    for (int i = 0; i < Geo::B_COPIES; i++) {
       const bool bv = k0 + b_k[i] < K && b_c[i] < Nout;
       cp_async_16_zfill(st + b_dst[i], bv ? Wz + (int64_t)(k0 + b_k[i]) * Nout + b_c[i] : W, bv);
     }
   };
 
   const int warp = tid >> 5, lane = tid & 31;
-  const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;
+  constexpr int NJ = Geo::NJ;
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * (TN / 4);
   const int fr = lane >> 2, fk = lane & 3;
-  double acc[4][4][2];
+  double acc[4][NJ][2];
 #pragma unroll
   for (int i = 0; i < 4; i++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) acc[i][j][0] = acc[i][j][1] = 0.0;
+    for (int j = 0; j < NJ; j++) acc[i][j][0] = acc[i][j][1] = 0.0;
 
   const int nk = (K + DM_K - 1) / DM_K;
 #pragma unroll
@@ -219,15 +237,15 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
     const double *Bs = As + DM_TILE * DM_AS;
 #pragma unroll
     for (int kk = 0; kk < DM_K; kk += 4) {
-      double a[4], b[4];
+      double a[4], b[NJ];
 #pragma unroll
       for (int i = 0; i < 4; i++) a[i] = As[(wm + i * 8 + fr) * DM_AS + kk + fk];
 #pragma unroll
-      for (int j = 0; j < 4; j++) b[j] = Bs[(kk + fk) * DM_BS + wn + j * 8 + fr];
+      for (int j = 0; j < NJ; j++) b[j] = Bs[(kk + fk) * DM_BS + wn + j * 8 + fr];
 #pragma unroll
       for (int i = 0; i < 4; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++)
+        for (int j = 0; j < NJ; j++)
           asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
                        : "+d"(acc[i][j][0]), "+d"(acc[i][j][1])
                        : "d"(a[i]), "d"(b[j]));
@@ -240,7 +258,7 @@ __global__ void __launch_bounds__(DM_THREADS, 1)
     const int64_t grow = row_of[wm + i * 8 + fr];
     if (grow < 0) continue;
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < NJ; j++) {
       const int c = n0 + wn + j * 8 + 2 * fk;
       if (c < Nout)   // Nout is even: both columns or none
         *reinterpret_cast<double2 *>(out + grow * Nout + c) = make_double2(acc[i][j][0] * scale, acc[i][j][1] * scale);
@@ -253,14 +271,15 @@ static int linear_dmma(const double *X, const double *W, const int32_t *node_ord
                        cmace_stream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(linear_dmma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(linear_dmma_kernel<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             DmGeom<128>::SMEM_BYTES) != cudaSuccess)
       return fail(CMACE_ERR_CUDA, "cmace_linear_f64: cannot reserve shared memory");
     attr_set = true;
   }
   const int64_t max_tiles = (nnodes * 7 + DM_TILE - 1) / DM_TILE + nelements;
   if (max_tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear: too many rows");
   dim3 grid((unsigned)max_tiles, 4, (unsigned)((Nout + DM_TILE - 1) / DM_TILE));
-  linear_dmma_kernel<false><<<grid, DM_THREADS, DM_SMEM_BYTES, (cudaStream_t)stream>>>(
+  linear_dmma_kernel<false, 128><<<grid, DM_THREADS, DmGeom<128>::SMEM_BYTES, (cudaStream_t)stream>>>(
       X, W, node_order, elem_start, nelements, nnodes, K, Nout, scale, out);
   return check_launch("cmace_linear_f64");
 }
@@ -275,15 +294,24 @@ static int gemm_f64(const double *A, const double *B, int64_t M, int K, int N, d
   if (K % 2 == 0 && N % 2 == 0 && aligned16(A) && aligned16(B) && aligned16(out)) {
     static bool attr_set = false;
     if (!attr_set) {
-      if (cudaFuncSetAttribute(linear_dmma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM_BYTES) != cudaSuccess)
+      if (cudaFuncSetAttribute(linear_dmma_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               DmGeom<128>::SMEM_BYTES) != cudaSuccess ||
+          cudaFuncSetAttribute(linear_dmma_kernel<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               DmGeom<64>::SMEM_BYTES) != cudaSuccess)
         return fail(CMACE_ERR_CUDA, "cmace_gemm_f64: cannot reserve shared memory");
       attr_set = true;
     }
     const int64_t tiles = (M + DM_TILE - 1) / DM_TILE;
     if (tiles > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "cmace_gemm_f64: too many rows");
-    dim3 grid((unsigned)tiles, 1, (unsigned)((N + DM_TILE - 1) / DM_TILE));
-    linear_dmma_kernel<true><<<grid, DM_THREADS, DM_SMEM_BYTES, (cudaStream_t)stream>>>(A, B, nullptr, nullptr, 1, M, K, N,
-                                                                                         scale, out);
+    if (N <= 64) {   // narrow output: 64-column tiles
+      dim3 grid((unsigned)tiles, 1, 1);
+      linear_dmma_kernel<true, 64><<<grid, DM_THREADS, DmGeom<64>::SMEM_BYTES, (cudaStream_t)stream>>>(
+          A, B, nullptr, nullptr, 1, M, K, N, scale, out);
+    } else {
+      dim3 grid((unsigned)tiles, 1, (unsigned)((N + DM_TILE - 1) / DM_TILE));
+      linear_dmma_kernel<true, 128><<<grid, DM_THREADS, DmGeom<128>::SMEM_BYTES, (cudaStream_t)stream>>>(
+          A, B, nullptr, nullptr, 1, M, K, N, scale, out);
+    }
     return check_launch("cmace_gemm_f64");
   }
   const int64_t tiles = (M + TILE_M - 1) / TILE_M;

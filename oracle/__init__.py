@@ -17,19 +17,15 @@ What it restates (paths are relative to the cuda-mace project):
                                  cuda_mace/ops/symmetric_contraction.py:91-232
 * model wiring                   cuda_mace/models/InvariantMACE.py:77-165, :246-379
 
-Parity status: the reference holds no golden vectors and its own tests compare
-against live `mace` / `e3nn` installs (tests/*.py), neither of which exists in
-this environment.  The Bessel basis, polynomial cutoff, radial MLP, readout and
-generalised Clebsch-Gordan conventions are therefore restated from the published
-MACE / e3nn definitions: PARITY UNPINNED against upstream MACE for those parts.
-The operator semantics that live in the reference tree itself (the files listed
-above) are followed line by line and the small committed fixtures under
-tests/golden/ freeze this restatement's outputs.
+Parity status.  PINNED against the reference's own kernels: oracle/build_ref.py builds the reference's library
+from its sources, oracle/ref_run.py runs its six operator classes (and an energy+force step re-assembled from them,
+oracle/ref_model.py) on a B200, and tests/test_reference_pin.py holds this restatement and the CUDA library to those
+outputs, both through committed fixtures (tests/golden/reference_ops_b200.npz) and live where the built library is
+present.  Also pinned, against the reference's Python run on the CPU (tests/golden/make_reference_pins.py): the
+sparse packing of the U tensors (cuda_mace/ops/symmetric_contraction.py:91-187, bit for bit) and the natural-spline
+coefficient solve (cuda_mace/ops/cubic_spline.py:41-84).
 
-PINNED against the reference's own code, run on seeded inputs
-(tests/golden/make_reference_pins.py -> tests/golden/reference_pins.npz): the
-sparse packing of the U tensors (cuda_mace/ops/symmetric_contraction.py:91-187,
-bit for bit) and the natural-spline coefficient solve
-(cuda_mace/ops/cubic_spline.py:41-84).  The reference's kernels themselves only
-run on a GPU through its cmake / NVRTC build, which this project does not run.
+PARITY UNPINNED against upstream MACE / e3nn for what the reference borrows from them and this environment cannot
+install: the Bessel basis, polynomial cutoff, radial perceptron, readout normalisations and the scale and sign of
+each symmetric class of generalised Clebsch-Gordan paths are restated from the published definitions.
 """

@@ -30,7 +30,9 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB_PATH = os.path.join(OUT_DIR, "libcuda_mace.so")
-DEFAULT_REFERENCE = os.environ.get("CUDA_MACE_REFERENCE", "/root/reference")
+# the reference checkout: $CUDA_MACE_REFERENCE, else a directory "reference" next to this repository
+DEFAULT_REFERENCE = os.environ.get("CUDA_MACE_REFERENCE",
+                                   os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 KERNEL_FILES = ["cubic_spline_impl", "invariant_message_passing_impl", "spherical_harmonics_impl", "linear_impl",
                 "symmetric_contraction_impl"]

@@ -157,7 +157,13 @@ def test_schemas_equal_the_reference_library(classes):
             assert str(obj._get_method(method).schema) == schema, (ns, name, method)
 
 
-REFERENCE_ROOT = "/root/reference"
+def _reference_root():
+    from oracle import build_ref
+
+    return build_ref.DEFAULT_REFERENCE
+
+
+REFERENCE_ROOT = _reference_root()
 
 
 def _load_reference_python(rel_path, name):

@@ -770,6 +770,16 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // integer operations, no warp-wide shuffle or re-convergence.  Whatever sits between the batches leaves the
     // tensor core idle (the issue of an MMA blocks until the previous ones have drained, so the queue is shallow).
     if (lane != 0) ok = false;
+    // low / high words of the operand descriptors (umma_desc_sw128): the low word of stage 0, its step per stage
+    const uint64_t d0 = umma_desc_sw128(smem_base);
+    const uint32_t desc_hi32 = (uint32_t)(d0 >> 32);
+    const uint32_t stage_step = GT_STAGE_BYTES >> 4;
+    const uint32_t a_hi_first = (uint32_t)d0;
+    const uint32_t a_lo_first = (uint32_t)umma_desc_sw128(smem_base + GT_A_SLAB);
+    const uint32_t b_ring_first = (uint32_t)umma_desc_sw128(smem_base + b_off);
+    const uint32_t bres_lo32 = (uint32_t)umma_desc_sw128(smem_first), bres_step = (2u * b_image) >> 4;
+    uint32_t a_hi_lo32 = a_hi_first, a_lo_lo32 = a_lo_first, b_ring_lo32 = b_ring_first;
+    const bool full_k = (g.K % GT_KBLOCK) == 0;
     TileWalker<MODE> tiles(g, tab);
     Tile T;
     while (ok && tiles.next(T)) {
@@ -794,24 +804,20 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         }
         tc_fence_after();
         {
-          // descriptors of K step j differ from those of step 0 by j * 32 bytes = 2 address units
-          const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-          const uint64_t a_hi0 = umma_desc_sw128(sA), a_lo0 = umma_desc_sw128(sA + GT_A_SLAB);
-          const uint64_t b_hi0 =
-              umma_desc_sw128(g.b_resident ? smem_first + (uint32_t)kb * 2u * b_image : sA + b_off);
-          int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
-          ksteps = ksteps > 4 ? 4 : ksteps;
-          // the issuing thread shares its scheduler with busy warps, so every instruction between two
-          // MMAs costs issue latency: descriptors are formed first, then the MMAs go back to back
+          // Operand descriptors: only the low word (address field) changes from stage to stage and from K step to K
+          // step (j * 32 bytes = 2 address units); the high word is a constant.  This thread shares its scheduler
+          // with busy warps, so every instruction between two MMAs costs issue latency: the low words advance with
+          // one add per item, the eight MMAs go back to back.
+          const uint32_t b_lo32 = g.b_resident ? bres_lo32 + (uint32_t)kb * bres_step : b_ring_lo32;
           uint64_t ah[4], al[4], bh[4];
 #pragma unroll
           for (int j = 0; j < 4; j++) {
-            ah[j] = a_hi0 + (uint64_t)(2 * j);
-            al[j] = a_lo0 + (uint64_t)(2 * j);
-            bh[j] = b_hi0 + (uint64_t)(2 * j);
+            asm("mov.b64 %0, {%1, %2};" : "=l"(ah[j]) : "r"(a_hi_lo32 + 2u * j), "r"(desc_hi32));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(al[j]) : "r"(a_lo_lo32 + 2u * j), "r"(desc_hi32));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(bh[j]) : "r"(b_lo32 + 2u * j), "r"(desc_hi32));
           }
           const uint32_t a_lo_t = lo_ring + 32u * (uint32_t)stage;   // TS: K step j at + 8 j columns
-          if (ksteps == 4) {
+          if (full_k) {
             umma_tf32(d_tmem, ah[0], bh[0], idesc2, kb != 0);
             if (TS) umma_tf32_ts_acc(d_tmem, a_lo_t, bh[0], idesc1);
             else umma_tf32_acc(d_tmem, al[0], bh[0], idesc1);
@@ -822,6 +828,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
               else umma_tf32_acc(d_tmem, al[j], bh[j], idesc1);
             }
           } else {
+            int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
+            ksteps = ksteps > 4 ? 4 : ksteps;
             for (int j = 0; j < ksteps; j++) {
               umma_tf32(d_tmem, ah[j], bh[j], idesc2, (kb | j) != 0);
               if (TS) umma_tf32_ts_acc(d_tmem, a_lo_t + 8u * j, bh[j], idesc1);
@@ -831,9 +839,15 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           umma_commit(empty_bar + 8 * stage);
           if (kb == k_blocks - 1) umma_commit(acc_full + 8 * acc);
         }
+        a_hi_lo32 += stage_step;
+        a_lo_lo32 += stage_step;
+        b_ring_lo32 += stage_step;
         if (++stage == GT_STAGES) {
           stage = 0;
           phase ^= 1;
+          a_hi_lo32 = a_hi_first;
+          a_lo_lo32 = a_lo_first;
+          b_ring_lo32 = b_ring_first;
         }
       }
       acc_phase[acc] ^= 1;

@@ -96,6 +96,7 @@ struct GemmArgs {
   const int32_t *sender, *receiver;
   int C;
   int g_stage_bytes;            // GRADR: shared memory behind the ring and the epilogue buffers for staged G rows
+  int b_slots;                  // GRADR: depth of the separate ring of B blocks behind the staged G rows
 };
 
 // ---- tile bookkeeping ----------------------------------------------------------------------------
@@ -280,7 +281,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GT_STAGES; s++) {
-      // LINEAR: one arrival per producer warp + the expect_tx arrival of the B copy; PLAIN: converters only
+      // LINEAR, GRADR: one arrival per producer warp + the expect_tx arrival of the B copy; PLAIN: converters only
       mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS + (MODE == GT_MODE_PLAIN ? 0 : 1));
       mbar_init(tma_full + 8 * s, 1);         // the loader's expect_tx arrival (+ the copies' bytes)
       mbar_init(empty_bar + 8 * s, 1);        // one tcgen05.commit
@@ -427,13 +428,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // the G rows of that range (8 KB per receiver at C = 128, one contiguous piece) into one of two shared-memory
     // buffers a tile ahead, and the inner loop reads them from there (warp-wide broadcasts); receivers beyond
     // the staged range, when a tile spans many low-degree receivers, are read from global memory.
-    // The hand-over of an item (wait for the tensor-memory store, fences, arrival) is delayed until the next
-    // item's operand has been computed, so that the store's latency is covered by arithmetic.
+    // The B blocks are copied by the loader warp into a region of their own with the same slot index and barriers as
+    // the A images; the ring is as deep as shared memory allows (five slots), because the round trip of a slot
+    // (hand-over, MMAs, commit, wake-up) divided by the depth bounds the rate.
     const int q4 = warp & 3, hf = warp >> 2;
     const int r = q4 * 32 + lane;
     const int p = threadIdx.x;
     const int C = CC ? CC : g.C, ncb = C >> 5;
-    const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES + GT_EP_TMA_BYTES;
+    const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES;
     const uint32_t g_half = (uint32_t)g.g_stage_bytes / 2u;
     const int max_staged = (int)(g_half / (uint32_t)(16 * C * 4));
     uint32_t soff[4];
@@ -536,7 +538,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           }
 #pragma unroll
           for (int c = 0; c < 8; c++) asm("mul.rn.f32x2 %0, %0, %1;" : "+l"(a2[c]) : "l"(x2[c]));
-          hand_over();   // the previous item
           // the slot (shared-memory image and tensor-memory columns) is free once the MMAs that read it completed
           uint32_t got = 1;
           if (lane == 0) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
@@ -546,12 +547,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             break;
           }
           const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-          if (p == 0) {
-            const int kb = l * ncb + cb;
-            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) + (int64_t)kb * (2 * (int64_t)b_image);
-            mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
-            bulk_copy_g2s(sA + GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
-          }
           // hi image: the raw values (the tensor core ignores the low 13 mantissa bits of its operands);
           // residual image: a - trunc(a), exact in float32 and at most 2^-10 |a|; it is read with the same truncation,
           // which leaves an error below 2^-20 |a| per element
@@ -569,6 +564,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           }
           tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
           pending_stage = stage;
+          hand_over();
           if (++stage == GT_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -688,22 +684,25 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // matrix) into the hi image, and the bulk copy of the matching pre-packed B block.  Nothing waits in
     // registers for HBM; the ring depth sets the bytes in flight.
     if (MODE == GT_MODE_GRADR && lane == 0) {
-      // one bulk copy per tile: the G rows of the tile's receiver range (contiguous) into the buffer the producers
-      // released two tiles ago
-      const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES + GT_EP_TMA_BYTES;
+      // Per item the B block of the producers' K block order (cb outer, l inner) into a ring of g.b_slots slots; per
+      // tile one bulk copy of the G rows of the NEXT tile's receiver range (contiguous) into the buffer the producers
+      // released, issued in the middle of the current tile: by then every producer warp has left the previous tile
+      // (they run at most a few items ahead of the tensor core), so this thread never waits long for the buffer.
+      const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES;
       const uint32_t g_half = (uint32_t)g.g_stage_bytes / 2u;
+      const uint32_t b_ring0 = g_stage0 + (uint32_t)g.g_stage_bytes;
       const int per_receiver = 16 * g.C * 4;
       const int max_staged = (int)(g_half / (uint32_t)per_receiver);
-      TileWalker<MODE> tiles(g, tab);
-      Tile T;
-      for (int t = 0; tiles.next(T); t++) {
-        const int buf = t & 1;
-        if (t >= 2 && !mbar_wait(g_empty + 8 * buf, ((uint32_t)(t >> 1) & 1u) ^ 1u)) {
+      const int ncb = g.C >> 5;
+      bool ok = true;
+      auto copy_g = [&](const Tile &Tg, int tg) -> bool {
+        const int buf = tg & 1;
+        if (tg >= 2 && !mbar_wait(g_empty + 8 * buf, ((uint32_t)(tg >> 1) & 1u) ^ 1u)) {
           report(g, 7);
-          break;
+          return false;
         }
-        const int64_t e_last = T.row0 + GT_TILE_M - 1 < g.M ? T.row0 + GT_TILE_M - 1 : g.M - 1;
-        const int r_first = __ldg(g.receiver + T.row0);
+        const int64_t e_last = Tg.row0 + GT_TILE_M - 1 < g.M ? Tg.row0 + GT_TILE_M - 1 : g.M - 1;
+        const int r_first = __ldg(g.receiver + Tg.row0);
         const int r_count = __ldg(g.receiver + e_last) - r_first + 1;
         const uint32_t bytes = (uint32_t)((r_count < max_staged ? r_count : max_staged) * per_receiver);
         const unsigned char *src = reinterpret_cast<const unsigned char *>(g.gg + (int64_t)r_first * 16 * g.C);
@@ -712,6 +711,36 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           const uint32_t n = bytes - off < 8192u ? bytes - off : 8192u;
           bulk_copy_g2s(g_stage0 + buf * g_half + off, src + off, n, g_full + 8 * buf);
         }
+        return true;
+      };
+      TileWalker<MODE> tiles(g, tab);
+      Tile Tc, Tn;
+      bool have = tiles.next(Tc);
+      if (have) ok = copy_g(Tc, 0);
+      int slot = 0;
+      uint32_t bphase = 0;
+      for (int t = 0; ok && have; t++) {
+        const bool have_next = tiles.next(Tn);
+        for (int j = 0; ok && j < 4 * ncb; j++) {
+          if (j == 2 * ncb && have_next) ok = copy_g(Tn, t + 1);
+          if (!ok) break;
+          if (!mbar_wait(empty_bar + 8 * slot, bphase ^ 1)) {   // same slot index and barrier as the A image
+            report(g, 9);
+            ok = false;
+            break;
+          }
+          const int cb = j >> 2, l = j & 3;
+          const int kb = l * ncb + cb;
+          const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) + (int64_t)kb * (2 * (int64_t)b_image);
+          mbar_arrive_expect_tx(full_bar + 8 * slot, 2 * b_image);
+          bulk_copy_g2s(b_ring0 + (uint32_t)slot * 2u * b_image, bsrc, 2 * b_image, full_bar + 8 * slot);
+          if (++slot == g.b_slots) {
+            slot = 0;
+            bphase ^= 1;
+          }
+        }
+        Tc = Tn;
+        have = have_next;
       }
     }
     if (MODE == GT_MODE_PLAIN && lane == 0) {
@@ -780,6 +809,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     const uint32_t bres_lo32 = (uint32_t)umma_desc_sw128(smem_first), bres_step = (2u * b_image) >> 4;
     uint32_t a_hi_lo32 = a_hi_first, a_lo_lo32 = a_lo_first, b_ring_lo32 = b_ring_first;
     const bool full_k = (g.K % GT_KBLOCK) == 0;
+    const uint32_t bb_first = (uint32_t)umma_desc_sw128(smem_base + GT_STAGES * GT_STAGE_BYTES + (uint32_t)g.g_stage_bytes);
     TileWalker<MODE> tiles(g, tab);
     Tile T;
     while (ok && tiles.next(T)) {
@@ -808,7 +838,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           // step (j * 32 bytes = 2 address units); the high word is a constant.  This thread shares its scheduler
           // with busy warps, so every instruction between two MMAs costs issue latency: the low words advance with
           // one add per item, the eight MMAs go back to back.
-          const uint32_t b_lo32 = g.b_resident ? bres_lo32 + (uint32_t)kb * bres_step : b_ring_lo32;
+          const uint32_t b_lo32 = MODE == GT_MODE_GRADR ? bb_first + (uint32_t)stage * bres_step
+                                  : g.b_resident      ? bres_lo32 + (uint32_t)kb * bres_step
+                                                      : b_ring_lo32;
           uint64_t ah[4], al[4], bh[4];
 #pragma unroll
           for (int j = 0; j < 4; j++) {
@@ -1159,15 +1191,27 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (g.a_lo_tmem && g.stages > ts_slots) g.stages = ts_slots;
   g.g_stage_bytes = 0;
   if (g.mode == GT_MODE_GRADR) {
-    // three ring slots are enough here (the producers compute, nothing waits for HBM); what is left of shared
-    // memory holds the G rows of a tile's receivers, twice (the next tile's are copied while this one is consumed)
+    // Shared memory: a ring of A images (hi image only, 16 KB a slot), a ring of B blocks of its own, and the G rows
+    // of a tile's receivers twice (the next tile's are copied while this one is consumed).  No epilogue staging
+    // buffers: the narrow output goes from tensor memory to global memory through registers.
     const int per_receiver = 16 * g.C * 4;
-    if (g.stages > 3) g.stages = 3;
-    g.g_stage_bytes = ((budget - ep_bytes - 1024 - g.stages * g.stage_bytes) / (2 * per_receiver)) * 2 * per_receiver;
+    g.ep_tma = 0;
+    g.stage_bytes = GT_A_SLAB;
+    g.stages = 5;
+    g.b_slots = 5;           // the B blocks live in a region of their own but share slot index and barriers with A
+    int left = budget - 1024 - g.stages * g.stage_bytes - g.b_slots * 2 * g.npad * 128;
+    while (g.stages > 2 && left < 2 * 4 * per_receiver) {   // keep room for four receivers per buffer
+      g.stages--;
+      g.b_slots--;
+      left += g.stage_bytes + 2 * g.npad * 128;
+    }
+    if (left < 0) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
+    g.g_stage_bytes = (left / (2 * per_receiver)) * 2 * per_receiver;
     if (g.g_stage_bytes < 0) g.g_stage_bytes = 0;
   }
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
-  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + ep_bytes + 1024 + (size_t)g.g_stage_bytes;
+  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + (g.mode == GT_MODE_GRADR ? 0 : ep_bytes) + 1024 +
+                      (size_t)g.g_stage_bytes + (size_t)g.b_slots * 2 * g.npad * 128;
   CUtensorMap tmap, tmap_out;
   memset(&tmap, 0, sizeof(tmap));
   memset(&tmap_out, 0, sizeof(tmap_out));

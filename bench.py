@@ -175,7 +175,7 @@ _SRC = "profiles/step_kernels_small_case_f32.txt"
 NCU_TRAFFIC_PER_EDGE = {
     "cmace_imp_bwd_edge_f32[no gradR]": (2675.0, _SRC),   # mean of a step's two launches (with / without the T array)
     "cmace_imp_fwd_f32": (2170.0, _SRC),
-    "cmace_gemm3x_gradr_f32": (403.0, _SRC),
+    "cmace_gemm3x_gradr_f32": (409.0, _SRC),
     "cmace_gemm3x_f32[K=64,N=512]": (2162.0, _SRC),
     "cmace_radial_hidden_fwd_f32": (925.0, _SRC),
     "cmace_radial_hidden_bwd_f32": (1126.0, _SRC),

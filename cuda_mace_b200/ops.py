@@ -41,9 +41,18 @@ def _suffix(t):
 
 
 def _check_cuda(*tensors):
+    """Every operand on the GPU, and on the CURRENT device: the entry points launch on the current device's
+    stream and allocate their outputs there (use torch.cuda.device(...) around calls for another GPU)."""
+    cur = None
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError("cuda_mace_b200 operators need CUDA tensors (there is no CPU path)")
+        if cur is None:
+            cur = torch.cuda.current_device()
+        if t.device.index != cur:
+            raise RuntimeError(f"operand on cuda:{t.device.index} while cuda:{cur} is the current device")
 
 
 class _RefCache:

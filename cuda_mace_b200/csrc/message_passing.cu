@@ -232,6 +232,31 @@ __device__ __forceinline__ void cursor_next(EdgeCursor &c, const int32_t *__rest
   cursor_seek(c, row_ptr, nnodes, stride);
 }
 
+// two floats in one 64-bit register and the arithmetic that handles both with one instruction: the edge pass is
+// bound by instruction issue, and every product and sum here runs over the four channels of a lane
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &a, float &b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// WANT_T / WANT_GR: whether T [E,C] and gradR [E,4,C] are written.  With neither (the first layer of a model whose
+// radial gradient is formed inside the GEMM) u[l,c] is not needed at all, and Y is not read: gradY does not depend
+// on it.
+template <bool WANT_T, bool WANT_GR>
 __global__ void __launch_bounds__(BS_WARPS * 32, 1)
     imp_bwd_edge_staged_kernel(const float *__restrict__ X, const float *__restrict__ Y, const float *__restrict__ R,
                                const float *__restrict__ G, const int32_t *__restrict__ sender,
@@ -286,19 +311,24 @@ __global__ void __launch_bounds__(BS_WARPS * 32, 1)
 
   const int c0 = lane * 4;
   const int ylm = lane & 15;
-  float g[16][4];
+  constexpr bool WANT_U = WANT_T || WANT_GR;
+  unsigned long long g2[16][2];   // G[node, m, c0 .. c0 + 3] as two register pairs
   int64_t g_node = -1;
-  float yv_next = cc.e >= 0 ? __ldg(Y + (int64_t)ylm * nedges + cc.e) : 0.f;
+  float yv_next = (WANT_U && cc.e >= 0) ? __ldg(Y + (int64_t)ylm * nedges + cc.e) : 0.f;
   while (cc.e >= 0) {
     const int64_t e = cc.e, node = cc.node;
     EdgeCursor nc = cc;
     cursor_next(nc, row_ptr, nnodes, stride);
     const float yv = yv_next;
-    if (nc.e >= 0) yv_next = __ldg(Y + (int64_t)ylm * nedges + nc.e);
+    if (WANT_U && nc.e >= 0) yv_next = __ldg(Y + (int64_t)ylm * nedges + nc.e);
     if (node != g_node) {
       g_node = node;
 #pragma unroll
-      for (int m = 0; m < 16; m++) load_vec<float, 4>(g[m], G + (node * 16 + m) * BS_C + c0);
+      for (int m = 0; m < 16; m++) {
+        const ulonglong2 v = __ldg(reinterpret_cast<const ulonglong2 *>(G + (node * 16 + m) * BS_C + c0));
+        g2[m][0] = v.x;
+        g2[m][1] = v.y;
+      }
     }
     // wait for the edge's slot
     const uint32_t slot = ring + (ccount % BS_SLOTS) * BS_SLOT_BYTES, bar = bar0 + 8 * (ccount % BS_SLOTS);
@@ -338,53 +368,59 @@ __global__ void __launch_bounds__(BS_WARPS * 32, 1)
         break;
       }
     }
-    float x[4], r[4][4];
-    {
-      float4 v;
-      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                   : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                   : "r"(slot + BS_R_BYTES + lane * 16));
-      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-#pragma unroll
-      for (int l = 0; l < 4; l++) {
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                     : "r"(slot + l * (BS_C * 4) + lane * 16));
-        r[l][0] = v.x; r[l][1] = v.y; r[l][2] = v.z; r[l][3] = v.w;
-      }
-    }
-    float u[4][4], p[16];
-#pragma unroll
-    for (int l = 0; l < 4; l++)
-#pragma unroll
-      for (int v = 0; v < 4; v++) u[l][v] = 0.f;
-#pragma unroll
-    for (int m = 0; m < 16; m++) {
-      const float y = __shfl_sync(0xffffffffu, yv, m);
-      float pm = 0.f;
-#pragma unroll
-      for (int v = 0; v < 4; v++) {
-        u[l_of_lm(m)][v] = fmaf(y, g[m][v], u[l_of_lm(m)][v]);
-        pm = fmaf(g[m][v], r[l_of_lm(m)][v] * x[v], pm);
-      }
-      p[m] = pm;
-    }
-    float t[4] = {0.f, 0.f, 0.f, 0.f};
+    unsigned long long x2[2], r2[4][2], rx2[4][2];
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(x2[0]), "=l"(x2[1]) : "r"(slot + BS_R_BYTES + lane * 16));
 #pragma unroll
     for (int l = 0; l < 4; l++) {
-      float gr[4];
+      asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];"
+                   : "=l"(r2[l][0]), "=l"(r2[l][1])
+                   : "r"(slot + l * (BS_C * 4) + lane * 16));
+      rx2[l][0] = mul2(r2[l][0], x2[0]);
+      rx2[l][1] = mul2(r2[l][1], x2[1]);
+    }
+    unsigned long long u2[4][2];
+    float p[16];
 #pragma unroll
-      for (int v = 0; v < 4; v++) {
-        t[v] = fmaf(u[l][v], r[l][v], t[v]);
-        gr[v] = x[v] * u[l][v];
+    for (int l = 0; l < 4; l++) u2[l][0] = u2[l][1] = 0ull;
+#pragma unroll
+    for (int m = 0; m < 16; m++) {
+      const int l = l_of_lm(m);
+      if (WANT_U) {
+        const float y = __shfl_sync(0xffffffffu, yv, m);
+        const unsigned long long yy = pack2(y, y);
+        u2[l][0] = fma2(yy, g2[m][0], u2[l][0]);
+        u2[l][1] = fma2(yy, g2[m][1], u2[l][1]);
       }
-      if (gradR != nullptr) store_vec_stream<float, 4>(gradR + (e * 4 + l) * BS_C + c0, gr);
+      const unsigned long long pm = fma2(g2[m][1], rx2[l][1], mul2(g2[m][0], rx2[l][0]));
+      float pa, pb;
+      unpack2(pm, pa, pb);
+      p[m] = pa + pb;
+    }
+    float t[4] = {0.f, 0.f, 0.f, 0.f};
+    if (WANT_T) {
+      unsigned long long t2[2] = {0ull, 0ull};
+#pragma unroll
+      for (int l = 0; l < 4; l++) {
+        t2[0] = fma2(u2[l][0], r2[l][0], t2[0]);
+        t2[1] = fma2(u2[l][1], r2[l][1], t2[1]);
+      }
+      unpack2(t2[0], t[0], t[1]);
+      unpack2(t2[1], t[2], t[3]);
+    }
+    if (WANT_GR) {
+#pragma unroll
+      for (int l = 0; l < 4; l++) {
+        float gr[4];
+        unpack2(mul2(x2[0], u2[l][0]), gr[0], gr[1]);
+        unpack2(mul2(x2[1], u2[l][1]), gr[2], gr[3]);
+        store_vec_stream<float, 4>(gradR + (e * 4 + l) * BS_C + c0, gr);
+      }
     }
     // every value read from the slot has been consumed by now: the next copy may go into it
     __syncwarp();
     ccount++;
     issue_one();
-    if (Tout != nullptr) store_vec<float, 4>(Tout + e * BS_C + c0, t);
+    if (WANT_T) store_vec<float, 4>(Tout + e * BS_C + c0, t);
     const float tot = warp_reduce16(p, lane);
     if ((lane & 1) == 0) gy[(int64_t)(lane >> 1) * nedges + e] = tot;
     cc = nc;
@@ -530,13 +566,19 @@ static int imp_bwd_edge(const T *X, const T *Y, const T *R, const T *G, const in
         if (num_sms <= 0) num_sms = 148;
       }
       const size_t smem = (size_t)BS_WARPS * BS_SLOTS * BS_SLOT_BYTES;
-      cudaError_t e = cudaFuncSetAttribute(imp_bwd_edge_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "cmace_imp_bwd_edge: %s", cudaGetErrorString(e));
       int64_t blocks = (nnodes + BS_WARPS - 1) / BS_WARPS;
       blocks = blocks < num_sms ? blocks : num_sms;
-      imp_bwd_edge_staged_kernel<<<(unsigned)blocks, BS_WARPS * 32, smem, st>>>(
-          X, Y, R, G, sender, row_ptr, nnodes, nedges, gradR, gy, Tout, staged_stall_flag());
-      return check_launch("cmace_imp_bwd_edge");
+      auto launch = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "cmace_imp_bwd_edge: %s", cudaGetErrorString(e));
+        kernel<<<(unsigned)blocks, BS_WARPS * 32, smem, st>>>(X, Y, R, G, sender, row_ptr, nnodes, nedges, gradR, gy,
+                                                              Tout, staged_stall_flag());
+        return check_launch("cmace_imp_bwd_edge");
+      };
+      if (Tout && gradR) return launch(imp_bwd_edge_staged_kernel<true, true>);
+      if (Tout) return launch(imp_bwd_edge_staged_kernel<true, false>);
+      if (gradR) return launch(imp_bwd_edge_staged_kernel<false, true>);
+      return launch(imp_bwd_edge_staged_kernel<false, false>);
     }
   }
   switch (vec) {

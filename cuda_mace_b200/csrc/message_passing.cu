@@ -232,27 +232,6 @@ __device__ __forceinline__ void cursor_next(EdgeCursor &c, const int32_t *__rest
   cursor_seek(c, row_ptr, nnodes, stride);
 }
 
-// two floats in one 64-bit register and the arithmetic that handles both with one instruction: the edge pass is
-// bound by instruction issue, and every product and sum here runs over the four channels of a lane
-__device__ __forceinline__ unsigned long long pack2(float a, float b) {
-  unsigned long long r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long v, float &a, float &b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
-  unsigned long long r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-
 // WANT_T / WANT_GR: whether T [E,C] and gradR [E,4,C] are written.  With neither (the first layer of a model whose
 // radial gradient is formed inside the GEMM) u[l,c] is not needed at all, and Y is not read: gradY does not depend
 // on it.

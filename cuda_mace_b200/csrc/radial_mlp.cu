@@ -5,18 +5,25 @@
 //
 // (the 1/sqrt(fan_in) factors and the normalisation constant of the activation are folded into the weights by
 // the caller).  The activations never leave the SM: a layer's accumulator is read from tensor memory, activated,
-// split into the hi / lo TF32 images and written to shared memory as the next layer's A operand.  Every product
-// uses the 3-term split  Ahi*Bhi + Ahi*Blo + Alo*Bhi  with the float32 accumulator in tensor memory, three
-// tcgen05.mma per K step into the same columns (one tensor-memory load per value in the elementwise phase).
+// split into the hi / lo TF32 images and written back as the next layer's A operand.  Every product uses the
+// 3-term split  Ahi*Bhi + Ahi*Blo + Alo*Bhi  with the float32 accumulator in tensor memory, three tcgen05.mma per
+// K step into the same columns (one tensor-memory load per value in the elementwise phase).
 // The forward stores the activation derivatives d_k = silu'(z_k) (three [E, 64] arrays in a tiled layout that
 // both kernels access with coalesced 16-byte transfers); the backward is then three products with an
 // elementwise factor between them and needs no special-function work.
 //
-// One CTA per SM, two independent groups of eight warps.  A group works on one 128-edge tile at a time and
-// runs its layers one after the other (write A, barrier, one thread issues the MMAs, everybody waits for
-// their completion, read the accumulator); while one group waits for the tensor core the other one does
-// its elementwise phase.  The weights (80 KB forward, 72 KB backward) are loaded into shared memory once.
-// Every mbarrier wait is bounded: on a time-out the group records a code in *status and leaves its loop.
+// One CTA per SM, two independent groups of eight warps; the weights (80 KB forward, 72 KB backward) are loaded
+// into shared memory once.  A tile's layers form a chain: elementwise phase, hand-over, MMAs, completion,
+// accumulator load, next elementwise phase; the fixed latencies of that chain are longer than the arithmetic.
+// Forward: every group keeps TWO 128-edge tiles in flight and alternates between them, so one tile's
+// elementwise phase runs while the other tile's products are on the tensor core; a warp of its own issues each
+// group's MMAs, so no elementwise warp is held up by the issue.  Four tiles per SM need four operand buffers: the
+// raw values (= hi image) of the 64 activations go to shared memory (32 KB a tile), their residual image to
+// tensor memory, from where the third product term reads its A operand.
+// Backward: a group works on one tile at a time (write A, barrier, one thread issues the MMAs, everybody waits
+// for their completion, read the accumulator); while one group waits for the tensor core the other one does
+// its elementwise phase.
+// Every mbarrier wait is bounded: on a time-out the role records a code in *status and leaves its loop.
 #include <cstring>
 
 #include "common.cuh"
@@ -32,7 +39,13 @@ constexpr int RH_A_SLAB = RH_TILE * 128;    // one image (hi or lo) of one 32-co
 constexpr int RH_A_GROUP = 4 * RH_A_SLAB;   // two K blocks x (hi, lo)
 constexpr int RH_W_SMALL = 2 * 64 * 128;    // packed [nb <= 32, 64]: one K block, hi + lo images of 64 rows
 constexpr int RH_W_BIG = 2 * RH_W_SMALL;    // packed [64, 64]: two K blocks
-constexpr int RH_TMEM_COLS = 128;           // two groups x 64 accumulator columns
+constexpr int RH_TMEM_COLS = 128;           // backward: two groups x 64 accumulator columns
+// forward
+constexpr int RF_THREADS = RH_THREADS + 64;   // + one MMA-issuing warp per group
+constexpr int RF_SLOT_BYTES = 2 * RH_A_SLAB;  // operand buffer of a tile in flight: raw images of two K blocks
+                                              // (first layer: raw and residual image of the basis)
+constexpr int RF_TMEM_SLOT = 128;             // tensor-memory columns of a tile in flight: 64 accumulator + 64 residual
+constexpr int RF_TMEM_COLS = 4 * RF_TMEM_SLOT;
 
 struct RadialArgs {
   const float *in;        // forward: basis [E, nb]; backward: grad h3 [E, 64]
@@ -102,8 +115,264 @@ __device__ __forceinline__ void silu_both(float z, float &a, float &d) {
   d = s * fmaf(z, 1.0f - s, 1.0f);
 }
 
-template <bool BACKWARD>
-__global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const RadialArgs g) {
+// special-function unit: 2^x and 1/x, about 2 ulp and 1 ulp
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// silu(z) = z s and silu'(z) = s (1 + z (1 - s)), s = 1 / (1 + 2^(-z log2 e)), for two values at once: four
+// special-function and six packed instructions per pair.  Large |z| saturate cleanly (s = 0 or 1), no NaN.
+__device__ __forceinline__ void silu_both2(unsigned long long z2, unsigned long long &a2, unsigned long long &d2) {
+  const unsigned long long one2 = pack2(1.0f, 1.0f);
+  float t0, t1;
+  unpack2(mul2(z2, pack2(-1.4426950408889634f, -1.4426950408889634f)), t0, t1);
+  float n0, n1;
+  unpack2(add2(pack2(ex2_approx(t0), ex2_approx(t1)), one2), n0, n1);
+  const unsigned long long s2 = pack2(rcp_approx(n0), rcp_approx(n1));
+  a2 = mul2(z2, s2);
+  d2 = mul2(s2, fma2(z2, fma2(s2, pack2(-1.0f, -1.0f), one2), one2));
+}
+
+// The products of one forward layer for a tile in flight.  First layer: A = the basis, raw image in slab 0 and
+// residual image in slab 1 of the tile's buffer, K = nb.  Other layers: K = 64, raw images of the two K blocks in
+// the two slabs, residual image in tensor memory (column k of the tile's residual region = column k of A).
+__device__ __forceinline__ void issue_fwd_layer(uint32_t acc, uint32_t lo_tmem, uint32_t sA, uint32_t sB, bool first,
+                                                int nb) {
+  const uint32_t idesc = umma_idesc_tf32(RH_TILE, RH_H);
+  const uint32_t b_image = (uint32_t)RH_H * 128u;
+  if (first) {
+    const uint64_t a_hi = umma_desc_sw128(sA), a_lo = umma_desc_sw128(sA + RH_A_SLAB);
+    const uint64_t b_hi = umma_desc_sw128(sB), b_lo = umma_desc_sw128(sB + b_image);
+    for (int j = 0; j < nb / 8; j++) {
+      umma_tf32(acc, a_hi + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc, j != 0);
+      umma_tf32_acc(acc, a_hi + (uint64_t)(2 * j), b_lo + (uint64_t)(2 * j), idesc);
+      umma_tf32_acc(acc, a_lo + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc);
+    }
+    return;
+  }
+#pragma unroll
+  for (int kb = 0; kb < 2; kb++) {
+    const uint64_t a_hi = umma_desc_sw128(sA + kb * RH_A_SLAB);
+    const uint64_t b_hi = umma_desc_sw128(sB + kb * 2 * b_image);
+    const uint64_t b_lo = umma_desc_sw128(sB + kb * 2 * b_image + b_image);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      umma_tf32(acc, a_hi + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc, (kb | j) != 0);
+      umma_tf32_acc(acc, a_hi + (uint64_t)(2 * j), b_lo + (uint64_t)(2 * j), idesc);
+      umma_tf32_ts_acc(acc, lo_tmem + 32u * kb + 8u * j, b_hi + (uint64_t)(2 * j), idesc);
+    }
+  }
+}
+
+// NI: 16-byte chunks of the basis a thread carries per tile (256 threads x NI chunks cover 128 rows of nb floats:
+// 1 for nb = 8, 4 up to nb = 32)
+template <int NI>
+__global__ void __launch_bounds__(RF_THREADS, 1)
+    radial_hidden_fwd_kernel(const RadialArgs g, const __grid_constant__ CUtensorMap out_map) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bars[9];   // weights; ready[group][slot]; done[group][slot]
+  __shared__ uint32_t tmem_base_slot;
+
+  const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool mma_role = warp >= 16;
+  const int group = mma_role ? warp - 16 : warp >> 3;
+  const uint32_t wbar = smem_u32(&bars[0]);
+  const uint32_t ready0 = wbar + 8u * (1 + 2 * group);   // + 8 * slot
+  const uint32_t done0 = wbar + 8u * (5 + 2 * group);
+
+  const uint32_t w_bytes[3] = {(uint32_t)RH_W_SMALL, (uint32_t)RH_W_BIG, (uint32_t)RH_W_BIG};
+  const uint32_t sW[3] = {smem_base, smem_base + w_bytes[0], smem_base + w_bytes[0] + w_bytes[1]};
+  const uint32_t sA0 = smem_base + w_bytes[0] + w_bytes[1] + w_bytes[2] + (uint32_t)(2 * group) * RF_SLOT_BYTES;
+
+  if (tid == 0) {
+    mbar_init(wbar, 1);
+    for (int i = 0; i < 4; i++) {
+      mbar_init(wbar + 8u * (1 + i), 8);   // ready: one arrival per elementwise warp of the group
+      mbar_init(wbar + 8u * (5 + i), 1);   // done: the commit of the layer's MMAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(smem_u32(&tmem_base_slot), RF_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem0 = tmem_base_slot + (uint32_t)(2 * group) * RF_TMEM_SLOT;   // + slot * RF_TMEM_SLOT; residual at + 64
+
+  if (tid == 0) {
+    mbar_arrive_expect_tx(wbar, w_bytes[0] + w_bytes[1] + w_bytes[2]);
+    for (int i = 0; i < 3; i++)
+      for (uint32_t off = 0; off < w_bytes[i]; off += 8192u) {
+        const uint32_t n = w_bytes[i] - off < 8192u ? w_bytes[i] - off : 8192u;
+        bulk_copy_g2s(sW[i] + off, reinterpret_cast<const unsigned char *>(g.w[i]) + off, n, wbar);
+      }
+  }
+  bool ok = warp_wait(wbar, 0, lane);
+  if (!ok && lane == 0 && g.status) atomicCAS(g.status, 0, 11);
+
+  // the group's tiles: first, first + step, ...; tile number j of the group uses slot j & 1, and the two slots
+  // move through their layers side by side
+  const int64_t ntiles = (g.E + RH_TILE - 1) / RH_TILE;
+  const int64_t step = (int64_t)gridDim.x * 2;
+  const int64_t first = (int64_t)blockIdx.x * 2 + group;
+
+  if (mma_role) {
+    if (lane == 0) {
+      uint32_t phase = 0;   // both slots' ready barriers complete once per layer: one parity bit serves them
+      for (int64_t t0 = first; ok && t0 < ntiles; t0 += 2 * step) {
+        const int nslots = t0 + step < ntiles ? 2 : 1;
+        for (int layer = 0; ok && layer < 3; layer++) {
+          for (int s = 0; s < nslots; s++) {
+            if (!mbar_wait(ready0 + 8u * s, phase)) {
+              if (g.status) atomicCAS(g.status, 0, 13);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t acc = tmem0 + (uint32_t)s * RF_TMEM_SLOT;
+            issue_fwd_layer(acc, acc + 64u, sA0 + (uint32_t)s * RF_SLOT_BYTES, sW[layer], layer == 0, g.nb);
+            umma_commit(done0 + 8u * s);
+          }
+          phase ^= 1;
+        }
+        // a lone last tile leaves slot 1's barriers untouched, and it is the last thing this group does
+      }
+    }
+  } else {
+    const int gw = warp & 7, gtid = tid & (RH_GROUP_THREADS - 1);
+    const int q = gw & 3, h = gw >> 2;      // tensor-memory lane quarter, column half (= K block of the next layer)
+    const int r = q * 32 + lane;            // row of the tile this thread owns in the elementwise phases
+    const uint32_t lane_field = (uint32_t)(q * 32) << 16;
+    const int nchunks = g.nb / 4;           // 16-byte chunks per row of the basis
+    uint32_t phase = 0;
+
+    // the basis rows of a tile: up to four 16-byte chunks per thread, fetched a whole pass ahead
+    float4 pre[2][NI];
+    auto load_basis = [&](int64_t t, float4 (&dst)[NI]) {
+#pragma unroll
+      for (int i = 0; i < NI; i++) {
+        const int idx = gtid + RH_GROUP_THREADS * i;
+        const int rr = idx / nchunks, c = idx - rr * nchunks;
+        const int64_t ee = t * RH_TILE + rr;
+        dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t < ntiles && rr < RH_TILE && ee < g.E) dst[i] = __ldg(reinterpret_cast<const float4 *>(g.in + ee * g.nb) + c);
+      }
+    };
+    load_basis(first, pre[0]);
+    load_basis(first + step, pre[1]);
+
+    for (int64_t t0 = first; ok && t0 < ntiles; t0 += 2 * step) {
+      const int nslots = t0 + step < ntiles ? 2 : 1;
+      if (t0 != first) {
+        // the tile stores of the previous pass read the buffers that are written next
+        if (gtid == 0) tma_store_wait_read();
+        group_sync(group);
+      }
+      // ---- first layer's operand: the basis rows, raw image in slab 0, residual image in slab 1
+#pragma unroll
+      for (int s = 0; s < 2; s++) {
+        if (s < nslots) {
+          const uint32_t sA = sA0 + (uint32_t)s * RF_SLOT_BYTES;
+#pragma unroll
+          for (int i = 0; i < NI; i++) {
+            const int idx = gtid + RH_GROUP_THREADS * i;
+            const int rr = idx / nchunks, c = idx - rr * nchunks;
+            if (rr < RH_TILE) store_split(sA + (uint32_t)sw128_offset(rr, c), pre[s][i]);
+          }
+          tc_fence_before();      // orders this warp's accumulator loads of the previous pass before the new MMAs
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(ready0 + 8u * s);
+        }
+      }
+      for (int layer = 0; ok && layer < 3; layer++) {
+        if (layer == 2) {
+          load_basis(t0 + 2 * step, pre[0]);
+          load_basis(t0 + 3 * step, pre[1]);
+        }
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+          if (s < nslots && ok) {
+            const int64_t tile = t0 + s * step;
+            const uint32_t acc = tmem0 + (uint32_t)s * RF_TMEM_SLOT + lane_field;
+            const uint32_t a_row = sA0 + (uint32_t)s * RF_SLOT_BYTES + (uint32_t)h * RH_A_SLAB;
+            float4 *dtile = g.dsave + ((tile * 3 + layer) * 16 + h * 8) * RH_TILE + r;   // + chunk * 128
+            if (!warp_wait(done0 + 8u * s, phase, lane)) {
+              if (lane == 0 && g.status) atomicCAS(g.status, 0, 12);
+              ok = false;
+            } else {
+              tc_fence_after();
+              uint32_t v[32];
+              tmem_ld32_nowait(acc + 32u * h, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int hh = 0; hh < 2; hh++) {          // 16 columns at a time: one tensor-memory store each
+                uint32_t lo[16];
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                  const int col = 16 * hh + 4 * c;
+                  unsigned long long a01, a23, d01, d23;
+                  silu_both2(pack2(__uint_as_float(v[col]), __uint_as_float(v[col + 1])), a01, d01);
+                  silu_both2(pack2(__uint_as_float(v[col + 2]), __uint_as_float(v[col + 3])), a23, d23);
+                  float4 d;
+                  unpack2(d01, d.x, d.y);
+                  unpack2(d23, d.z, d.w);
+                  if (g.dsave != nullptr) dtile[(4 * hh + c) * RH_TILE] = d;
+                  // layers 1, 2: the raw values are the next operand's hi image.  Layer 3: the same swizzled 128-row
+                  // x 32-column image is what the tile store of h3 reads (a thread owns a row: stores from registers
+                  // would hit 32 different 128-byte lines per instruction, which measured 0.3 ms of a 0.85 ms kernel)
+                  asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(a_row + (uint32_t)sw128_offset(r, 4 * hh + c)),
+                               "l"(a01), "l"(a23)
+                               : "memory");
+                  if (layer < 2) {
+                    // the residual a - trunc(a) is exact in float32 and is read by the tensor core with the same
+                    // truncation as the hi image (error below 2^-20 |a|)
+                    const unsigned long long l01 = sub2(a01, a01 & 0xFFFFE000FFFFE000ull);
+                    const unsigned long long l23 = sub2(a23, a23 & 0xFFFFE000FFFFE000ull);
+                    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo[4 * c]), "=r"(lo[4 * c + 1]) : "l"(l01));
+                    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo[4 * c + 2]), "=r"(lo[4 * c + 3]) : "l"(l23));
+                  }
+                }
+                if (layer < 2) tmem_st16(acc + 64u + 32u * h + 16u * hh, lo);
+              }
+              if (layer < 2) {
+                tmem_st_wait();
+                tc_fence_before();
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ready0 + 8u * s);
+              } else {
+                // h3 [128, 64] of the tile: two 32-column boxes, rows past the end of the array are clipped
+                fence_proxy_async();
+                group_sync(group);
+                if (gtid == 0) {
+                  const uint32_t sT = sA0 + (uint32_t)s * RF_SLOT_BYTES;
+                  tma_store_2d(&out_map, 0, (int)(tile * RH_TILE), sT);
+                  tma_store_2d(&out_map, 32, (int)(tile * RH_TILE), sT + RH_A_SLAB);
+                }
+              }
+            }
+          }
+        }
+        phase ^= 1;
+      }
+    }
+    if (gtid == 0) tma_store_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base_slot, RF_TMEM_COLS);
+}
+
+__global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_bwd_kernel(const RadialArgs g) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[3];
   __shared__ uint32_t tmem_base_slot;
@@ -114,9 +383,8 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
   const uint32_t wbar = smem_u32(&bars[0]);
   const uint32_t mma_bar = smem_u32(&bars[1 + group]);
 
-  // weights: forward W1 (one K block), W2, W3; backward W3^T, W2^T, W1^T (narrow)
-  const uint32_t w_bytes[3] = {BACKWARD ? (uint32_t)RH_W_BIG : (uint32_t)RH_W_SMALL, (uint32_t)RH_W_BIG,
-                               BACKWARD ? 2u * 2u * (uint32_t)g.npad_last * 128u : (uint32_t)RH_W_BIG};
+  // weights: W3^T, W2^T, W1^T (narrow)
+  const uint32_t w_bytes[3] = {(uint32_t)RH_W_BIG, (uint32_t)RH_W_BIG, 2u * 2u * (uint32_t)g.npad_last * 128u};
   const uint32_t sW[3] = {smem_base, smem_base + w_bytes[0], smem_base + w_bytes[0] + w_bytes[1]};
   const uint32_t sA = smem_base + w_bytes[0] + w_bytes[1] + w_bytes[2] + group * RH_A_GROUP;
 
@@ -149,8 +417,6 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
   const uint32_t a_row = sA + h * 2 * RH_A_SLAB;   // hi slab of K block h
   uint32_t phase = 0;
   const int64_t ntiles = (g.E + RH_TILE - 1) / RH_TILE;
-  const int nchunks = g.nb / 4;           // 16-byte chunks per row of the basis
-
   // one layer = start_layer (barrier, MMAs issued by one thread) ... finish_layer (wait for them); whatever is
   // placed between the two overlaps with the tensor core: the global loads of the next elementwise phase
   auto start_layer = [&](uint32_t sB, int K, int npad) {
@@ -172,58 +438,7 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_kernel(const Radi
   const int64_t tile_step = (int64_t)gridDim.x * 2;
   int64_t tile = (int64_t)blockIdx.x * 2 + group;
 
-  if (!BACKWARD) {
-    // the basis rows of a tile: one or two 16-byte chunks per thread, fetched one tile ahead
-    float4 pre[4];
-    auto load_basis = [&](int64_t t) {
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const int idx = gtid + RH_GROUP_THREADS * i;
-        const int rr = idx / nchunks, c = idx - rr * nchunks;
-        const int64_t ee = t * RH_TILE + rr;
-        pre[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (t < ntiles && rr < RH_TILE && ee < g.E) pre[i] = __ldg(reinterpret_cast<const float4 *>(g.in + ee * g.nb) + c);
-      }
-    };
-    load_basis(tile);
-    for (; ok && tile < ntiles; tile += tile_step) {
-      const int64_t e = tile * RH_TILE + r;
-      const bool row_ok = e < g.E;
-      float4 *dtile = g.dsave + (tile * 3) * 16 * RH_TILE + (h * 8) * RH_TILE + r;   // + (layer*16 + chunk)*128
-      // ---- layer 1 operand: the basis rows, raw + residual images, K block 0
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const int idx = gtid + RH_GROUP_THREADS * i;
-        const int rr = idx / nchunks, c = idx - rr * nchunks;
-        if (rr < RH_TILE) store_split(sA + (uint32_t)sw128_offset(rr, c), pre[i]);
-      }
-      start_layer(sW[0], g.nb, RH_H);
-      load_basis(tile + tile_step);
-      if (!(ok = finish_layer())) break;
-      for (int layer = 0; layer < 3; layer++) {
-uint32_t v[32];
-        tmem_ld32_nowait(t_row + 32 * h, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-          float4 a, d;
-          silu_both(__uint_as_float(v[4 * c]), a.x, d.x);
-          silu_both(__uint_as_float(v[4 * c + 1]), a.y, d.y);
-          silu_both(__uint_as_float(v[4 * c + 2]), a.z, d.z);
-          silu_both(__uint_as_float(v[4 * c + 3]), a.w, d.w);
-          if (layer < 2)
-            store_split(a_row + (uint32_t)sw128_offset(r, c), a);
-          else if (row_ok)
-            *reinterpret_cast<float4 *>(g.out + e * RH_H + 32 * h + 4 * c) = a;
-          if (g.dsave != nullptr) dtile[(layer * 16 + c) * RH_TILE] = d;
-        }
-        if (layer < 2) {
-          start_layer(sW[layer + 1], RH_H, RH_H);
-          if (!(ok = finish_layer())) break;
-        }
-      }
-    }
-  } else {
+  {
     // grad h3 and d3 of a tile are fetched while the previous tile's last product runs; d2 and d1 while the
     // product that precedes their use runs
     float4 pg[8], pd[8];
@@ -317,14 +532,23 @@ static int radial_launch(RadialArgs &g, bool backward, const char *what, cudaStr
     if (num_sms <= 0) num_sms = 148;
   }
   const size_t w_total = backward ? (size_t)2 * RH_W_BIG + (size_t)4 * g.npad_last * 128 : (size_t)RH_W_SMALL + 2 * RH_W_BIG;
-  const size_t smem = w_total + 2 * (size_t)RH_A_GROUP + 1024;
-  auto kern = backward ? radial_hidden_kernel<true> : radial_hidden_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  const size_t smem = w_total + (backward ? 2 * (size_t)RH_A_GROUP : 4 * (size_t)RF_SLOT_BYTES) + 1024;
   const int64_t ntiles = (g.E + RH_TILE - 1) / RH_TILE;
   int64_t blocks = (ntiles + 1) / 2;
   blocks = blocks < num_sms ? blocks : num_sms;
-  kern<<<(unsigned)blocks, RH_THREADS, smem, st>>>(g);
+  if (backward) {
+    cudaError_t e = cudaFuncSetAttribute(radial_hidden_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    radial_hidden_bwd_kernel<<<(unsigned)blocks, RH_THREADS, smem, st>>>(g);
+  } else {
+    if (ntiles * RH_TILE > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many edges", what);
+    CUtensorMap out_map;   // h3 [E, 64] as 128-row x 32-column boxes
+    if (int rc = encode_rows_tensor_map(&out_map, g.out, g.E, RH_H, what)) return rc;
+    auto kern = g.nb == 8 ? radial_hidden_fwd_kernel<1> : radial_hidden_fwd_kernel<4>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    kern<<<(unsigned)blocks, RF_THREADS, smem, st>>>(g, out_map);
+  }
   return check_launch(what);
 }
 

@@ -374,7 +374,7 @@ def test_contraction_generated_and_table_driven_kernels_agree(dtype, dev, U, mon
     assert rel_err(results[0][0], results[1][0]) < TOL[dtype]["out"]
 
 
-@pytest.mark.parametrize("E,nb", [(3000, 8), (128, 8), (517, 16), (1, 32), (70000, 8)])
+@pytest.mark.parametrize("E,nb", [(3000, 8), (128, 8), (517, 16), (1, 32), (70000, 8), (400000, 8), (150000, 24)])
 def test_hidden_radial_layers_in_one_kernel(E, nb, dev):
     """Three hidden layers with their activations on chip against the oracle's perceptron without its last
     layer: value and gradient with respect to the basis, ragged last tile included."""

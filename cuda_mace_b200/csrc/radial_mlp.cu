@@ -36,11 +36,8 @@ constexpr int RH_TILE = 128;                // edges per tile
 constexpr int RH_GROUP_THREADS = 256;       // eight warps
 constexpr int RH_THREADS = 2 * RH_GROUP_THREADS;
 constexpr int RH_A_SLAB = RH_TILE * 128;    // one image (hi or lo) of one 32-column K block: 16 KB
-constexpr int RH_A_GROUP = 4 * RH_A_SLAB;   // two K blocks x (hi, lo)
 constexpr int RH_W_SMALL = 2 * 64 * 128;    // packed [nb <= 32, 64]: one K block, hi + lo images of 64 rows
 constexpr int RH_W_BIG = 2 * RH_W_SMALL;    // packed [64, 64]: two K blocks
-constexpr int RH_TMEM_COLS = 128;           // backward: two groups x 64 accumulator columns
-// forward
 constexpr int RF_THREADS = RH_THREADS + 64;   // + one MMA-issuing warp per group
 constexpr int RF_SLOT_BYTES = 2 * RH_A_SLAB;  // operand buffer of a tile in flight: raw images of two K blocks
                                               // (first layer: raw and residual image of the basis)
@@ -70,28 +67,6 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// One layer's products for a 128-row tile: A images at sA (per K block: hi slab, lo slab), packed weights at sB
-// (per K block: hi image then lo image of npad rows).  The three terms Ahi*Bhi + Ahi*Blo + Alo*Bhi accumulate into
-// the same npad columns, so the elementwise phase reads each value once and needs no addition.
-__device__ __forceinline__ void issue_layer(uint32_t d_tmem, uint32_t sA, uint32_t sB, int K, int npad) {
-  const uint32_t idesc = umma_idesc_tf32(RH_TILE, npad);
-  const uint32_t b_image = (uint32_t)npad * 128u, b_block = 2u * b_image;
-  for (int k0 = 0, kb = 0; k0 < K; k0 += 32, kb++) {
-    const uint64_t a_hi = umma_desc_sw128(sA + kb * 2 * RH_A_SLAB);
-    const uint64_t a_lo = umma_desc_sw128(sA + kb * 2 * RH_A_SLAB + RH_A_SLAB);
-    const uint64_t b_hi = umma_desc_sw128(sB + kb * b_block);
-    const uint64_t b_lo = umma_desc_sw128(sB + kb * b_block + b_image);
-    int ksteps = (K - k0) / 8;
-    ksteps = ksteps > 4 ? 4 : ksteps;
-    for (int j = 0; j < ksteps; j++) {
-      // K step j starts 32 bytes = 2 address units further into every row
-      umma_tf32(d_tmem, a_hi + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc, (kb | j) != 0);
-      umma_tf32_acc(d_tmem, a_hi + (uint64_t)(2 * j), b_lo + (uint64_t)(2 * j), idesc);
-      umma_tf32_acc(d_tmem, a_lo + (uint64_t)(2 * j), b_hi + (uint64_t)(2 * j), idesc);
-    }
-  }
-}
-
 __device__ __forceinline__ void store_split(uint32_t s_hi, float4 a) {
   // raw values are the hi image (the tensor core ignores the low 13 mantissa bits), lo = tf32(a - trunc(a))
   float4 lo;
@@ -103,16 +78,6 @@ __device__ __forceinline__ void store_split(uint32_t s_hi, float4 a) {
   asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(s_hi + RH_A_SLAB), "f"(lo.x), "f"(lo.y), "f"(lo.z),
                "f"(lo.w)
                : "memory");
-}
-
-__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ void silu_both(float z, float &a, float &d) {
-  const float s = sigmoid_fast(z);
-  a = z * s;
-  d = s * fmaf(z, 1.0f - s, 1.0f);
 }
 
 // special-function unit: 2^x and 1/x, about 2 ulp and 1 ulp
@@ -140,13 +105,14 @@ __device__ __forceinline__ void silu_both2(unsigned long long z2, unsigned long 
   d2 = mul2(s2, fma2(z2, fma2(s2, pack2(-1.0f, -1.0f), one2), one2));
 }
 
-// The products of one forward layer for a tile in flight.  First layer: A = the basis, raw image in slab 0 and
-// residual image in slab 1 of the tile's buffer, K = nb.  Other layers: K = 64, raw images of the two K blocks in
-// the two slabs, residual image in tensor memory (column k of the tile's residual region = column k of A).
-__device__ __forceinline__ void issue_fwd_layer(uint32_t acc, uint32_t lo_tmem, uint32_t sA, uint32_t sB, bool first,
-                                                int nb) {
-  const uint32_t idesc = umma_idesc_tf32(RH_TILE, RH_H);
-  const uint32_t b_image = (uint32_t)RH_H * 128u;
+// The products of one layer for a tile in flight, into npad accumulator columns.  `first` (forward, layer 1): A =
+// the basis, raw image in slab 0 and residual image in slab 1 of the tile's buffer, K = nb.  Otherwise K = 64: raw
+// images of the two K blocks in the two slabs, residual image in tensor memory (column k of the tile's residual
+// region = column k of A).  sB: packed weights, per K block the hi image then the lo image of npad rows.
+__device__ __forceinline__ void issue_tile_layer(uint32_t acc, uint32_t lo_tmem, uint32_t sA, uint32_t sB, bool first,
+                                                 int nb, int npad) {
+  const uint32_t idesc = umma_idesc_tf32(RH_TILE, npad);
+  const uint32_t b_image = (uint32_t)npad * 128u;
   if (first) {
     const uint64_t a_hi = umma_desc_sw128(sA), a_lo = umma_desc_sw128(sA + RH_A_SLAB);
     const uint64_t b_hi = umma_desc_sw128(sB), b_lo = umma_desc_sw128(sB + b_image);
@@ -237,7 +203,7 @@ __global__ void __launch_bounds__(RF_THREADS, 1)
             }
             tc_fence_after();
             const uint32_t acc = tmem0 + (uint32_t)s * RF_TMEM_SLOT;
-            issue_fwd_layer(acc, acc + 64u, sA0 + (uint32_t)s * RF_SLOT_BYTES, sW[layer], layer == 0, g.nb);
+            issue_tile_layer(acc, acc + 64u, sA0 + (uint32_t)s * RF_SLOT_BYTES, sW[layer], layer == 0, g.nb, RH_H);
             umma_commit(done0 + 8u * s);
           }
           phase ^= 1;
@@ -372,33 +338,46 @@ __global__ void __launch_bounds__(RF_THREADS, 1)
   if (warp == 0) tmem_dealloc(tmem_base_slot, RF_TMEM_COLS);
 }
 
-__global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_bwd_kernel(const RadialArgs g) {
+// ---- backward ------------------------------------------------------------------------------------------
+// Same arrangement as the forward: two tiles in flight per group, raw images in shared memory (32 KB a tile),
+// residual images in tensor memory.  A tile goes through four phases:
+//   0  operand = grad h3 * d3 (the grad h3 tile was put into the tile's buffer by TMA, a thread multiplies its own
+//      row in place), product with W3^T;   1  operand = accumulator * d2, product with W2^T;
+//   2  operand = accumulator * d1, product with W1^T (narrow);   3  grad basis = accumulator columns [0, nb).
+// The derivatives of the phase a tile enters next are fetched into registers as soon as the current phase has
+// consumed its own (32 registers per tile in flight), so they are on their way during the other tile's phase;
+// the grad h3 tile of a buffer's next tile is requested in phase 3, when the last product that read the buffer
+// has completed.  (Pulling the next pass's derivative arrays into L2 ahead of time measured slower: 0.89 against
+// 0.73 ms.  What bounds the kernel is the bytes the register buffers keep in flight: 64 registers x 512 threads,
+// in flight for about 70 % of the time.)  The MMAs are issued by the first thread of the group after the group's barrier: the elementwise
+// phases are short here (no special functions), and a warp of its own would cost every thread 32 registers.
+__global__ void __launch_bounds__(RH_THREADS, 1)
+    radial_hidden_bwd_kernel(const RadialArgs g, const __grid_constant__ CUtensorMap in_map) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[3];
+  __shared__ __align__(8) uint64_t bars[9];   // weights; done[group][slot]; grad h3 tile landed [group][slot]
   __shared__ uint32_t tmem_base_slot;
 
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int group = warp >> 3, gw = warp & 7, gtid = tid & (RH_GROUP_THREADS - 1);
   const uint32_t wbar = smem_u32(&bars[0]);
-  const uint32_t mma_bar = smem_u32(&bars[1 + group]);
+  const uint32_t done0 = wbar + 8u * (1 + 2 * group);   // + 8 * slot
+  const uint32_t gin0 = wbar + 8u * (5 + 2 * group);
 
   // weights: W3^T, W2^T, W1^T (narrow)
   const uint32_t w_bytes[3] = {(uint32_t)RH_W_BIG, (uint32_t)RH_W_BIG, 2u * 2u * (uint32_t)g.npad_last * 128u};
   const uint32_t sW[3] = {smem_base, smem_base + w_bytes[0], smem_base + w_bytes[0] + w_bytes[1]};
-  const uint32_t sA = smem_base + w_bytes[0] + w_bytes[1] + w_bytes[2] + group * RH_A_GROUP;
+  const uint32_t sA0 = smem_base + w_bytes[0] + w_bytes[1] + w_bytes[2] + (uint32_t)(2 * group) * RF_SLOT_BYTES;
 
   if (tid == 0) {
-    mbar_init(wbar, 1);
-    mbar_init(wbar + 8, 1);
-    mbar_init(wbar + 16, 1);
+    for (int i = 0; i < 9; i++) mbar_init(wbar + 8u * i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) tmem_alloc(smem_u32(&tmem_base_slot), RH_TMEM_COLS);
+  if (warp == 0) tmem_alloc(smem_u32(&tmem_base_slot), RF_TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = tmem_base_slot + group * RH_H;
+  const uint32_t tmem0 = tmem_base_slot + (uint32_t)(2 * group) * RF_TMEM_SLOT;
 
   if (tid == 0) {
     mbar_arrive_expect_tx(wbar, w_bytes[0] + w_bytes[1] + w_bytes[2]);
@@ -413,114 +392,171 @@ __global__ void __launch_bounds__(RH_THREADS, 1) radial_hidden_bwd_kernel(const 
 
   const int q = gw & 3, h = gw >> 2;      // tensor-memory lane quarter, column half (= K block of the next layer)
   const int r = q * 32 + lane;            // row of the tile this thread owns in the elementwise phases
-  const uint32_t t_row = tmem_acc + ((uint32_t)(q * 32) << 16);
-  const uint32_t a_row = sA + h * 2 * RH_A_SLAB;   // hi slab of K block h
-  uint32_t phase = 0;
+  const uint32_t lane_field = (uint32_t)(q * 32) << 16;
   const int64_t ntiles = (g.E + RH_TILE - 1) / RH_TILE;
-  // one layer = start_layer (barrier, MMAs issued by one thread) ... finish_layer (wait for them); whatever is
-  // placed between the two overlaps with the tensor core: the global loads of the next elementwise phase
-  auto start_layer = [&](uint32_t sB, int K, int npad) {
+  const int64_t step = (int64_t)gridDim.x * 2;
+  const int64_t first = (int64_t)blockIdx.x * 2 + group;
+
+  // grad h3 [128, 64] of a tile into the buffer of slot s: two 32-column boxes, rows past the end read as zero
+  auto request_g = [&](int s, int64_t tile) {
+    if (tile >= ntiles) return;
+    const uint32_t dst = sA0 + (uint32_t)s * RF_SLOT_BYTES, bar = gin0 + 8u * s;
+    mbar_arrive_expect_tx(bar, 2u * RH_A_SLAB);
+    tma_load_2d(dst, &in_map, 0, (int)(tile * RH_TILE), bar);
+    tma_load_2d(dst + RH_A_SLAB, &in_map, 32, (int)(tile * RH_TILE), bar);
+  };
+  // d_{layer+1} of a tile: this thread's row, its 32 columns (8 chunks of 16 bytes, 512 bytes apart in the tiled array)
+  float4 buf[2][8];
+  auto load_d = [&](float4 (&dst)[8], int64_t tile, int layer) {
+    if (tile >= ntiles) return;
+    const float4 *dt = g.dsave + ((tile * 3 + layer) * 16 + h * 8) * RH_TILE + r;
+#pragma unroll
+    for (int c = 0; c < 8; c++) dst[c] = dt[c * RH_TILE];
+  };
+  // the whole group has written its part of the operand: one thread issues the layer's products
+  auto hand_over = [&](int s, int layer) {
+    tmem_st_wait();
     tc_fence_before();
     fence_proxy_async();
     group_sync(group);
     if (gtid == 0) {
       tc_fence_after();
-      issue_layer(tmem_acc, sA, sB, K, npad);
-      umma_commit(mma_bar);
+      const uint32_t acc = tmem0 + (uint32_t)s * RF_TMEM_SLOT;
+      issue_tile_layer(acc, acc + 64u, sA0 + (uint32_t)s * RF_SLOT_BYTES, sW[layer], false, 0,
+                       layer == 2 ? g.npad_last : RH_H);
+      umma_commit(done0 + 8u * s);
     }
   };
-  auto finish_layer = [&]() -> bool {
-    const bool got = warp_wait(mma_bar, phase, lane);
-    phase ^= 1;
-    tc_fence_after();
-    return got;
+  // 16 columns of the operand: raw values into the swizzled image, residual into tensor memory
+  auto put16 = [&](int s, int hh, const unsigned long long (&a)[8]) {
+    const uint32_t a_row = sA0 + (uint32_t)s * RF_SLOT_BYTES + (uint32_t)h * RH_A_SLAB;
+    uint32_t lo[16];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(a_row + (uint32_t)sw128_offset(r, 4 * hh + c)), "l"(a[2 * c]),
+                   "l"(a[2 * c + 1])
+                   : "memory");
+#pragma unroll
+      for (int k = 0; k < 2; k++) {
+        const unsigned long long l2 = sub2(a[2 * c + k], a[2 * c + k] & 0xFFFFE000FFFFE000ull);
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(lo[4 * c + 2 * k]), "=r"(lo[4 * c + 2 * k + 1]) : "l"(l2));
+      }
+    }
+    tmem_st16(tmem0 + (uint32_t)s * RF_TMEM_SLOT + lane_field + 64u + 32u * h + 16u * hh, lo);
   };
-  const int64_t tile_step = (int64_t)gridDim.x * 2;
-  int64_t tile = (int64_t)blockIdx.x * 2 + group;
 
-  {
-    // grad h3 and d3 of a tile are fetched while the previous tile's last product runs; d2 and d1 while the
-    // product that precedes their use runs
-    float4 pg[8], pd[8];
-    auto load_first = [&](int64_t t) {
-      const int64_t e = t * RH_TILE + r;
-      const float4 *dt = g.dsave + (t * 3 + 2) * 16 * RH_TILE + (h * 8) * RH_TILE + r;
+  if (gtid == 0) {
+    request_g(0, first);
+    request_g(1, first + step);
+  }
+  load_d(buf[0], first, 2);
+  load_d(buf[1], first + step, 2);
+  uint32_t done_phase = 0, gin_phase = 0;   // one parity bit each: both slots' barriers complete side by side
+
+  for (int64_t t0 = first; ok && t0 < ntiles; t0 += 2 * step) {
+    const int nslots = t0 + step < ntiles ? 2 : 1;
+    // ---- phase 0: grad z3 = grad h3 * d3, in place
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
-        pg[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-        pd[c] = pg[c];
-        if (t < ntiles) {
-          if (e < g.E) pg[c] = __ldg(reinterpret_cast<const float4 *>(g.in + e * RH_H + 32 * h) + c);
-          pd[c] = dt[c * RH_TILE];
-        }
-      }
-    };
-    load_first(tile);
-    for (; ok && tile < ntiles; tile += tile_step) {
-      const int64_t e = tile * RH_TILE + r;
-      const bool row_ok = e < g.E;
-      const float4 *dtile = g.dsave + (tile * 3) * 16 * RH_TILE + (h * 8) * RH_TILE + r;
-      // The phases of a tile wait one after the other for their operands, so HBM latency adds up three times per
-      // tile; pulling the group's next tile (96 KB of derivatives, 32 KB of gradient rows, both contiguous) into L2
-      // a whole tile ahead shortens every one of those waits.
-      if (gtid == 0 && tile + tile_step < ntiles) {   // (two tiles ahead measured slower)
-        const int64_t tn = tile + tile_step;
-        const char *dsrc = reinterpret_cast<const char *>(g.dsave + tn * 3 * 16 * RH_TILE);
-        for (int off = 0; off < 3 * 16 * RH_TILE * 16; off += 32768) l2_prefetch(dsrc + off, 32768);
-        const int64_t rows = g.E - tn * RH_TILE < RH_TILE ? g.E - tn * RH_TILE : RH_TILE;
-        l2_prefetch(reinterpret_cast<const char *>(g.in + tn * RH_TILE * RH_H), (uint32_t)(rows * RH_H * 4));
-      }
-      // ---- grad z3 = grad h3 * d3
-#pragma unroll
-      for (int c = 0; c < 8; c++)
-        store_split(a_row + (uint32_t)sw128_offset(r, c),
-                    make_float4(pg[c].x * pd[c].x, pg[c].y * pd[c].y, pg[c].z * pd[c].z, pg[c].w * pd[c].w));
-      start_layer(sW[0], RH_H, RH_H);
-#pragma unroll
-      for (int c = 0; c < 8; c++) pd[c] = dtile[(16 + c) * RH_TILE];        // d2
-      if (!(ok = finish_layer())) break;
-      for (int layer = 1; layer >= 0; layer--) {
-uint32_t v[32];
-        tmem_ld32_nowait(t_row + 32 * h, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-          const float4 d = pd[c];
-          store_split(a_row + (uint32_t)sw128_offset(r, c),
-                      make_float4(__uint_as_float(v[4 * c]) * d.x, __uint_as_float(v[4 * c + 1]) * d.y,
-                                  __uint_as_float(v[4 * c + 2]) * d.z, __uint_as_float(v[4 * c + 3]) * d.w));
-        }
-        start_layer(sW[2 - layer], RH_H, layer == 0 ? g.npad_last : RH_H);
-        if (layer == 1) {
-#pragma unroll
-          for (int c = 0; c < 8; c++) pd[c] = dtile[c * RH_TILE];            // d1
+    for (int s = 0; s < 2; s++) {
+      if (s < nslots && ok) {
+        const int64_t tile = t0 + s * step;
+        if (!warp_wait(gin0 + 8u * s, gin_phase, lane)) {
+          if (lane == 0 && g.status) atomicCAS(g.status, 0, 14);
+          ok = false;
         } else {
-          load_first(tile + tile_step);
+          const uint32_t a_row = sA0 + (uint32_t)s * RF_SLOT_BYTES + (uint32_t)h * RH_A_SLAB;
+#pragma unroll
+          for (int hh = 0; hh < 2; hh++) {
+            unsigned long long a[8];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+              unsigned long long g01, g23;
+              asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];"
+                           : "=l"(g01), "=l"(g23)
+                           : "r"(a_row + (uint32_t)sw128_offset(r, 4 * hh + c))
+                           : "memory");
+              const float4 d = buf[s][4 * hh + c];
+              a[2 * c] = mul2(g01, pack2(d.x, d.y));
+              a[2 * c + 1] = mul2(g23, pack2(d.z, d.w));
+            }
+            put16(s, hh, a);
+          }
+          load_d(buf[s], tile, 1);
+          hand_over(s, 0);
         }
-        if (!(ok = finish_layer())) break;
       }
-      if (!ok) break;
-      // ---- grad basis: columns [0, nb) of the accumulator
-      if (h == 0) {
-        for (int c0 = 0; c0 < g.nb; c0 += 8) {
-          uint32_t v[8];
-          tmem_ld8(t_row + c0, v);
-          if (row_ok) {
-            float *o = g.out + e * g.nb + c0;
-            *reinterpret_cast<float4 *>(o) = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]),
-                                                         __uint_as_float(v[2]), __uint_as_float(v[3]));
-            *reinterpret_cast<float4 *>(o + 4) = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]),
-                                                             __uint_as_float(v[6]), __uint_as_float(v[7]));
+    }
+    gin_phase ^= 1;
+    // ---- phases 1 and 2: grad z_k = accumulator * d_k
+    for (int k = 1; ok && k < 3; k++) {
+#pragma unroll
+      for (int s = 0; s < 2; s++) {
+        if (s < nslots && ok) {
+          const int64_t tile = t0 + s * step;
+          if (!warp_wait(done0 + 8u * s, done_phase, lane)) {
+            if (lane == 0 && g.status) atomicCAS(g.status, 0, 12);
+            ok = false;
+          } else {
+            tc_fence_after();
+            const uint32_t t_row = tmem0 + (uint32_t)s * RF_TMEM_SLOT + lane_field + 32u * h;
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+              uint32_t v[16];
+              tmem_ld16_nowait(t_row + 16u * hh, v);
+              tmem_ld_wait();
+              unsigned long long a[8];
+#pragma unroll
+              for (int c = 0; c < 4; c++) {
+                const float4 d = buf[s][4 * hh + c];
+                a[2 * c] = mul2(pack2(__uint_as_float(v[4 * c]), __uint_as_float(v[4 * c + 1])), pack2(d.x, d.y));
+                a[2 * c + 1] = mul2(pack2(__uint_as_float(v[4 * c + 2]), __uint_as_float(v[4 * c + 3])), pack2(d.z, d.w));
+              }
+              put16(s, hh, a);
+            }
+            if (k == 1) load_d(buf[s], tile, 0);
+            else load_d(buf[s], tile + 2 * step, 2);
+            hand_over(s, k);
           }
         }
       }
+      done_phase ^= 1;
     }
+    // ---- phase 3: grad basis = columns [0, nb) of the accumulator; the buffer is free for its next tile
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+      if (s < nslots && ok) {
+        const int64_t tile = t0 + s * step;
+        if (!warp_wait(done0 + 8u * s, done_phase, lane)) {
+          if (lane == 0 && g.status) atomicCAS(g.status, 0, 12);
+          ok = false;
+        } else {
+          tc_fence_after();
+          if (gtid == 0) request_g(s, tile + 2 * step);
+          const int64_t e = tile * RH_TILE + r;
+          if (h == 0) {
+            const uint32_t t_row = tmem0 + (uint32_t)s * RF_TMEM_SLOT + lane_field;
+            for (int c0 = 0; c0 < g.nb; c0 += 8) {
+              uint32_t v[8];
+              tmem_ld8(t_row + c0, v);
+              if (e < g.E) {
+                float *o = g.out + e * g.nb + c0;
+                *reinterpret_cast<float4 *>(o) = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]),
+                                                             __uint_as_float(v[2]), __uint_as_float(v[3]));
+                *reinterpret_cast<float4 *>(o + 4) = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]),
+                                                                 __uint_as_float(v[6]), __uint_as_float(v[7]));
+              }
+            }
+          }
+          tc_fence_before();
+        }
+      }
+    }
+    done_phase ^= 1;
   }
-  if (!ok && lane == 0 && g.status) atomicCAS(g.status, 0, 12);
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base_slot, RH_TMEM_COLS);
+  if (warp == 0) tmem_dealloc(tmem_base_slot, RF_TMEM_COLS);
 }
 
 static int radial_launch(RadialArgs &g, bool backward, const char *what, cudaStream_t st) {
@@ -532,22 +568,23 @@ static int radial_launch(RadialArgs &g, bool backward, const char *what, cudaStr
     if (num_sms <= 0) num_sms = 148;
   }
   const size_t w_total = backward ? (size_t)2 * RH_W_BIG + (size_t)4 * g.npad_last * 128 : (size_t)RH_W_SMALL + 2 * RH_W_BIG;
-  const size_t smem = w_total + (backward ? 2 * (size_t)RH_A_GROUP : 4 * (size_t)RF_SLOT_BYTES) + 1024;
+  const size_t smem = w_total + 4 * (size_t)RF_SLOT_BYTES + 1024;
   const int64_t ntiles = (g.E + RH_TILE - 1) / RH_TILE;
   int64_t blocks = (ntiles + 1) / 2;
   blocks = blocks < num_sms ? blocks : num_sms;
+  if (ntiles * RH_TILE > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many edges", what);
+  // the [E, 64] array that moves by TMA as 128-row x 32-column boxes: grad h3 in (backward), h3 out (forward)
+  CUtensorMap map;
+  if (int rc = encode_rows_tensor_map(&map, backward ? g.in : g.out, g.E, RH_H, what)) return rc;
   if (backward) {
     cudaError_t e = cudaFuncSetAttribute(radial_hidden_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
-    radial_hidden_bwd_kernel<<<(unsigned)blocks, RH_THREADS, smem, st>>>(g);
+    radial_hidden_bwd_kernel<<<(unsigned)blocks, RH_THREADS, smem, st>>>(g, map);
   } else {
-    if (ntiles * RH_TILE > 0x7fffffffLL) return fail(CMACE_ERR_UNSUPPORTED, "%s: too many edges", what);
-    CUtensorMap out_map;   // h3 [E, 64] as 128-row x 32-column boxes
-    if (int rc = encode_rows_tensor_map(&out_map, g.out, g.E, RH_H, what)) return rc;
     auto kern = g.nb == 8 ? radial_hidden_fwd_kernel<1> : radial_hidden_fwd_kernel<4>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
-    kern<<<(unsigned)blocks, RF_THREADS, smem, st>>>(g, out_map);
+    kern<<<(unsigned)blocks, RF_THREADS, smem, st>>>(g, map);
   }
   return check_launch(what);
 }

@@ -97,7 +97,15 @@ struct GemmArgs {
   int C;
   int g_stage_bytes;            // GRADR: shared memory behind the ring and the epilogue buffers for staged G rows
   int b_slots;                  // GRADR: depth of the separate ring of B blocks behind the staged G rows
+  int lin_tma;                  // LINEAR: rows move by TMA through rank-3 tensor maps (nodes in storage order)
 };
+
+// LINEAR with lin_tma: [nodes, 16, K] in and [nodes, 16, N] out, per l a box of (columns, 2l+1 components, nodes)
+struct LinMaps {
+  CUtensorMap in[4], out[4];
+};
+// rows a quarter of a tile (32 tensor-memory lanes) holds: whole nodes only, so that a box covers it
+__host__ __device__ constexpr int lin_nodes_per_quarter(int l) { return 32 / (2 * l + 1); }
 
 // ---- tile bookkeeping ----------------------------------------------------------------------------
 struct Tile {
@@ -106,6 +114,8 @@ struct Tile {
   int64_t seg_begin;  // LINEAR: first slot of the element in node_order
   int64_t seg_rows;   // LINEAR: rows of the problem
   int l, nl, mat, ntile;
+  int64_t node0;      // LINEAR with lin_tma: first node slot of the tile; quarter q holds nodes node0 + q nq .. + nq - 1
+  int nq;
 };
 
 // LINEAR: the (l, element) problems in the order their tiles are numbered (l outer, element inner), built once
@@ -130,7 +140,9 @@ __device__ __forceinline__ void build_problem_table(const GemmArgs &g, ProblemTa
     const uint32_t rows = (uint32_t)(cnt * (2 * l + 1));   // fits 32 bits (checked on the host)
     tab->seg_begin[p] = b;
     tab->seg_rows[p] = (int32_t)rows;
-    tab->tile_begin[p + 1] = (int32_t)((rows + GT_TILE_M - 1) / GT_TILE_M);   // count; prefix-summed below
+    const uint32_t per_tile = 4u * (uint32_t)lin_nodes_per_quarter(l);   // lin_tma: nodes per tile
+    tab->tile_begin[p + 1] = g.lin_tma ? (int32_t)(((uint32_t)cnt + per_tile - 1) / per_tile)
+                                       : (int32_t)((rows + GT_TILE_M - 1) / GT_TILE_M);   // count; prefix-summed below
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -212,6 +224,8 @@ struct TileWalker {
     }
     if (prob >= nprob) return false;
     T.row0 = (t - tab->tile_begin[prob]) * GT_TILE_M;
+    T.nq = lin_nodes_per_quarter(l);
+    T.node0 = tab->seg_begin[prob] + (t - tab->tile_begin[prob]) * 4 * T.nq;
     T.seg_begin = tab->seg_begin[prob];
     T.seg_rows = tab->seg_rows[prob];
     T.l = l;
@@ -255,7 +269,7 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 template <int MODE, bool TS = false, int CC = 0>
 __global__ void __launch_bounds__(GT_THREADS, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap,
-                       const __grid_constant__ CUtensorMap tmap_out) {
+                       const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ LinMaps lin_maps) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[3 * GT_MAX_STAGES + 9];
   __shared__ uint32_t tmem_base_slot;
@@ -282,7 +296,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < GT_STAGES; s++) {
       // LINEAR, GRADR: one arrival per producer warp + the expect_tx arrival of the B copy; PLAIN: converters only
-      mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS + (MODE == GT_MODE_PLAIN ? 0 : 1));
+      mbar_init(full_bar + 8 * s, GT_PRODUCER_WARPS + ((MODE == GT_MODE_PLAIN || g.lin_tma) ? 0 : 1));
       mbar_init(tma_full + 8 * s, 1);         // the loader's expect_tx arrival (+ the copies' bytes)
       mbar_init(empty_bar + 8 * s, 1);        // one tcgen05.commit
     }
@@ -307,11 +321,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
   const uint32_t b_image = (uint32_t)g.npad * 128u;  // bytes of one B image
   const uint32_t b_off = TS ? GT_A_SLAB : 2 * GT_A_SLAB;          // the stage's B block follows its A image(s)
   // tensor-memory columns between the accumulators; TS: ring of residual images behind them, 32 columns a slot
-  const uint32_t acc_stride = TS ? 2u * (uint32_t)g.npad : 256u;
-  const uint32_t lo_ring = tmem_base + 4u * (uint32_t)g.npad;
+  // LINEAR with TS: the three product terms share one set of npad columns (ONE_ACC), which leaves room for the ring
+  // of residual images next to two accumulators of 128 columns
+  constexpr bool ONE_ACC = MODE == GT_MODE_LINEAR && TS;
+  const uint32_t acc_stride = ONE_ACC ? (uint32_t)g.npad : (TS ? 2u * (uint32_t)g.npad : 256u);
+  const uint32_t lo_ring = tmem_base + (ONE_ACC ? 2u : 4u) * (uint32_t)g.npad;
   const int items = k_blocks;                                     // pipeline items per tile
 
-  if (MODE == GT_MODE_PLAIN && TS && warp < GT_PRODUCER_WARPS) {
+  if (((MODE == GT_MODE_PLAIN && TS) || (MODE == GT_MODE_LINEAR && TS && g.lin_tma)) && warp < GT_PRODUCER_WARPS) {
     // ================================ converters, residual image to tensor memory ================================
     // A thread owns one row of the tile (the tensor-memory lane its warp may access) and 16 of the K block's 32
     // columns: four 16-byte shared-memory loads (conflict-free: the 128-byte swizzle puts the same logical chunk of
@@ -581,9 +598,15 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
     // GT_PREFETCH items ahead of the conversion in a register ring, so that enough bytes are in flight
     // per SM to cover HBM latency (about a microsecond) independently of the shared-memory ring depth.
+    // Without TS: 8 threads cover the 128-byte K-block segment of a row, rows rbase + 32 i.  With TS the residual
+    // image goes to tensor memory, which a warp reaches only for the 32 lanes (= rows) of its quarter: warp (q, hf)
+    // loads rows 32 q .. 32 q + 31, the 64-byte half hf of their segments (4 threads a row, rows (lane >> 2) + 8 i),
+    // writes the raw values to the shared-memory image, and then every lane reads ITS row's half back (all of it
+    // written by this warp) to form the residuals.
     const int p = threadIdx.x;       // 0..255
-    const int chunk = p & 7;         // 16-byte chunk of the 128-byte row segment
-    const int rbase = p >> 3;        // rows rbase + GT_ROW_STEP * i
+    const int chunk = TS ? 4 * (warp >> 2) + (lane & 3) : (p & 7);   // 16-byte chunk of the 128-byte row segment
+    const int rbase = TS ? 32 * (warp & 3) + (lane >> 2) : (p >> 3); // rows rbase + row_step * i
+    constexpr int row_step = TS ? 8 : GT_ROW_STEP;
     // head: the next (tile, K block) item whose loads have not been issued yet
     struct Head {
       Tile T;
@@ -598,7 +621,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       head.valid = tiles.next(head.T);
       if (!head.valid) return;
 #pragma unroll
-      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row<MODE>(g, head.T, rbase + GT_ROW_STEP * i);
+      for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row<MODE>(g, head.T, rbase + row_step * i);
     };
     // an item in flight only has to remember where its B block lives (-1: no item)
     auto issue = [&](float4 (&v)[GT_ROWS_PER_THREAD]) -> int64_t {
@@ -627,6 +650,42 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         return false;
       }
       const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
+      if (TS) {
+        // (the B block of the item is copied by the loader warp into a ring of its own)
+#pragma unroll
+        for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
+          const uint32_t off = (uint32_t)sw128_offset(rbase + row_step * i, chunk);
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(v[i].x), "f"(v[i].y), "f"(v[i].z),
+                       "f"(v[i].w)
+                       : "memory");
+        }
+        __syncwarp();
+        const int q = warp & 3, hf = warp >> 2;
+        uint32_t lo[16];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          float4 a;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
+                       : "r"(sA + (uint32_t)sw128_offset(32 * q + lane, 4 * hf + c))
+                       : "memory");
+          lo[4 * c] = __float_as_uint(to_tf32(a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u)));
+          lo[4 * c + 1] = __float_as_uint(to_tf32(a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u)));
+          lo[4 * c + 2] = __float_as_uint(to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u)));
+          lo[4 * c + 3] = __float_as_uint(to_tf32(a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u)));
+        }
+        tmem_st16(lo_ring + 32u * (uint32_t)stage + ((uint32_t)(q * 32) << 16) + 16u * (uint32_t)hf, lo);
+        tmem_st_wait();
+        tc_fence_before();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar + 8 * stage);
+        if (++stage == GT_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+        return true;
+      }
       if (p == 0) {
         const unsigned char *bsrc =
             reinterpret_cast<const unsigned char *>(g.packed) + bblock * (2 * (int64_t)b_image);
@@ -743,6 +802,69 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         have = have_next;
       }
     }
+    if (MODE == GT_MODE_LINEAR && TS && g.lin_tma && lane == 0) {
+      // Rows by TMA: per item four box loads (one per quarter of the tile: nq whole nodes x 2l+1 components x 32
+      // columns land as consecutive 128-byte rows, swizzled, at the quarter's first row) and the B block, all on the
+      // slot's tma_full barrier; the converter warps then add the residual image.  Boxes that reach past the last
+      // node read zeros.
+      const uint32_t b_ring0 = smem_base + GT_STAGES * GT_STAGE_BYTES + (uint32_t)g.g_stage_bytes;
+      int slot = 0;
+      uint32_t bphase = 0;
+      bool ok = true;
+      TileWalker<MODE> tiles(g, tab);
+      Tile T;
+      while (ok && tiles.next(T)) {
+        const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
+                                    ((int64_t)(T.mat * g.n_tiles + T.ntile) * k_blocks) * (2 * (int64_t)b_image);
+        const uint32_t quarter_bytes = (uint32_t)(T.nq * T.nl) * 128u;
+        for (int kb = 0; kb < items; kb++) {
+          if (!mbar_wait(empty_bar + 8 * slot, bphase ^ 1)) {
+            report(g, 9);
+            ok = false;
+            break;
+          }
+          const uint32_t sA = smem_base + slot * GT_STAGE_BYTES, bar = tma_full + 8 * slot;
+          mbar_arrive_expect_tx(bar, 4u * quarter_bytes + 2 * b_image);
+#pragma unroll
+          for (int q = 0; q < 4; q++)
+            tma_load_3d(sA + (uint32_t)q * 4096u, &lin_maps.in[T.l], kb * GT_KBLOCK, T.l * T.l, (int)(T.node0 + q * T.nq), bar);
+          bulk_copy_g2s(b_ring0 + (uint32_t)slot * 2u * b_image, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image, bar);
+          if (++slot == GT_STAGES) {
+            slot = 0;
+            bphase ^= 1;
+          }
+        }
+      }
+    }
+    if (MODE == GT_MODE_LINEAR && TS && !g.lin_tma && lane == 0) {
+      // Per item the B block of the tile's (l, element) problem into the ring of B blocks, same slot index and
+      // barriers as the A images: the copy starts as soon as the slot is released, while the producers still
+      // convert the items before it.
+      const uint32_t b_ring0 = smem_base + GT_STAGES * GT_STAGE_BYTES + (uint32_t)g.g_stage_bytes;
+      int slot = 0;
+      uint32_t bphase = 0;
+      bool ok = true;
+      TileWalker<MODE> tiles(g, tab);
+      Tile T;
+      while (ok && tiles.next(T)) {
+        const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(g.packed) +
+                                    ((int64_t)(T.mat * g.n_tiles + T.ntile) * k_blocks) * (2 * (int64_t)b_image);
+        for (int kb = 0; kb < items; kb++) {
+          if (!mbar_wait(empty_bar + 8 * slot, bphase ^ 1)) {
+            report(g, 9);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(full_bar + 8 * slot, 2 * b_image);
+          bulk_copy_g2s(b_ring0 + (uint32_t)slot * 2u * b_image, bsrc + (int64_t)kb * (2 * (int64_t)b_image), 2 * b_image,
+                        full_bar + 8 * slot);
+          if (++slot == GT_STAGES) {
+            slot = 0;
+            bphase ^= 1;
+          }
+        }
+      }
+    }
     if (MODE == GT_MODE_PLAIN && lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -838,7 +960,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           // step (j * 32 bytes = 2 address units); the high word is a constant.  This thread shares its scheduler
           // with busy warps, so every instruction between two MMAs costs issue latency: the low words advance with
           // one add per item, the eight MMAs go back to back.
-          const uint32_t b_lo32 = MODE == GT_MODE_GRADR ? bb_first + (uint32_t)stage * bres_step
+          const uint32_t b_lo32 = (MODE == GT_MODE_GRADR || ONE_ACC) ? bb_first + (uint32_t)stage * bres_step
                                   : g.b_resident      ? bres_lo32 + (uint32_t)kb * bres_step
                                                       : b_ring_lo32;
           uint64_t ah[4], al[4], bh[4];
@@ -849,7 +971,22 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             asm("mov.b64 %0, {%1, %2};" : "=l"(bh[j]) : "r"(b_lo32 + 2u * j), "r"(desc_hi32));
           }
           const uint32_t a_lo_t = lo_ring + 32u * (uint32_t)stage;   // TS: K step j at + 8 j columns
-          if (full_k) {
+          if (ONE_ACC) {
+            // all three terms into the same npad columns; the B lo image follows the hi image, b_image bytes further
+            const uint32_t idescn = umma_idesc_tf32(GT_TILE_M, g.npad);
+            int ksteps = (g.K - kb * GT_KBLOCK + 7) / 8;
+            ksteps = ksteps > 4 ? 4 : ksteps;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              if (j < ksteps) {
+                uint64_t bl;
+                asm("mov.b64 %0, {%1, %2};" : "=l"(bl) : "r"(b_lo32 + (b_image >> 4) + 2u * j), "r"(desc_hi32));
+                umma_tf32(d_tmem, ah[j], bh[j], idescn, (kb | j) != 0);
+                umma_tf32_acc(d_tmem, ah[j], bl, idescn);
+                umma_tf32_ts_acc(d_tmem, a_lo_t + 8u * j, bh[j], idescn);
+              }
+            }
+          } else if (full_k) {
             umma_tf32(d_tmem, ah[0], bh[0], idesc2, kb != 0);
             if (TS) umma_tf32_ts_acc(d_tmem, a_lo_t, bh[0], idesc1);
             else umma_tf32_acc(d_tmem, al[0], bh[0], idesc1);
@@ -994,6 +1131,35 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             }
           }
         }
+      } else if (MODE == GT_MODE_LINEAR && TS && g.lin_tma) {
+        // Tile store by TMA: a warp writes 32 rows x 16 columns into a 2 KB staging buffer (64-byte rows, 64-byte
+        // swizzle: conflict-free 16-byte stores) and one thread hands it to the copy engine as a box of
+        // (16 columns, 2l+1 components, nq nodes) = the quarter's first nq (2l+1) rows; nodes and columns outside the
+        // array are clipped.  This takes the transposes and the row stores (one pass of the load/store pipe per
+        // 32-byte sector) out of the epilogue.
+        const uint32_t stg = smem_base + GT_STAGES * GT_STAGE_BYTES + (uint32_t)(warp - (GT_PRODUCER_WARPS + 1)) * 2048u;
+        const int node_q = (int)(T.node0 + q * T.nq);
+        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+#pragma unroll
+          for (int h16 = 0; h16 < 2; h16++) {
+            const int cc = c0 + 16 * h16;
+            if (cc >= ncols) break;  // warp-uniform
+            uint32_t v[16];
+            tmem_ld16_nowait(taddr + (uint32_t)cc, v);
+            tmem_ld_wait();
+            if (lane == 0) tma_store_wait_read();   // the previous store has left the staging buffer
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stg + (uint32_t)sw64_offset(lane, c)),
+                           "f"(__uint_as_float(v[4 * c]) * g.scale), "f"(__uint_as_float(v[4 * c + 1]) * g.scale),
+                           "f"(__uint_as_float(v[4 * c + 2]) * g.scale), "f"(__uint_as_float(v[4 * c + 3]) * g.scale)
+                           : "memory");
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && node_q < g.M) tma_store_3d(&lin_maps.out[T.l], n0 + cc, T.l * T.l, node_q, stg);
+          }
+        }
       } else {
         // rows each store instruction of this lane covers (8 rows x 64 bytes): row pointers, once per tile
         float *rowptr[4];
@@ -1008,8 +1174,13 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             const int cc = c0 + h16;
             if (cc >= ncols) break;  // warp-uniform
             uint32_t v[16], w[16];
-            tmem_ld16_nowait(taddr + cc, v);             // Ahi*Bhi + Alo*Bhi
-            tmem_ld16_nowait(taddr + g.npad + cc, w);    // Ahi*Blo
+            tmem_ld16_nowait(taddr + cc, v);             // Ahi*Bhi + Alo*Bhi (ONE_ACC: all three terms)
+            if (ONE_ACC) {
+#pragma unroll
+              for (int i = 0; i < 16; i++) w[i] = 0u;
+            } else {
+              tmem_ld16_nowait(taddr + g.npad + cc, w);  // Ahi*Blo
+            }
             tmem_ld_wait();
             // lane = row: write the row's 16 values, then read back 8 rows x 64 bytes per instruction
             float *mine = ep_buf + lane * GT_EP_STRIDE;
@@ -1041,7 +1212,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
       acc ^= 1;
     }
     // the copy engine still reads this warp's staging buffer and writes its tile: wait before the CTA retires
-    if (MODE != GT_MODE_LINEAR && g.ep_tma && lane == 0) tma_store_wait_all();
+    if (((MODE != GT_MODE_LINEAR && g.ep_tma) || (MODE == GT_MODE_LINEAR && g.lin_tma)) && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -1163,6 +1334,23 @@ static int encode_out_tensor_map(CUtensorMap *tmap, float *out, int64_t rows, in
   return CMACE_OK;
 }
 
+// [nodes, 16, width] float32 as boxes of (box_cols columns, 2l+1 components starting at l^2, nq whole nodes)
+static int encode_node_tensor_map(CUtensorMap *tmap, const float *base, int64_t nodes, int width, int l, int box_cols,
+                                  CUtensorMapSwizzle swizzle, const char *what) {
+  memset(tmap, 0, sizeof(*tmap));
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available", what);
+  const cuuint64_t dims[3] = {(cuuint64_t)width, 16, (cuuint64_t)nodes};
+  const cuuint64_t strides[2] = {(cuuint64_t)width * 4, (cuuint64_t)width * 64};
+  const cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)(2 * l + 1), (cuuint32_t)lin_nodes_per_quarter(l)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(CMACE_ERR_CUDA, "%s: cuTensorMapEncodeTiled (rank 3) failed (%d)", what, (int)r);
+  return CMACE_OK;
+}
+
 static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -1178,18 +1366,35 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   // residual image of A in tensor memory when at least four ring slots fit next to the two accumulators
   const int ts_slots = (GT_TMEM_COLS - 4 * g.npad) / 32;
   g.a_lo_tmem = ((g.mode == GT_MODE_PLAIN && ts_slots >= 4) || g.mode == GT_MODE_GRADR) ? 1 : 0;
+  // LINEAR: one set of accumulator columns for the three terms, so two accumulators take 2 npad columns
+  const int lin_ts_slots = (GT_TMEM_COLS - 2 * g.npad) / 32;
+  if (g.mode == GT_MODE_LINEAR && lin_ts_slots >= 3) g.a_lo_tmem = 1;
+  // rows by TMA when the nodes of every problem are consecutive in storage (no gather list)
+  g.lin_tma = (g.mode == GT_MODE_LINEAR && g.a_lo_tmem && g.node_order == nullptr && g.nelements == 1) ? 1 : 0;
   if (g.mode == GT_MODE_GRADR && ts_slots < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
   g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   // PLAIN: tile stores by TMA from a 4 KB staging buffer per epilogue warp (N >= 32: the box is 32 columns wide);
   // LINEAR: the transpose buffers of its epilogue
   g.ep_tma = (g.mode != GT_MODE_LINEAR && g.N >= 32) ? 1 : 0;
-  const int ep_bytes = g.mode != GT_MODE_LINEAR ? (g.ep_tma ? GT_EP_TMA_BYTES : 0) : GT_EP_BYTES;
+  const int ep_bytes = g.mode != GT_MODE_LINEAR ? (g.ep_tma ? GT_EP_TMA_BYTES : 0)
+                       : g.lin_tma              ? GT_EPILOGUE_WARPS * 2048
+                                                : GT_EP_BYTES;
   // the LINEAR variant holds its problem table in static shared memory
   const int budget = GT_SMEM_BUDGET - (g.mode == GT_MODE_LINEAR ? (int)sizeof(ProblemTable) + 1024 : 0);
   g.stages = (budget - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
-  if (g.a_lo_tmem && g.stages > ts_slots) g.stages = ts_slots;
+  if (g.a_lo_tmem && g.mode != GT_MODE_LINEAR && g.stages > ts_slots) g.stages = ts_slots;
   g.g_stage_bytes = 0;
+  if (g.mode == GT_MODE_LINEAR && g.a_lo_tmem) {
+    // ring of A images (raw values only, 16 KB a slot), the epilogue's transpose buffers behind it, then a ring of B
+    // blocks with the same slot count
+    g.stage_bytes = GT_A_SLAB;
+    g.stages = (budget - ep_bytes - 1024) / (GT_A_SLAB + 2 * g.npad * 128);
+    if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
+    if (g.stages > lin_ts_slots) g.stages = lin_ts_slots;
+    g.b_slots = g.stages;
+    g.g_stage_bytes = ep_bytes;   // the kernel finds the B ring behind stages * stage_bytes + g_stage_bytes
+  }
   if (g.mode == GT_MODE_GRADR) {
     // Shared memory: a ring of A images (hi image only, 16 KB a slot), a ring of B blocks of its own, and the G rows
     // of a tile's receivers twice (the next tile's are copied while this one is consumed).  No epilogue staging
@@ -1210,8 +1415,20 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     if (g.g_stage_bytes < 0) g.g_stage_bytes = 0;
   }
   if (g.stages < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: tile does not fit shared memory", what);
-  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes + (g.mode == GT_MODE_GRADR ? 0 : ep_bytes) + 1024 +
+  const size_t smem = (size_t)g.b_resident + (size_t)g.stages * g.stage_bytes +
+                      ((g.mode == GT_MODE_GRADR || (g.mode == GT_MODE_LINEAR && g.a_lo_tmem)) ? 0 : ep_bytes) + 1024 +
                       (size_t)g.g_stage_bytes + (size_t)g.b_slots * 2 * g.npad * 128;
+  LinMaps lin_maps;
+  memset(&lin_maps, 0, sizeof(lin_maps));
+  if (g.lin_tma) {
+    for (int l = 0; l < 4; l++) {
+      if (int rc = encode_node_tensor_map(&lin_maps.in[l], g.A, g.M, g.K, l, GT_KBLOCK, CU_TENSOR_MAP_SWIZZLE_128B, what)) return rc;
+      if (int rc = encode_node_tensor_map(&lin_maps.out[l], g.out, g.M, g.N, l, 16, CU_TENSOR_MAP_SWIZZLE_64B, what)) return rc;
+    }
+    // tiles hold whole nodes: 128, 40, 24 and 16 of them for l = 0 .. 3
+    g.total_tiles = 4 * (int64_t)g.nelements;
+    for (int l = 0; l < 4; l++) g.total_tiles += g.M / (4 * lin_nodes_per_quarter(l)) + 1;
+  }
   CUtensorMap tmap, tmap_out;
   memset(&tmap, 0, sizeof(tmap));
   memset(&tmap_out, 0, sizeof(tmap_out));
@@ -1221,7 +1438,8 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (g.ep_tma) {
     if (int rc = encode_out_tensor_map(&tmap_out, g.out, g.M, g.N, what)) return rc;
   }
-  auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<GT_MODE_LINEAR>
+  auto kern = g.mode == GT_MODE_LINEAR ? (g.a_lo_tmem ? gemm3x_tf32_kernel<GT_MODE_LINEAR, true>
+                                                      : gemm3x_tf32_kernel<GT_MODE_LINEAR>)
               : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<GT_MODE_GRADR, true, 128>
                                                        : gemm3x_tf32_kernel<GT_MODE_GRADR, true>)
               : g.a_lo_tmem            ? gemm3x_tf32_kernel<GT_MODE_PLAIN, true>
@@ -1239,7 +1457,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     g.total_tiles = ((row_tiles + per_col - 1) / per_col) * blocks;
   }
   if (blocks < 1) return CMACE_OK;
-  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g, tmap, tmap_out);
+  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g, tmap, tmap_out, lin_maps);
   return check_launch(what);
 }
 

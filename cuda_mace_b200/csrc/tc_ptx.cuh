@@ -60,6 +60,19 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int 
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+// the same for a rank-3 tensor map (coordinates innermost first)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(map), "r"(x), "r"(y),
+               "r"(z), "r"(src)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
 // the source buffers of all of this thread's stores have been read (they may be overwritten)
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // all of this thread's stores are complete
@@ -200,6 +213,9 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
 __device__ __host__ __forceinline__ int sw128_offset(int r, int c) {
   return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
 }
+
+// byte offset of the 16-byte chunk c (0..3) of row r inside an image of 64-byte rows with the 64-byte swizzle
+__device__ __host__ __forceinline__ int sw64_offset(int r, int c) { return r * 64 + ((c ^ ((r >> 1) & 3)) << 4); }
 
 // lane 0 polls for the warp; returns false on a time-out
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lane) {

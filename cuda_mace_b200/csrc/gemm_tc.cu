@@ -115,6 +115,7 @@ struct Tile {
   int64_t seg_rows;   // LINEAR: rows of the problem
   int l, nl, mat, ntile;
   int64_t node0;      // LINEAR with lin_tma: first node slot of the tile; quarter q holds nodes node0 + q nq .. + nq - 1
+  int64_t node_end;   //   one past the last node of the tile's (element, l) problem
   int nq;
 };
 
@@ -226,6 +227,7 @@ struct TileWalker {
     T.row0 = (t - tab->tile_begin[prob]) * GT_TILE_M;
     T.nq = lin_nodes_per_quarter(l);
     T.node0 = tab->seg_begin[prob] + (t - tab->tile_begin[prob]) * 4 * T.nq;
+    T.node_end = tab->seg_begin[prob] + tab->seg_rows[prob] / (2 * l + 1);
     T.seg_begin = tab->seg_begin[prob];
     T.seg_rows = tab->seg_rows[prob];
     T.l = l;
@@ -1138,7 +1140,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         // array are clipped.  This takes the transposes and the row stores (one pass of the load/store pipe per
         // 32-byte sector) out of the epilogue.
         const uint32_t stg = smem_base + GT_STAGES * GT_STAGE_BYTES + (uint32_t)(warp - (GT_PRODUCER_WARPS + 1)) * 2048u;
+        // A quarter that reaches past the last node of its problem (the next nodes belong to another element, or
+        // lie outside the array) is stored row by row from registers instead: one such tile per problem.
         const int node_q = (int)(T.node0 + q * T.nq);
+        const bool whole = node_q + T.nq <= T.node_end;
         for (int c0 = half * 32; c0 < ncols; c0 += 64) {
 #pragma unroll
           for (int h16 = 0; h16 < 2; h16++) {
@@ -1147,6 +1152,19 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
             uint32_t v[16];
             tmem_ld16_nowait(taddr + (uint32_t)cc, v);
             tmem_ld_wait();
+            if (!whole) {
+              const int node = node_q + lane / T.nl, m = lane - (lane / T.nl) * T.nl;
+              if (lane < T.nq * T.nl && node < T.node_end) {
+                float *o = g.out + ((int64_t)node * 16 + T.l * T.l + m) * g.N + n0 + cc;
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+                  if (cc + 4 * c < ncols)
+                    *reinterpret_cast<float4 *>(o + 4 * c) =
+                        make_float4(__uint_as_float(v[4 * c]) * g.scale, __uint_as_float(v[4 * c + 1]) * g.scale,
+                                    __uint_as_float(v[4 * c + 2]) * g.scale, __uint_as_float(v[4 * c + 3]) * g.scale);
+              }
+              continue;
+            }
             if (lane == 0) tma_store_wait_read();   // the previous store has left the staging buffer
             __syncwarp();
 #pragma unroll
@@ -1157,7 +1175,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
                            : "memory");
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0 && node_q < g.M) tma_store_3d(&lin_maps.out[T.l], n0 + cc, T.l * T.l, node_q, stg);
+            if (lane == 0) tma_store_3d(&lin_maps.out[T.l], n0 + cc, T.l * T.l, node_q, stg);
           }
         }
       } else {
@@ -1370,7 +1388,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   const int lin_ts_slots = (GT_TMEM_COLS - 2 * g.npad) / 32;
   if (g.mode == GT_MODE_LINEAR && lin_ts_slots >= 3) g.a_lo_tmem = 1;
   // rows by TMA when the nodes of every problem are consecutive in storage (no gather list)
-  g.lin_tma = (g.mode == GT_MODE_LINEAR && g.a_lo_tmem && g.node_order == nullptr && g.nelements == 1) ? 1 : 0;
+  g.lin_tma = (g.mode == GT_MODE_LINEAR && g.a_lo_tmem && g.node_order == nullptr) ? 1 : 0;
   if (g.mode == GT_MODE_GRADR && ts_slots < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
   g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   // PLAIN: tile stores by TMA from a 4 KB staging buffer per epilogue warp (N >= 32: the box is 32 columns wide);
@@ -1546,8 +1564,8 @@ int cmace_linear_tc_f32(const float *X, const float *packed, const int32_t *node
     return fail(CMACE_ERR_UNSUPPORTED, "cmace_linear_tc: at most %d elements", GT_MAX_PROBLEMS / 4);
   if (nnodes == 0) return CMACE_OK;
   if (!X || !packed || !out) return fail(CMACE_ERR_ARG, "cmace_linear_tc: null pointer");
-  if ((nelements > 1) != (node_order != nullptr) || (node_order != nullptr) != (elem_start != nullptr))
-    return fail(CMACE_ERR_ARG, "cmace_linear_tc: node_order and elem_start go together with nelements > 1");
+  if ((nelements > 1) != (elem_start != nullptr) || (node_order != nullptr && elem_start == nullptr))
+    return fail(CMACE_ERR_ARG, "cmace_linear_tc: elem_start goes with nelements > 1, node_order only with elem_start");
   if (!aligned16(X) || !aligned16(packed) || !aligned16(out))
     return fail(CMACE_ERR_ARG, "cmace_linear_tc: pointers must be 16-byte aligned");
   const PackGeom p = pack_geom(Nout, K);

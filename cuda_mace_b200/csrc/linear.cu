@@ -329,8 +329,9 @@ static int linear(const T *X, const T *W, const int32_t *node_order, const int32
   if (nnodes < 0 || K < 1 || Nout < 1 || nelements < 1) return fail(CMACE_ERR_ARG, "cmace_linear: bad size");
   if (nnodes == 0) return CMACE_OK;
   if (!X || !W || !out) return fail(CMACE_ERR_ARG, "cmace_linear: null pointer");
-  if ((nelements > 1) != (node_order != nullptr) || (node_order != nullptr) != (elem_start != nullptr))
-    return fail(CMACE_ERR_ARG, "cmace_linear: node_order and elem_start go together with nelements > 1");
+  // (node_order may be NULL for nelements > 1: the nodes are then stored grouped by element)
+  if ((nelements > 1) != (elem_start != nullptr) || (node_order != nullptr && elem_start == nullptr))
+    return fail(CMACE_ERR_ARG, "cmace_linear: elem_start goes with nelements > 1, node_order only with elem_start");
   if constexpr (sizeof(T) == 8) {
     // tensor-core path whenever its 16-byte copies are aligned: even K and Nout, 16-byte aligned bases
     if (K % 2 == 0 && Nout % 2 == 0 && aligned16(X) && aligned16(W) && aligned16(out))

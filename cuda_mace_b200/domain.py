@@ -46,16 +46,22 @@ class SlabDomain:
     pbc: tuple = (True, True, True)  # periodic axes of the local list: z is open once slabs carry ghost atoms
 
 
-def partition_slabs(positions, species, box, nranks, r_cut, rank):
+def partition_slabs(positions, species, box, nranks, r_cut, rank, group_species=True):
     """Splits a periodic orthorhombic system into `nranks` slabs along z with equal atom counts and
-    returns the local view of `rank`.  Every rank computes this from the same global arrays."""
+    returns the local view of `rank`.  Every rank computes this from the same global arrays.
+
+    group_species: the owned atoms of a slab are stored grouped by species (`owned_global` maps local rows back to
+    the caller's numbering, as it does for the slab order anyway).  The element-dependent operators then work on
+    contiguous row ranges instead of gather lists."""
     positions = np.asarray(positions, dtype=np.float64)
     species = np.asarray(species)
     N = positions.shape[0]
     if nranks == 1:
+        mine = np.argsort(species, kind="stable") if group_species else np.arange(N)
+        positions, species = positions[mine], species[mine]
         ei, sh = neighbor_list(positions, box, (True, True, True), r_cut)
         zero = np.zeros(0, dtype=np.int64)
-        return SlabDomain(0, 1, N, N, np.arange(N), positions, species, np.zeros_like(positions), ei, sh,
+        return SlabDomain(0, 1, N, N, mine, positions, species, np.zeros_like(positions), ei, sh,
                           zero, zero, (N, 0), (N, 0), 0, 0, np.asarray(box, dtype=np.float64), (True, True, True))
     order = np.argsort(positions[:, 2], kind="stable")
     bounds = [(N * p) // nranks for p in range(nranks + 1)]
@@ -65,6 +71,8 @@ def partition_slabs(positions, species, box, nranks, r_cut, rank):
     if np.min(np.diff(cut)) < r_cut:
         raise ValueError("a slab is thinner than the cutoff; use fewer ranks or a longer box")
     owned = [order[bounds[p]:bounds[p + 1]] for p in range(nranks)]
+    if group_species:
+        owned = [o[np.argsort(species[o], kind="stable")] for o in owned]
     down, up = (rank - 1) % nranks, (rank + 1) % nranks
 
     def boundary(p, side):

@@ -622,6 +622,11 @@ def group_by_element(elem, nelements):
     start = torch.empty(nelements + 1, dtype=torch.int32, device=dev)
     _abi.call("cmace_group_by_element", _ptr(elem), n, int(nelements), _ptr(order), _ptr(start), _ptr(ws),
               int(nbytes), _stream())
+    # Nodes already stored grouped by element need no gather list, and the float32 tensor-core kernel then moves
+    # their rows by TMA.  The check reads one flag back, once per element tensor (not while a graph is captured).
+    if n > 1 and not torch.cuda.is_current_stream_capturing():
+        if bool((elem[1:] >= elem[:-1]).all().item()):
+            order = None
     return _grouping_cache.put(key, (elem,), (order, start))
 
 

@@ -206,7 +206,8 @@ int cmace_imp_bwd_node_f64(const double *T, const int32_t *perm, const int32_t *
  * X [N,16,K]; W [nelements,4,K,Nout]; out [N,16,Nout].  The reference hard-codes
  * scale = 1/sqrt(K) (linear_impl.cu:33); pass that for the forward.  For Linear pass
  * nelements = 1 and node_order = elem_start = NULL.  For ElementalLinear pass the outputs of
- * cmace_group_by_element.  The backward of both is the same call with the transposed weights,
+ * cmace_group_by_element (node_order may be NULL when the nodes are already stored grouped by element:
+ * element z owns nodes elem_start[z] .. elem_start[z+1] - 1).  The backward of both is the same call with the transposed weights,
  * as in the reference (src/linear.cpp:29-44, :77-93), and with the FORWARD's scale (the
  * reference re-derives it from the transposed shape, which is only right for K = Nout).
  * One launch, no host synchronisation.  The float64 entry point runs on the FP64 tensor cores (mma.sync
@@ -230,7 +231,9 @@ int cmace_gemm_f64(const double *A, const double *B, int64_t M, int K, int N, do
  * (cuda/src/linear_impl.cu:85-101).  Weights are packed once into the shared-memory image the tensor
  * core reads: Bt [nmat, N, K] is the TRANSPOSE of each [K, N] weight matrix (K contiguous), i.e. W_T for
  * the forward of Linear and W for its backward.  packed needs cmace_gemm_packed_floats(nmat, N, K) floats.
- * cmace_linear_tc_f32 has the contract of cmace_linear_f32 (Nout <= 128); cmace_gemm3x_f32 is the plain
+ * cmace_linear_tc_f32 has the contract of cmace_linear_f32 (Nout <= 128), with one addition: for nelements > 1
+ * node_order may be NULL when the nodes are STORED grouped by element (element z owns the nodes
+ * elem_start[z] .. elem_start[z+1] - 1); without a gather list the rows move by TMA.  cmace_gemm3x_f32 is the plain
  * out[M,N] = scale * A[M,K] @ B used for the radial multilayer perceptron (which upstream MACE evaluates
  * with torch and the reference replaces by its spline table, models/InvariantMACE.py:226-240).
  * status: optional device int32, set non-zero if a bounded wait inside the kernel timed out. */

@@ -145,7 +145,9 @@ def test_single_gpu_slab_domain_equals_periodic(U):
     e, f = domain.distributed_energy_forces(node_energy, dom, plan, torch.from_numpy(dom.positions).cuda())
     out = m(data)
     assert abs(float(e) - float(out["interaction_energy"])) < 1e-12 * abs(float(e))
-    assert rel_err(f, out["forces"]) < 1e-12
+    # the domain stores its atoms grouped by species; owned_global maps its rows back
+    assert (np.diff(dom.species[: dom.n_owned]) >= 0).all()
+    assert rel_err(f, out["forces"][torch.from_numpy(dom.owned_global).cuda()]) < 1e-12
 
 
 def test_last_radial_layer_inside_message_passing_matches_oracle(U, monkeypatch):

@@ -144,6 +144,41 @@ def test_elemental_linear(dtype, N, Z, K, dev):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,Z,K", [(1000, 4, 128), (37, 10, 64), (333, 3, 32), (4, 2, 128)])
+def test_elemental_linear_on_nodes_stored_grouped_by_element(dtype, N, Z, K, dev):
+    """Nodes whose element index is already non-decreasing need no gather list: the operator passes none, and the
+    float32 kernel moves whole-node boxes by TMA (the last, partial box of every element row by row).  Same oracle,
+    same tolerances; elements without atoms and elements of fewer atoms than a box included."""
+    from cuda_mace_b200 import ops, systems
+    from oracle import ops as oops
+
+    g = torch.Generator().manual_seed(7 * N + Z)
+    X = torch.randn(N, 16, K, generator=g, dtype=torch.float64).to(dtype)
+    W = torch.randn(Z, 4, K, K, generator=g, dtype=torch.float64).to(dtype)
+    at = torch.randint(0, Z, (N,), generator=g)
+    at[at == 1] = 0  # one element with no atoms at all
+    at = torch.sort(at).values
+    onehot = systems.one_hot(at, Z)
+    Xo = X.double().clone().requires_grad_(True)
+    ref = oops.elemental_linear(Xo, W.double(), onehot)
+    (ref ** 2).sum().backward()
+    Xg = X.to(dev).clone().requires_grad_(True)
+    Wg = W.to(dev)
+    elem = at.to(torch.int32).to(dev)
+    order, start = ops.group_by_element(elem, Z)
+    assert order is None and start.tolist()[-1] == N
+    out = ops.elemental_linear_forward(Xg, Wg, Wg.transpose(-1, -2).contiguous(), elem)
+    (out ** 2).sum().backward()
+    ops.check_status()
+    assert rel_err(out, ref) < TOL[dtype]["out"]
+    assert rel_err(Xg.grad, Xo.grad) < TOL[dtype]["grad"]
+    # rows of other elements' nodes are not touched by a neighbour's partial box: exact agreement with the gathered path
+    shuffled = torch.randperm(N, generator=g)
+    out_g = ops.elemental_linear_forward(X[shuffled].to(dev), Wg, Wg.transpose(-1, -2).contiguous(), elem[shuffled.to(dev)])
+    assert rel_err(out_g, out.detach()[shuffled.to(dev)]) < (1e-6 if dtype == torch.float32 else 1e-13)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("N,C,Z", [(256, 128, 10), (19, 32, 1), (64, 64, 4),
                                    (4096, 128, 10)])   # last: the benchmark spec's configuration at full size
 def test_symmetric_contraction(dtype, N, C, Z, dev, U):

@@ -173,12 +173,12 @@ def algorithmic_bytes(name, s, N, Ns, E, C, Z):
 # edge kernel grows in proportion to E, so a full launch moves this many bytes times its own E.
 _SRC = "profiles/step_kernels_small_case_f32.txt"
 NCU_TRAFFIC_PER_EDGE = {
-    "cmace_imp_bwd_edge_f32[no gradR]": (2675.0, _SRC),   # mean of a step's two launches (with / without the T array)
-    "cmace_imp_fwd_f32": (2170.0, _SRC),
+    "cmace_imp_bwd_edge_f32[no gradR]": (2622.0, _SRC),   # mean of a step's two launches (with / without the T array)
+    "cmace_imp_fwd_f32": (2173.0, _SRC),
     "cmace_gemm3x_gradr_f32": (409.0, _SRC),
-    "cmace_gemm3x_f32[K=64,N=512]": (2162.0, _SRC),
-    "cmace_radial_hidden_fwd_f32": (925.0, _SRC),
-    "cmace_radial_hidden_bwd_f32": (1126.0, _SRC),
+    "cmace_gemm3x_f32[K=64,N=512]": (2163.0, _SRC),
+    "cmace_radial_hidden_fwd_f32": (920.0, _SRC),
+    "cmace_radial_hidden_bwd_f32": (1060.0, _SRC),
 }
 
 

@@ -1,7 +1,8 @@
 """The entry point for callers that cannot allocate device memory: cmace_imp_bwd_edge_f64_noalloc keeps
 its scratch in an array inside the library, so it is called with inputs and outputs only.  Checked through
-the C-ABI against cmace_imp_bwd_edge_f64 (caller-provided scratch) on two calls in a row, the second with
-different data, so stale contents of the shared array would show.  Collected last on purpose."""
+the C-ABI against cmace_imp_bwd_edge_f64 (caller-provided scratch) and against the oracle's gradients on two calls
+in a row, the second with different data, so stale contents of the shared array would show.  Collected last on
+purpose."""
 import pytest
 import torch
 
@@ -38,6 +39,17 @@ def run_pair(seed, N, deg, C, dev):
     for a, b in zip(*outs):
         assert not torch.isnan(b).any()
         assert rel_err(b, a) < 1e-10  # the float64 tolerance of the other operator tests
+    # and against the oracle's gradients of sum(out * G): dL/dR, dL/dY, and dL/dX = the T rows summed per sender
+    from oracle import ops as oops
+
+    Xo, Yo, Ro = (t.cpu().clone().requires_grad_(True) for t in (X, Y, R))
+    out = oops.invariant_message_passing(Xo, Yo, Ro, send.long(), recv.long(), N)
+    (out * G.cpu()).sum().backward()
+    gradR, gradY, T = outs[1]
+    assert rel_err(gradR.cpu(), Ro.grad) < 1e-10
+    assert rel_err(gradY.cpu(), Yo.grad) < 1e-10
+    gradX = torch.zeros(N, C, dtype=torch.float64).index_add_(0, send.long(), T.cpu())
+    assert rel_err(gradX, Xo.grad) < 1e-10
 
 
 def test_noalloc_entry_point_matches_on_two_calls_in_a_row():

@@ -55,7 +55,6 @@ constexpr int GT_MAX_STAGES = 8;
 constexpr int GT_TILE_M = 128;
 constexpr int GT_KBLOCK = 32;                       // floats per K block = one 128-byte swizzle row
 constexpr int GT_A_SLAB = GT_TILE_M * 128;          // bytes of one A image (hi or lo) per stage
-constexpr int GT_B_SLAB_MAX = 128 * 128;            // bytes of one B image per stage at N tile = 128
 constexpr int GT_PRODUCER_WARPS = 8;                 // 8 measured best (4: 0.47 ms, 8: 0.36 ms, 16: 0.59 ms on the Linear case)
 constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
 constexpr int GT_ROW_STEP = GT_PRODUCER_WARPS * 4;                       // rows between a thread's row segments
@@ -452,7 +451,6 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // (hand-over, MMAs, commit, wake-up) divided by the depth bounds the rate.
     const int q4 = warp & 3, hf = warp >> 2;
     const int r = q4 * 32 + lane;
-    const int p = threadIdx.x;
     const int C = CC ? CC : g.C, ncb = C >> 5;
     const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES;
     const uint32_t g_half = (uint32_t)g.g_stage_bytes / 2u;
@@ -600,15 +598,14 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
     // GT_PREFETCH items ahead of the conversion in a register ring, so that enough bytes are in flight
     // per SM to cover HBM latency (about a microsecond) independently of the shared-memory ring depth.
-    // Without TS: 8 threads cover the 128-byte K-block segment of a row, rows rbase + 32 i.  With TS the residual
-    // image goes to tensor memory, which a warp reaches only for the 32 lanes (= rows) of its quarter: warp (q, hf)
-    // loads rows 32 q .. 32 q + 31, the 64-byte half hf of their segments (4 threads a row, rows (lane >> 2) + 8 i),
-    // writes the raw values to the shared-memory image, and then every lane reads ITS row's half back (all of it
-    // written by this warp) to form the residuals.
-    const int p = threadIdx.x;       // 0..255
-    const int chunk = TS ? 4 * (warp >> 2) + (lane & 3) : (p & 7);   // 16-byte chunk of the 128-byte row segment
-    const int rbase = TS ? 32 * (warp & 3) + (lane >> 2) : (p >> 3); // rows rbase + row_step * i
-    constexpr int row_step = TS ? 8 : GT_ROW_STEP;
+    // (LINEAR always runs as the TS variant.)  The residual image goes to tensor memory, which a warp reaches only
+    // for the 32 lanes (= rows) of its quarter: warp (q, hf) loads rows 32 q .. 32 q + 31, the 64-byte half hf of
+    // their 128-byte K-block segments (4 threads a row, rows (lane >> 2) + 8 i), writes the raw values to the
+    // shared-memory image, and then every lane reads ITS row's half back (all of it written by this warp) to form the
+    // residuals.
+    const int chunk = 4 * (warp >> 2) + (lane & 3);      // 16-byte chunk of the 128-byte row segment
+    const int rbase = 32 * (warp & 3) + (lane >> 2);     // rows rbase + row_step * i
+    constexpr int row_step = 8;
     // head: the next (tile, K block) item whose loads have not been issued yet
     struct Head {
       Tile T;
@@ -625,7 +622,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) head.grow[i] = global_row<MODE>(g, head.T, rbase + row_step * i);
     };
-    // an item in flight only has to remember where its B block lives (-1: no item)
+    // returns -1 when there is no item left (otherwise the index of the item's B block, which the loader warp copies)
     auto issue = [&](float4 (&v)[GT_ROWS_PER_THREAD]) -> int64_t {
       if (!head.valid) return -1;
       const int k0 = head.kb * GT_KBLOCK + chunk * 4;
@@ -642,7 +639,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     int stage = 0;
     uint32_t phase = 0;
     // returns false on a timed-out wait
-    auto commit = [&](int64_t bblock, const float4 (&v)[GT_ROWS_PER_THREAD]) -> bool {
+    auto commit = [&](const float4 (&v)[GT_ROWS_PER_THREAD]) -> bool {
       // lane 0 polls the barrier for the warp
       uint32_t got = 1;
       if (lane == 0) got = mbar_wait(empty_bar + 8 * stage, phase ^ 1) ? 1u : 0u;
@@ -652,64 +649,32 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         return false;
       }
       const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
-      if (TS) {
-        // (the B block of the item is copied by the loader warp into a ring of its own)
-#pragma unroll
-        for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
-          const uint32_t off = (uint32_t)sw128_offset(rbase + row_step * i, chunk);
-          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(v[i].x), "f"(v[i].y), "f"(v[i].z),
-                       "f"(v[i].w)
-                       : "memory");
-        }
-        __syncwarp();
-        const int q = warp & 3, hf = warp >> 2;
-        uint32_t lo[16];
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-          float4 a;
-          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                       : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
-                       : "r"(sA + (uint32_t)sw128_offset(32 * q + lane, 4 * hf + c))
-                       : "memory");
-          lo[4 * c] = __float_as_uint(to_tf32(a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u)));
-          lo[4 * c + 1] = __float_as_uint(to_tf32(a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u)));
-          lo[4 * c + 2] = __float_as_uint(to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u)));
-          lo[4 * c + 3] = __float_as_uint(to_tf32(a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u)));
-        }
-        tmem_st16(lo_ring + 32u * (uint32_t)stage + ((uint32_t)(q * 32) << 16) + 16u * (uint32_t)hf, lo);
-        tmem_st_wait();
-        tc_fence_before();
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar + 8 * stage);
-        if (++stage == GT_STAGES) {
-          stage = 0;
-          phase ^= 1;
-        }
-        return true;
-      }
-      if (p == 0) {
-        const unsigned char *bsrc =
-            reinterpret_cast<const unsigned char *>(g.packed) + bblock * (2 * (int64_t)b_image);
-        mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * b_image);
-        bulk_copy_g2s(sA + 2 * GT_A_SLAB, bsrc, 2 * b_image, full_bar + 8 * stage);
-      }
+      // (the B block of the item is copied by the loader warp into a ring of its own)
 #pragma unroll
       for (int i = 0; i < GT_ROWS_PER_THREAD; i++) {
-        const int r = rbase + GT_ROW_STEP * i;
-        float4 a = v[i], hi, lo;
-        hi.x = to_tf32(a.x); lo.x = to_tf32(a.x - hi.x);
-        hi.y = to_tf32(a.y); lo.y = to_tf32(a.y - hi.y);
-        hi.z = to_tf32(a.z); lo.z = to_tf32(a.z - hi.z);
-        hi.w = to_tf32(a.w); lo.w = to_tf32(a.w - hi.w);
-        const uint32_t off = (uint32_t)sw128_offset(r, chunk);
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(hi.x), "f"(hi.y), "f"(hi.z),
-                     "f"(hi.w)
-                     : "memory");
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + GT_A_SLAB + off), "f"(lo.x), "f"(lo.y),
-                     "f"(lo.z), "f"(lo.w)
+        const uint32_t off = (uint32_t)sw128_offset(rbase + row_step * i, chunk);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sA + off), "f"(v[i].x), "f"(v[i].y), "f"(v[i].z),
+                     "f"(v[i].w)
                      : "memory");
       }
+      __syncwarp();
+      const int q = warp & 3, hf = warp >> 2;
+      uint32_t lo[16];
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        float4 a;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
+                     : "r"(sA + (uint32_t)sw128_offset(32 * q + lane, 4 * hf + c))
+                     : "memory");
+        lo[4 * c] = __float_as_uint(to_tf32(a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u)));
+        lo[4 * c + 1] = __float_as_uint(to_tf32(a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u)));
+        lo[4 * c + 2] = __float_as_uint(to_tf32(a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u)));
+        lo[4 * c + 3] = __float_as_uint(to_tf32(a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u)));
+      }
+      tmem_st16(lo_ring + 32u * (uint32_t)stage + ((uint32_t)(q * 32) << 16) + 16u * (uint32_t)hf, lo);
+      tmem_st_wait();
+      tc_fence_before();
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(full_bar + 8 * stage);
@@ -731,7 +696,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     for (bool run = true; run;) {
 #pragma unroll
       for (int d = 0; d < GT_PREFETCH; d++) {
-        if (inflight[d] < 0 || !commit(inflight[d], buf[d])) {
+        if (inflight[d] < 0 || !commit(buf[d])) {
           run = false;
           break;
         }
@@ -1191,24 +1156,16 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           for (int h16 = 0; h16 < 32; h16 += 16) {
             const int cc = c0 + h16;
             if (cc >= ncols) break;  // warp-uniform
-            uint32_t v[16], w[16];
-            tmem_ld16_nowait(taddr + cc, v);             // Ahi*Bhi + Alo*Bhi (ONE_ACC: all three terms)
-            if (ONE_ACC) {
-#pragma unroll
-              for (int i = 0; i < 16; i++) w[i] = 0u;
-            } else {
-              tmem_ld16_nowait(taddr + g.npad + cc, w);  // Ahi*Blo
-            }
+            uint32_t v[16];
+            tmem_ld16_nowait(taddr + cc, v);             // all three product terms share these columns
             tmem_ld_wait();
             // lane = row: write the row's 16 values, then read back 8 rows x 64 bytes per instruction
             float *mine = ep_buf + lane * GT_EP_STRIDE;
   #pragma unroll
             for (int i = 0; i < 16; i += 4)
               *reinterpret_cast<float4 *>(mine + i) =
-                  make_float4((__uint_as_float(v[i]) + __uint_as_float(w[i])) * g.scale,
-                              (__uint_as_float(v[i + 1]) + __uint_as_float(w[i + 1])) * g.scale,
-                              (__uint_as_float(v[i + 2]) + __uint_as_float(w[i + 2])) * g.scale,
-                              (__uint_as_float(v[i + 3]) + __uint_as_float(w[i + 3])) * g.scale);
+                  make_float4(__uint_as_float(v[i]) * g.scale, __uint_as_float(v[i + 1]) * g.scale,
+                              __uint_as_float(v[i + 2]) * g.scale, __uint_as_float(v[i + 3]) * g.scale);
             __syncwarp();
             const bool col_ok = cc + (lane & 3) * 4 < ncols;
   #pragma unroll
@@ -1386,7 +1343,10 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   g.a_lo_tmem = ((g.mode == GT_MODE_PLAIN && ts_slots >= 4) || g.mode == GT_MODE_GRADR) ? 1 : 0;
   // LINEAR: one set of accumulator columns for the three terms, so two accumulators take 2 npad columns
   const int lin_ts_slots = (GT_TMEM_COLS - 2 * g.npad) / 32;
-  if (g.mode == GT_MODE_LINEAR && lin_ts_slots >= 3) g.a_lo_tmem = 1;
+  if (g.mode == GT_MODE_LINEAR) {
+    if (lin_ts_slots < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
+    g.a_lo_tmem = 1;
+  }
   // rows by TMA when the nodes of every problem are consecutive in storage (no gather list)
   g.lin_tma = (g.mode == GT_MODE_LINEAR && g.a_lo_tmem && g.node_order == nullptr) ? 1 : 0;
   if (g.mode == GT_MODE_GRADR && ts_slots < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
@@ -1456,8 +1416,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   if (g.ep_tma) {
     if (int rc = encode_out_tensor_map(&tmap_out, g.out, g.M, g.N, what)) return rc;
   }
-  auto kern = g.mode == GT_MODE_LINEAR ? (g.a_lo_tmem ? gemm3x_tf32_kernel<GT_MODE_LINEAR, true>
-                                                      : gemm3x_tf32_kernel<GT_MODE_LINEAR>)
+  auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<GT_MODE_LINEAR, true>
               : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<GT_MODE_GRADR, true, 128>
                                                        : gemm3x_tf32_kernel<GT_MODE_GRADR, true>)
               : g.a_lo_tmem            ? gemm3x_tf32_kernel<GT_MODE_PLAIN, true>

@@ -267,8 +267,11 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 // for; this takes the image's 16 KB store and its 16 KB read by the tensor core out of every pipeline item.  Needs
 // room in tensor memory next to the accumulators: two accumulators of 2 npad columns + 32 columns per ring slot.
 // CC: compile-time channel count of the GRADR producers (0: read it from the arguments)
-template <int MODE, bool TS = false, int CC = 0>
-__global__ void __launch_bounds__(GT_THREADS, 1)
+// EW: epilogue warps, 8 (two per tensor-memory lane quarter, alternate 32-column chunks) or 4.  GRADR runs with 4:
+// its narrow output leaves the epilogue idle most of the time, and 14 warps instead of 18 give every thread 128
+// registers instead of 96, which is what its producer warps were short of (2.73 -> 2.35 ms).
+template <int MODE, bool TS = false, int CC = 0, int EW = GT_EPILOGUE_WARPS>
+__global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap,
                        const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ LinMaps lin_maps) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -303,7 +306,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(acc_full + 8 * a, 1);         // one tcgen05.commit
-      mbar_init(acc_empty + 8 * a, GT_EPILOGUE_WARPS);  // one arrival per epilogue warp
+      mbar_init(acc_empty + 8 * a, EW);  // one arrival per epilogue warp
     }
     mbar_init(b_full, 1);
     for (int b2 = 0; b2 < 2; b2++) {
@@ -703,7 +706,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         inflight[d] = issue(buf[d]);
       }
     }
-  } else if (warp == GT_LOADER_WARP) {
+  } else if (warp == GT_PRODUCER_WARPS + 1 + EW) {
     // ================================ loader ================================
     // PLAIN row map only.  Per pipeline item one thread starts two asynchronous copies that complete on the
     // stage's barrier: the TMA tile load of A (128 rows x 32 columns, 128-byte swizzle, zeros outside the
@@ -1024,7 +1027,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         // stores per thread) and one thread hands the buffer to the copy engine, which clips rows and columns
         // outside the matrix.
         const uint32_t stg = smem_base + GT_STAGES * GT_STAGE_BYTES + (uint32_t)(warp - (GT_PRODUCER_WARPS + 1)) * 4096u;
-        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+        for (int c0 = half * 32; c0 < ncols; c0 += 8 * EW) {
           if (lane == 0) tma_store_wait_read();   // the previous store has left the staging buffer
           __syncwarp();
 #pragma unroll
@@ -1057,7 +1060,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         // lane writes whole 32-byte sectors.  Shared memory is the scarce resource of this kernel (at the TF32
         // rate the tensor core's own operand reads take most of its 128 bytes per clock): [E,64]x[64,512] went
         // from 1.98 to 1.79 ms.  With gathered rows (LINEAR) it measured the same as the staged version below.
-        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+        for (int c0 = half * 32; c0 < ncols; c0 += 8 * EW) {
 #pragma unroll
           for (int hr = 0; hr < 2; hr++) {
             uint32_t v[16], w[16];
@@ -1109,7 +1112,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
         // lie outside the array) is stored row by row from registers instead: one such tile per problem.
         const int node_q = (int)(T.node0 + q * T.nq);
         const bool whole = node_q + T.nq <= T.node_end;
-        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+        for (int c0 = half * 32; c0 < ncols; c0 += 8 * EW) {
 #pragma unroll
           for (int h16 = 0; h16 < 2; h16++) {
             const int cc = c0 + 16 * h16;
@@ -1151,7 +1154,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1)
           const int64_t gr = __shfl_sync(0xffffffffu, grow, it * 8 + (lane >> 2));
           rowptr[it] = gr >= 0 ? g.out + gr * g.N + n0 + (lane & 3) * 4 : nullptr;
         }
-        for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+        for (int c0 = half * 32; c0 < ncols; c0 += 8 * EW) {
   #pragma unroll
           for (int h16 = 0; h16 < 32; h16 += 16) {
             const int cc = c0 + h16;
@@ -1417,8 +1420,8 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     if (int rc = encode_out_tensor_map(&tmap_out, g.out, g.M, g.N, what)) return rc;
   }
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<GT_MODE_LINEAR, true>
-              : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<GT_MODE_GRADR, true, 128>
-                                                       : gemm3x_tf32_kernel<GT_MODE_GRADR, true>)
+              : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<GT_MODE_GRADR, true, 128, 4>
+                                                       : gemm3x_tf32_kernel<GT_MODE_GRADR, true, 0, 4>)
               : g.a_lo_tmem            ? gemm3x_tf32_kernel<GT_MODE_PLAIN, true>
                                        : gemm3x_tf32_kernel<GT_MODE_PLAIN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1434,7 +1437,8 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     g.total_tiles = ((row_tiles + per_col - 1) / per_col) * blocks;
   }
   if (blocks < 1) return CMACE_OK;
-  kern<<<(unsigned)blocks, GT_THREADS, smem, st>>>(g, tmap, tmap_out, lin_maps);
+  const int nthreads = g.mode == GT_MODE_GRADR ? (GT_PRODUCER_WARPS + 1 + 4 + 1) * 32 : GT_THREADS;
+  kern<<<(unsigned)blocks, nthreads, smem, st>>>(g, tmap, tmap_out, lin_maps);
   return check_launch(what);
 }
 

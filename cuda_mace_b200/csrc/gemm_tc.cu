@@ -267,10 +267,13 @@ __device__ __forceinline__ void report(const GemmArgs &g, int code) {
 // for; this takes the image's 16 KB store and its 16 KB read by the tensor core out of every pipeline item.  Needs
 // room in tensor memory next to the accumulators: two accumulators of 2 npad columns + 32 columns per ring slot.
 // CC: compile-time channel count of the GRADR producers (0: read it from the arguments)
+// OA: PLAIN with the three product terms in ONE set of accumulator columns (three MMAs per K step instead of two on a
+// double-width B operand): two accumulators then take 2 npad columns, which leaves room for the residual images of a
+// 128-column tile in tensor memory; [E,64]x[64,512] went from 1.49 to 1.37 ms with it.
 // EW: epilogue warps, 8 (two per tensor-memory lane quarter, alternate 32-column chunks) or 4.  GRADR runs with 4:
 // its narrow output leaves the epilogue idle most of the time, and 14 warps instead of 18 give every thread 128
 // registers instead of 96, which is what its producer warps were short of (2.73 -> 2.35 ms).
-template <int MODE, bool TS = false, int CC = 0, int EW = GT_EPILOGUE_WARPS>
+template <int MODE, bool TS = false, int CC = 0, int EW = GT_EPILOGUE_WARPS, bool OA = false>
 __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
     gemm3x_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap tmap,
                        const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ LinMaps lin_maps) {
@@ -327,7 +330,7 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
   // tensor-memory columns between the accumulators; TS: ring of residual images behind them, 32 columns a slot
   // LINEAR with TS: the three product terms share one set of npad columns (ONE_ACC), which leaves room for the ring
   // of residual images next to two accumulators of 128 columns
-  constexpr bool ONE_ACC = MODE == GT_MODE_LINEAR && TS;
+  constexpr bool ONE_ACC = (MODE == GT_MODE_LINEAR && TS) || OA;
   const uint32_t acc_stride = ONE_ACC ? (uint32_t)g.npad : (TS ? 2u * (uint32_t)g.npad : 256u);
   const uint32_t lo_ring = tmem_base + (ONE_ACC ? 2u : 4u) * (uint32_t)g.npad;
   const int items = k_blocks;                                     // pipeline items per tile
@@ -931,7 +934,7 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
           // step (j * 32 bytes = 2 address units); the high word is a constant.  This thread shares its scheduler
           // with busy warps, so every instruction between two MMAs costs issue latency: the low words advance with
           // one add per item, the eight MMAs go back to back.
-          const uint32_t b_lo32 = (MODE == GT_MODE_GRADR || ONE_ACC) ? bb_first + (uint32_t)stage * bres_step
+          const uint32_t b_lo32 = (MODE == GT_MODE_GRADR || MODE == GT_MODE_LINEAR) ? bb_first + (uint32_t)stage * bres_step
                                   : g.b_resident      ? bres_lo32 + (uint32_t)kb * bres_step
                                                       : b_ring_lo32;
           uint64_t ah[4], al[4], bh[4];
@@ -1035,7 +1038,12 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
           for (int h16 = 0; h16 < 2; h16++) {
             uint32_t v[16], w[16];
             tmem_ld16_nowait(taddr + (uint32_t)(c0 + 16 * h16), v);
-            tmem_ld16_nowait(taddr + (uint32_t)(g.npad + c0 + 16 * h16), w);
+            if (OA) {
+#pragma unroll
+              for (int i = 0; i < 16; i++) w[i] = 0u;
+            } else {
+              tmem_ld16_nowait(taddr + (uint32_t)(g.npad + c0 + 16 * h16), w);
+            }
             tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 4; c++) {
@@ -1345,6 +1353,11 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   // residual image of A in tensor memory when at least four ring slots fit next to the two accumulators
   const int ts_slots = (GT_TMEM_COLS - 4 * g.npad) / 32;
   g.a_lo_tmem = ((g.mode == GT_MODE_PLAIN && ts_slots >= 4) || g.mode == GT_MODE_GRADR) ? 1 : 0;
+  // PLAIN, full K blocks, wide output: one set of accumulator columns for the three terms leaves tensor memory for the
+  // residual images where two sets would not
+  const int oa_slots = (GT_TMEM_COLS - 2 * g.npad) / 32;
+  const bool one_acc = g.mode == GT_MODE_PLAIN && !g.a_lo_tmem && g.K % GT_KBLOCK == 0 && g.N >= 32 && oa_slots >= 4;
+  if (one_acc) g.a_lo_tmem = 1;
   // LINEAR: one set of accumulator columns for the three terms, so two accumulators take 2 npad columns
   const int lin_ts_slots = (GT_TMEM_COLS - 2 * g.npad) / 32;
   if (g.mode == GT_MODE_LINEAR) {
@@ -1365,7 +1378,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   const int budget = GT_SMEM_BUDGET - (g.mode == GT_MODE_LINEAR ? (int)sizeof(ProblemTable) + 1024 : 0);
   g.stages = (budget - ep_bytes - 1024 - g.b_resident) / g.stage_bytes;
   if (g.stages > GT_MAX_STAGES) g.stages = GT_MAX_STAGES;
-  if (g.a_lo_tmem && g.mode != GT_MODE_LINEAR && g.stages > ts_slots) g.stages = ts_slots;
+  if (g.a_lo_tmem && g.mode != GT_MODE_LINEAR && g.stages > (one_acc ? oa_slots : ts_slots)) g.stages = one_acc ? oa_slots : ts_slots;
   g.g_stage_bytes = 0;
   if (g.mode == GT_MODE_LINEAR && g.a_lo_tmem) {
     // ring of A images (raw values only, 16 KB a slot), the epilogue's transpose buffers behind it, then a ring of B
@@ -1423,6 +1436,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   auto kern = g.mode == GT_MODE_LINEAR ? gemm3x_tf32_kernel<GT_MODE_LINEAR, true>
               : g.mode == GT_MODE_GRADR ? (g.C == 128 ? gemm3x_tf32_kernel<GT_MODE_GRADR, true, 128, 4>
                                                        : gemm3x_tf32_kernel<GT_MODE_GRADR, true, 0, 4>)
+              : one_acc                ? gemm3x_tf32_kernel<GT_MODE_PLAIN, true, 0, GT_EPILOGUE_WARPS, true>
               : g.a_lo_tmem            ? gemm3x_tf32_kernel<GT_MODE_PLAIN, true>
                                        : gemm3x_tf32_kernel<GT_MODE_PLAIN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

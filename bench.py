@@ -175,7 +175,7 @@ _SRC = "profiles/step_kernels_small_case_f32.txt"
 NCU_TRAFFIC_PER_EDGE = {
     "cmace_imp_bwd_edge_f32[no gradR]": (2622.0, _SRC),   # mean of a step's two launches (with / without the T array)
     "cmace_imp_fwd_f32": (2173.0, _SRC),
-    "cmace_gemm3x_gradr_f32": (409.0, _SRC),
+    "cmace_gemm3x_gradr_f32": (402.0, _SRC),
     "cmace_gemm3x_f32[K=64,N=512]": (2163.0, _SRC),
     "cmace_radial_hidden_fwd_f32": (920.0, _SRC),
     "cmace_radial_hidden_bwd_f32": (1060.0, _SRC),

@@ -15,14 +15,11 @@
 // One CTA per SM, two independent groups of eight warps; the weights (80 KB forward, 72 KB backward) are loaded
 // into shared memory once.  A tile's layers form a chain: elementwise phase, hand-over, MMAs, completion,
 // accumulator load, next elementwise phase; the fixed latencies of that chain are longer than the arithmetic.
-// Forward: every group keeps TWO 128-edge tiles in flight and alternates between them, so one tile's
-// elementwise phase runs while the other tile's products are on the tensor core; a warp of its own issues each
-// group's MMAs, so no elementwise warp is held up by the issue.  Four tiles per SM need four operand buffers: the
-// raw values (= hi image) of the 64 activations go to shared memory (32 KB a tile), their residual image to
-// tensor memory, from where the third product term reads its A operand.
-// Backward: a group works on one tile at a time (write A, barrier, one thread issues the MMAs, everybody waits
-// for their completion, read the accumulator); while one group waits for the tensor core the other one does
-// its elementwise phase.
+// Both kernels: every group keeps TWO 128-edge tiles in flight and alternates between them, so one tile's
+// elementwise phase runs while the other tile's products are on the tensor core.  Four tiles per SM need four
+// operand buffers: the raw values (= hi image) of the 64 activations go to shared memory (32 KB a tile), their
+// residual image to tensor memory, from where the third product term reads its A operand.  The first thread of
+// a group issues its MMAs after the group's barrier: 16 warps per CTA keep the register limit at 128 per thread.
 // Every mbarrier wait is bounded: on a time-out the role records a code in *status and leaves its loop.
 #include <cstring>
 
@@ -38,7 +35,6 @@ constexpr int RH_THREADS = 2 * RH_GROUP_THREADS;
 constexpr int RH_A_SLAB = RH_TILE * 128;    // one image (hi or lo) of one 32-column K block: 16 KB
 constexpr int RH_W_SMALL = 2 * 64 * 128;    // packed [nb <= 32, 64]: one K block, hi + lo images of 64 rows
 constexpr int RH_W_BIG = 2 * RH_W_SMALL;    // packed [64, 64]: two K blocks
-constexpr int RF_THREADS = RH_THREADS + 64;   // + one MMA-issuing warp per group
 constexpr int RF_SLOT_BYTES = 2 * RH_A_SLAB;  // operand buffer of a tile in flight: raw images of two K blocks
                                               // (first layer: raw and residual image of the basis)
 constexpr int RF_TMEM_SLOT = 128;             // tensor-memory columns of a tile in flight: 64 accumulator + 64 residual
@@ -140,30 +136,24 @@ __device__ __forceinline__ void issue_tile_layer(uint32_t acc, uint32_t lo_tmem,
 // NI: 16-byte chunks of the basis a thread carries per tile (256 threads x NI chunks cover 128 rows of nb floats:
 // 1 for nb = 8, 4 up to nb = 32)
 template <int NI>
-__global__ void __launch_bounds__(RF_THREADS, 1)
+__global__ void __launch_bounds__(RH_THREADS, 1)
     radial_hidden_fwd_kernel(const RadialArgs g, const __grid_constant__ CUtensorMap out_map) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[9];   // weights; ready[group][slot]; done[group][slot]
+  __shared__ __align__(8) uint64_t bars[5];   // weights; done[group][slot]
   __shared__ uint32_t tmem_base_slot;
 
   const uint32_t smem_base = (smem_u32(smem) + 1023u) & ~1023u;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool mma_role = warp >= 16;
-  const int group = mma_role ? warp - 16 : warp >> 3;
+  const int group = warp >> 3;
   const uint32_t wbar = smem_u32(&bars[0]);
-  const uint32_t ready0 = wbar + 8u * (1 + 2 * group);   // + 8 * slot
-  const uint32_t done0 = wbar + 8u * (5 + 2 * group);
+  const uint32_t done0 = wbar + 8u * (1 + 2 * group);   // + 8 * slot
 
   const uint32_t w_bytes[3] = {(uint32_t)RH_W_SMALL, (uint32_t)RH_W_BIG, (uint32_t)RH_W_BIG};
   const uint32_t sW[3] = {smem_base, smem_base + w_bytes[0], smem_base + w_bytes[0] + w_bytes[1]};
   const uint32_t sA0 = smem_base + w_bytes[0] + w_bytes[1] + w_bytes[2] + (uint32_t)(2 * group) * RF_SLOT_BYTES;
 
   if (tid == 0) {
-    mbar_init(wbar, 1);
-    for (int i = 0; i < 4; i++) {
-      mbar_init(wbar + 8u * (1 + i), 8);   // ready: one arrival per elementwise warp of the group
-      mbar_init(wbar + 8u * (5 + i), 1);   // done: the commit of the layer's MMAs
-    }
+    for (int i = 0; i < 5; i++) mbar_init(wbar + 8u * i, 1);   // weights; done: the commit of a layer's MMAs
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) tmem_alloc(smem_u32(&tmem_base_slot), RF_TMEM_COLS);
@@ -189,29 +179,7 @@ __global__ void __launch_bounds__(RF_THREADS, 1)
   const int64_t step = (int64_t)gridDim.x * 2;
   const int64_t first = (int64_t)blockIdx.x * 2 + group;
 
-  if (mma_role) {
-    if (lane == 0) {
-      uint32_t phase = 0;   // both slots' ready barriers complete once per layer: one parity bit serves them
-      for (int64_t t0 = first; ok && t0 < ntiles; t0 += 2 * step) {
-        const int nslots = t0 + step < ntiles ? 2 : 1;
-        for (int layer = 0; ok && layer < 3; layer++) {
-          for (int s = 0; s < nslots; s++) {
-            if (!mbar_wait(ready0 + 8u * s, phase)) {
-              if (g.status) atomicCAS(g.status, 0, 13);
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint32_t acc = tmem0 + (uint32_t)s * RF_TMEM_SLOT;
-            issue_tile_layer(acc, acc + 64u, sA0 + (uint32_t)s * RF_SLOT_BYTES, sW[layer], layer == 0, g.nb, RH_H);
-            umma_commit(done0 + 8u * s);
-          }
-          phase ^= 1;
-        }
-        // a lone last tile leaves slot 1's barriers untouched, and it is the last thing this group does
-      }
-    }
-  } else {
+  {
     const int gw = warp & 7, gtid = tid & (RH_GROUP_THREADS - 1);
     const int q = gw & 3, h = gw >> 2;      // tensor-memory lane quarter, column half (= K block of the next layer)
     const int r = q * 32 + lane;            // row of the tile this thread owns in the elementwise phases
@@ -233,6 +201,19 @@ __global__ void __launch_bounds__(RF_THREADS, 1)
     };
     load_basis(first, pre[0]);
     load_basis(first + step, pre[1]);
+    // the whole group has written its part of an operand: its first thread issues the layer's products.  (A warp of
+    // its own for the issue made the CTA 18 warps and the register limit 96; with 16 warps and 128 registers the
+    // kernel is 9 % faster although the issuing thread's warp is held up.)
+    auto hand_over = [&](int s, int layer) {
+      fence_proxy_async();
+      group_sync(group);
+      if (gtid == 0) {
+        tc_fence_after();
+        const uint32_t acc0 = tmem0 + (uint32_t)s * RF_TMEM_SLOT;
+        issue_tile_layer(acc0, acc0 + 64u, sA0 + (uint32_t)s * RF_SLOT_BYTES, sW[layer], layer == 0, g.nb, RH_H);
+        umma_commit(done0 + 8u * s);
+      }
+    };
 
     for (int64_t t0 = first; ok && t0 < ntiles; t0 += 2 * step) {
       const int nslots = t0 + step < ntiles ? 2 : 1;
@@ -253,9 +234,7 @@ __global__ void __launch_bounds__(RF_THREADS, 1)
             if (rr < RH_TILE) store_split(sA + (uint32_t)sw128_offset(rr, c), pre[s][i]);
           }
           tc_fence_before();      // orders this warp's accumulator loads of the previous pass before the new MMAs
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(ready0 + 8u * s);
+          hand_over(s, 0);
         }
       }
       for (int layer = 0; ok && layer < 3; layer++) {
@@ -311,9 +290,7 @@ __global__ void __launch_bounds__(RF_THREADS, 1)
               if (layer < 2) {
                 tmem_st_wait();
                 tc_fence_before();
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(ready0 + 8u * s);
+                hand_over(s, layer + 1);
               } else {
                 // h3 [128, 64] of the tile: two 32-column boxes, rows past the end of the array are clipped
                 fence_proxy_async();
@@ -584,7 +561,7 @@ static int radial_launch(RadialArgs &g, bool backward, const char *what, cudaStr
     auto kern = g.nb == 8 ? radial_hidden_fwd_kernel<1> : radial_hidden_fwd_kernel<4>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(CMACE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
-    kern<<<(unsigned)blocks, RF_THREADS, smem, st>>>(g, map);
+    kern<<<(unsigned)blocks, RH_THREADS, smem, st>>>(g, map);
   }
   return check_launch(what);
 }

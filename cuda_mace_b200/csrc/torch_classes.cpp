@@ -217,6 +217,40 @@ Tensor packed_weights(const Tensor &Bt) {
   return packed;
 }
 
+// Element grouping of a one-hot node attribute matrix [nnodes, Z], cached per tensor (it is the same tensor for every
+// layer and every step of a model): node_order [nnodes] (empty when the nodes are already stored grouped by element,
+// which lets the float32 kernel move whole-node boxes by TMA) and elem_start [Z + 1].  The first call for a tensor
+// reads one flag back from the device; the entry keeps the source alive like the weight cache does.
+struct GroupEntry {
+  Tensor source, order, start;
+};
+
+GroupEntry element_grouping(const Tensor &one_hot) {
+  static std::mutex m;
+  using Key = std::tuple<void *, int64_t, int, std::vector<int64_t>>;
+  static std::map<Key, GroupEntry> cache;
+  const Key key = std::make_tuple(one_hot.data_ptr(), (int64_t)one_hot._version(), (int)one_hot.device().index(),
+                                  one_hot.sizes().vec());
+  std::lock_guard<std::mutex> lock(m);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 16) cache.clear();
+  const int64_t N = one_hot.size(0), Z = one_hot.size(1);
+  Tensor elem = one_hot.argmax(1).to(torch::kInt32).contiguous();
+  const int64_t nbytes = cmace_sender_order_workspace_bytes(N);
+  Tensor ws = torch::empty({std::max<int64_t>(nbytes, 1)}, elem.options().dtype(torch::kUInt8));
+  Tensor order = torch::empty({std::max<int64_t>(N, 1)}, elem.options());
+  Tensor start = torch::empty({Z + 1}, elem.options());
+  check(cmace_group_by_element(elem.data_ptr<int32_t>(), N, (int)Z, order.data_ptr<int32_t>(),
+                               start.data_ptr<int32_t>(), ws.data_ptr(), nbytes, stream_of(elem)),
+        "cmace_group_by_element");
+  if (N > 1 && elem.slice(0, 1, N).ge(elem.slice(0, 0, N - 1)).all().item<bool>())
+    order = torch::empty({0}, elem.options());
+  GroupEntry e{one_hot, order, start};
+  cache.emplace(key, e);
+  return e;
+}
+
 // out = scale * X @ W[z, l] per row; Wt is the transposed copy of W
 Tensor linear_call(const Tensor &Xin, const Tensor &W, const Tensor &Wt, const Tensor &node_order,
                    const Tensor &elem_start, int64_t nelements, double scale) {
@@ -512,15 +546,8 @@ class ElementalLinear : public torch::CustomClassHolder {
       Tensor none = torch::empty({0}, torch::dtype(torch::kInt32).device(X.device()));
       return LinearAutograd::apply(X, W, W_T, none, none, 1);
     }
-    Tensor elem = one_hot_encoding.argmax(1).to(torch::kInt32).contiguous();
-    const int64_t nbytes = cmace_sender_order_workspace_bytes(N);
-    Tensor ws = torch::empty({std::max<int64_t>(nbytes, 1)}, elem.options().dtype(torch::kUInt8));
-    Tensor order = torch::empty({std::max<int64_t>(N, 1)}, elem.options());
-    Tensor start = torch::empty({Z + 1}, elem.options());
-    check(cmace_group_by_element(elem.data_ptr<int32_t>(), N, (int)Z, order.data_ptr<int32_t>(),
-                                 start.data_ptr<int32_t>(), ws.data_ptr(), nbytes, stream_of(elem)),
-          "cmace_group_by_element");
-    return LinearAutograd::apply(X, W, W_T, order, start, Z);
+    const GroupEntry grouping = element_grouping(one_hot_encoding);
+    return LinearAutograd::apply(X, W, W_T, grouping.order, grouping.start, Z);
   }
   std::vector<Tensor> __getstate__() { return {}; }
   void __setstate__(const std::vector<Tensor> &) {}

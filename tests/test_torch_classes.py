@@ -268,6 +268,45 @@ def test_elemental_linear_class_single_species(classes, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+def test_elemental_linear_class_on_grouped_and_on_shuffled_nodes(classes, dtype):
+    """The class caches the element grouping of a one-hot matrix and passes no gather list when the nodes are stored
+    grouped by element (whole-node boxes by TMA in float32); the same nodes in random order take the gather list.
+    Both against the oracle, twice in a row with the same one-hot tensor (second call: cached grouping), and once
+    more after the tensor was edited in place (the cache must not serve the old grouping)."""
+    from oracle import ops as oops
+    from cuda_mace_b200 import systems
+
+    tol = 1e-10 if dtype == torch.float64 else 1e-4
+    g = torch.Generator().manual_seed(21)
+    N, K, Z = 700, 128, 4
+    X = torch.randn(N, 16, K, generator=g, dtype=torch.float64).to(dtype)
+    WZ = torch.randn(Z, 4, K, K, generator=g, dtype=torch.float64).to(dtype)
+    Wg, WTg = WZ.cuda(), WZ.transpose(-1, -2).contiguous().cuda()
+    at_sorted = torch.sort(torch.randint(0, Z, (N,), generator=g)).values
+    for at in (at_sorted, at_sorted[torch.randperm(N, generator=g)]):
+        one_hot = systems.one_hot(at, Z).to(dtype)
+        Xo = X.double().clone().requires_grad_(True)
+        ref = oops.elemental_linear(Xo, WZ.double(), one_hot.double())
+        (ref ** 2).sum().backward()
+        oh = one_hot.cuda()
+        for _ in range(2):
+            Xg = X.cuda().requires_grad_(True)
+            out = classes.linear_wmma.ElementalLinear().forward(Xg, Wg, WTg, oh)
+            (out ** 2).sum().backward()
+            assert rel_err(out, ref) < tol and rel_err(Xg.grad, Xo.grad) < tol
+        # in-place edit: node 0 moves to the last element
+        oh[0] = 0.0
+        oh[0, Z - 1] = 1.0
+        at2 = at.clone()
+        at2[0] = Z - 1
+        ref2 = oops.elemental_linear(X.double(), WZ.double(), systems.one_hot(at2, Z).double())
+        out2 = classes.linear_wmma.ElementalLinear().forward(X.cuda(), Wg, WTg, oh)
+        assert rel_err(out2, ref2) < tol
+    assert int(torch.ops.cmace_b200_internal.check_status()) == 0
+
+
+@pytest.mark.gpu
 def test_keyword_call_and_status_op(classes):
     """A keyword call with the reference's argument names (including its spelling "raidal"), and the status
     operator that reports kernels whose bounded waits gave up (0 = none did)."""

@@ -59,7 +59,6 @@ constexpr int GT_PRODUCER_WARPS = 8;                 // 8 measured best (4: 0.47
 constexpr int GT_ROWS_PER_THREAD = GT_TILE_M / (GT_PRODUCER_WARPS * 4);  // 8 threads cover one row segment
 constexpr int GT_ROW_STEP = GT_PRODUCER_WARPS * 4;                       // rows between a thread's row segments
 constexpr int GT_EPILOGUE_WARPS = 8;
-constexpr int GT_LOADER_WARP = GT_PRODUCER_WARPS + 1 + GT_EPILOGUE_WARPS;  // warp that starts the asynchronous copies
 constexpr int GT_THREADS = (GT_PRODUCER_WARPS + 1 + GT_EPILOGUE_WARPS + 1) * 32;
 constexpr int GT_SMEM_BUDGET = 227 * 1024 - 2048;    // dynamic shared memory (the static barriers count against the same 227 KB)
 constexpr int GT_TMEM_COLS = 512;                   // two accumulators of 2 x 128 columns
@@ -441,7 +440,9 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
     }
   } else if (MODE == GT_MODE_GRADR && warp < GT_PRODUCER_WARPS) {
     // ================================ producers, operand formed on the fly ================================
-    // (always the TS variant: raw values are the hi image in shared memory, the residual image goes to tensor memory)
+    // (always the TS variant, and here BOTH images of A go to tensor memory: the raw values as the hi image, the
+    // residual a - trunc(a) as the lo image, 32 columns each per slot.  No shared-memory store, hence no proxy fence
+    // in the hand-over: 2.32 -> 2.20 ms with 128 registers a thread; with 96 it had been slower.)
     // A thread owns one row of the tile = one edge e (the tensor-memory lane its warp may write) and 16 of a K
     // block's 32 columns.  K block (l, cb) covers the columns l*C + 32 cb .. + 31 of A; the items of a tile run
     // cb-outer, l-inner (the order of a sum does not matter to the accumulator, the producer only has to fetch the
@@ -452,18 +453,14 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
     // the G rows of that range (8 KB per receiver at C = 128, one contiguous piece) into one of two shared-memory
     // buffers a tile ahead, and the inner loop reads them from there (warp-wide broadcasts); receivers beyond
     // the staged range, when a tile spans many low-degree receivers, are read from global memory.
-    // The B blocks are copied by the loader warp into a region of their own with the same slot index and barriers as
-    // the A images; the ring is as deep as shared memory allows (five slots), because the round trip of a slot
-    // (hand-over, MMAs, commit, wake-up) divided by the depth bounds the rate.
+    // The B blocks are copied by the loader warp into a ring with the same slot index and barriers as the A images;
+    // four slots: two accumulators of 2 x 64 columns leave 256 tensor-memory columns for the images.
     const int q4 = warp & 3, hf = warp >> 2;
     const int r = q4 * 32 + lane;
     const int C = CC ? CC : g.C, ncb = C >> 5;
     const uint32_t g_stage0 = smem_base + GT_STAGES * GT_STAGE_BYTES;
     const uint32_t g_half = (uint32_t)g.g_stage_bytes / 2u;
     const int max_staged = (int)(g_half / (uint32_t)(16 * C * 4));
-    uint32_t soff[4];
-#pragma unroll
-    for (int c = 0; c < 4; c++) soff[c] = (uint32_t)sw128_offset(r, 4 * hf + c);
     const uint32_t t_lo = lo_ring + ((uint32_t)(q4 * 32) << 16) + 16u * (uint32_t)hf;
     int stage = 0, pending_stage = -1;
     uint32_t phase = 0;
@@ -471,7 +468,6 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
     auto hand_over = [&]() {
       if (pending_stage < 0) return;
       tmem_st_wait();
-      fence_proxy_async();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(full_bar + 8 * pending_stage);
@@ -571,23 +567,23 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
             ok = false;
             break;
           }
-          const uint32_t sA = smem_base + stage * GT_STAGE_BYTES;
           // hi image: the raw values (the tensor core ignores the low 13 mantissa bits of its operands);
           // residual image: a - trunc(a), exact in float32 and at most 2^-10 |a|; it is read with the same truncation,
           // which leaves an error below 2^-20 |a| per element
-          uint32_t lo[16];
+          uint32_t lo[16], hi[16];
 #pragma unroll
           for (int c = 0; c < 4; c++) {
-            asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(sA + soff[c]), "l"(a2[2 * c]), "l"(a2[2 * c + 1]) : "memory");
 #pragma unroll
             for (int h2 = 0; h2 < 2; h2++) {
               unsigned long long d;
               const unsigned long long tr = a2[2 * c + h2] & 0xFFFFE000FFFFE000ull;
               asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a2[2 * c + h2]), "l"(tr));
               asm("mov.b64 {%0, %1}, %2;" : "=r"(lo[4 * c + 2 * h2]), "=r"(lo[4 * c + 2 * h2 + 1]) : "l"(d));
+              asm("mov.b64 {%0, %1}, %2;" : "=r"(hi[4 * c + 2 * h2]), "=r"(hi[4 * c + 2 * h2 + 1]) : "l"(a2[2 * c + h2]));
             }
           }
           tmem_st16(t_lo + 32u * (uint32_t)stage, lo);
+          tmem_st16(t_lo + 32u * (uint32_t)(GT_STAGES + stage), hi);   // the hi ring follows the lo ring
           pending_stage = stage;
           if (++stage == GT_STAGES) {
             stage = 0;
@@ -959,6 +955,13 @@ __global__ void __launch_bounds__((GT_PRODUCER_WARPS + 1 + EW + 1) * 32, 1)
                 umma_tf32_acc(d_tmem, ah[j], bl, idescn);
                 umma_tf32_ts_acc(d_tmem, a_lo_t + 8u * j, bh[j], idescn);
               }
+            }
+          } else if (full_k && MODE == GT_MODE_GRADR) {
+            const uint32_t a_hi_t = a_lo_t + 32u * (uint32_t)GT_STAGES;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              umma_tf32_ts(d_tmem, a_hi_t + 8u * j, bh[j], idesc2, (kb | j) != 0);
+              umma_tf32_ts_acc(d_tmem, a_lo_t + 8u * j, bh[j], idesc1);
             }
           } else if (full_k) {
             umma_tf32(d_tmem, ah[0], bh[0], idesc2, kb != 0);
@@ -1366,7 +1369,7 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
   }
   // rows by TMA when the nodes of every problem are consecutive in storage (no gather list)
   g.lin_tma = (g.mode == GT_MODE_LINEAR && g.a_lo_tmem && g.node_order == nullptr) ? 1 : 0;
-  if (g.mode == GT_MODE_GRADR && ts_slots < 2) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
+  if (g.mode == GT_MODE_GRADR && ts_slots < 4) return fail(CMACE_ERR_UNSUPPORTED, "%s: no room in tensor memory", what);
   g.stage_bytes = (g.a_lo_tmem ? 1 : 2) * GT_A_SLAB + (g.b_resident ? 0 : 2 * g.npad * 128);
   // PLAIN: tile stores by TMA from a 4 KB staging buffer per epilogue warp (N >= 32: the box is 32 columns wide);
   // LINEAR: the transpose buffers of its epilogue
@@ -1391,14 +1394,14 @@ static int gemm_launch(GemmArgs &g, const char *what, cudaStream_t st) {
     g.g_stage_bytes = ep_bytes;   // the kernel finds the B ring behind stages * stage_bytes + g_stage_bytes
   }
   if (g.mode == GT_MODE_GRADR) {
-    // Shared memory: a ring of A images (hi image only, 16 KB a slot), a ring of B blocks of its own, and the G rows
-    // of a tile's receivers twice (the next tile's are copied while this one is consumed).  No epilogue staging
-    // buffers: the narrow output goes from tensor memory to global memory through registers.
+    // Shared memory: a ring of B blocks and the G rows of a tile's receivers twice (the next tile's are copied while
+    // this one is consumed).  No A images (they live in tensor memory) and no epilogue staging buffers (the narrow
+    // output goes from tensor memory to global memory through registers).
     const int per_receiver = 16 * g.C * 4;
     g.ep_tma = 0;
-    g.stage_bytes = GT_A_SLAB;
-    g.stages = 5;
-    g.b_slots = 5;           // the B blocks live in a region of their own but share slot index and barriers with A
+    g.stage_bytes = 0;       // both images of A live in tensor memory: 64 columns a slot
+    g.stages = ts_slots / 2 < 4 ? ts_slots / 2 : 4;
+    g.b_slots = g.stages;    // the B blocks share slot index and barriers with the A images
     int left = budget - 1024 - g.stages * g.stage_bytes - g.b_slots * 2 * g.npad * 128;
     while (g.stages > 2 && left < 2 * 4 * per_receiver) {   // keep room for four receivers per buffer
       g.stages--;

@@ -116,6 +116,17 @@ __device__ __forceinline__ void umma_tf32_ts_acc(uint32_t d_tmem, uint32_t a_tme
       "r"(a_tmem), "l"(bdesc), "r"(idesc)
       : "memory");
 }
+// A operand in tensor memory, with the accumulate flag as an argument
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // registers -> tensor memory: thread t of the warp writes lane (base lane + t), 16 consecutive columns
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(

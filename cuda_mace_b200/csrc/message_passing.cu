@@ -200,8 +200,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 // ring of BS_SLOTS shared-memory slots; one lane starts, BS_SLOTS edges ahead of where the warp computes, a bulk
 // copy of the edge's four R rows (2 KB, contiguous) and of its sender's feature row (512 B) that completes on the
 // slot's mbarrier.  160 KB per SM are then on their way from HBM at any time, independent of registers.
-// The arithmetic per edge is that of imp_bwd_edge_kernel.  Receivers are dealt out cyclically to the warps of a
-// persistent grid; every wait is bounded and sets *stalled when it gives up.  Measured at 64 000 atoms: 3.36 ms with
+// The arithmetic per edge is that of imp_bwd_edge_kernel.  Everything this pass writes is per edge (gradY, T, gradR),
+// so the edge list is cut into equal contiguous pieces, one per warp of a persistent grid, wherever the receiver
+// boundaries fall (a warp reloads G when its edges move on to the next receiver): the warps finish together
+// whatever the degrees are, which matters most for small systems (3 000 atoms: 2 368 warps, 0.139 -> 0.10 ms).
+// Every wait is bounded and sets *stalled when it gives up.  Measured at 64 000 atoms: 3.36 ms with
 // the register-prefetch kernel, 3.38 ms with 8 warps x 8 slots (two warps per scheduler cannot hide the latency of
 // their own instruction chains), 3.06 ms with 16 warps x 4 slots, 3.22 ms with 16 x 5 (the modulo by 5).
 constexpr int BS_WARPS = 16;
@@ -211,25 +214,37 @@ constexpr int BS_R_BYTES = 4 * BS_C * 4;
 constexpr int BS_SLOT_BYTES = BS_R_BYTES + BS_C * 4;
 constexpr long long BS_TIMEOUT_CYCLES = 400000000LL;   // bound of every wait, about 0.2 s
 
+// position in a warp's piece [e, end) of the receiver-sorted edge list: edge e belongs to receiver `node`, whose
+// edges end at e1; e = -1 when the piece is exhausted
 struct EdgeCursor {
-  int64_t node, e, e1;
+  int64_t node, e, e1, end;
 };
 
-__device__ __forceinline__ void cursor_seek(EdgeCursor &c, const int32_t *__restrict__ row_ptr, int64_t nnodes,
-                                            int64_t stride) {
-  while (c.node < nnodes) {
-    c.e = row_ptr[c.node];
-    c.e1 = row_ptr[c.node + 1];
-    if (c.e < c.e1) return;
-    c.node += stride;
+// first = first edge of the piece: the receiver is found by bisection in row_ptr [nnodes + 1]
+__device__ __forceinline__ void cursor_start(EdgeCursor &c, const int32_t *__restrict__ row_ptr, int64_t nnodes,
+                                             int64_t first, int64_t end) {
+  c.end = end;
+  if (first >= end) {
+    c.e = c.e1 = -1;
+    c.node = 0;
+    return;
   }
-  c.e = c.e1 = -1;
+  int64_t lo = 0, hi = nnodes;   // invariant: row_ptr[lo] <= first < row_ptr[hi]
+  while (hi - lo > 1) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (row_ptr[mid] <= first) lo = mid;
+    else hi = mid;
+  }
+  c.node = lo;
+  c.e = first;
+  c.e1 = row_ptr[lo + 1];
 }
-__device__ __forceinline__ void cursor_next(EdgeCursor &c, const int32_t *__restrict__ row_ptr, int64_t nnodes,
-                                            int64_t stride) {
-  if (++c.e < c.e1) return;
-  c.node += stride;
-  cursor_seek(c, row_ptr, nnodes, stride);
+__device__ __forceinline__ void cursor_next(EdgeCursor &c, const int32_t *__restrict__ row_ptr) {
+  if (++c.e >= c.end) {
+    c.e = -1;
+    return;
+  }
+  while (c.e >= c.e1) c.e1 = row_ptr[++c.node + 1];   // receivers without edges are stepped over
 }
 
 // WANT_T / WANT_GR: whether T [E,C] and gradR [E,4,C] are written.  With neither (the first layer of a model whose
@@ -254,22 +269,22 @@ __global__ void __launch_bounds__(BS_WARPS * 32, 1)
   }
   __syncwarp();
 
-  const int64_t stride = (int64_t)gridDim.x * BS_WARPS;
+  const int64_t nwarps = (int64_t)gridDim.x * BS_WARPS, wid = (int64_t)blockIdx.x * BS_WARPS + w;
+  const int64_t per = (nedges + nwarps - 1) / nwarps;
+  const int64_t e_first = wid * per, e_end = e_first + per < nedges ? e_first + per : nedges;
   EdgeCursor ic, cc;   // where copies are issued, where the warp computes
-  ic.node = cc.node = (int64_t)blockIdx.x * BS_WARPS + w;
-  cursor_seek(ic, row_ptr, nnodes, stride);
+  cursor_start(ic, row_ptr, nnodes, e_first, e_end);
   cc = ic;
-  int64_t chunk_base = -1, chunk_node = -1;
+  int64_t chunk_base = -64;
   int snd = 0;
   uint32_t icount = 0, ccount = 0;
 
   auto issue_one = [&]() {
     if (ic.e < 0) return;
     // sender indices of the issue stream, 32 at a time
-    if (ic.node != chunk_node || ic.e >= chunk_base + 32) {
-      chunk_node = ic.node;
+    if (ic.e >= chunk_base + 32) {
       chunk_base = ic.e;
-      snd = (ic.e + lane < ic.e1) ? sender[ic.e + lane] : 0;
+      snd = (ic.e + lane < ic.end) ? sender[ic.e + lane] : 0;
     }
     const int s = __shfl_sync(0xffffffffu, snd, (int)(ic.e - chunk_base));
     if (lane == 0) {
@@ -284,7 +299,7 @@ __global__ void __launch_bounds__(BS_WARPS * 32, 1)
                    : "memory");
     }
     icount++;
-    cursor_next(ic, row_ptr, nnodes, stride);
+    cursor_next(ic, row_ptr);
   };
   for (int i = 0; i < BS_SLOTS; i++) issue_one();
 
@@ -297,7 +312,7 @@ __global__ void __launch_bounds__(BS_WARPS * 32, 1)
   while (cc.e >= 0) {
     const int64_t e = cc.e, node = cc.node;
     EdgeCursor nc = cc;
-    cursor_next(nc, row_ptr, nnodes, stride);
+    cursor_next(nc, row_ptr);
     const float yv = yv_next;
     if (WANT_U && nc.e >= 0) yv_next = __ldg(Y + (int64_t)ylm * nedges + nc.e);
     if (node != g_node) {
@@ -545,7 +560,7 @@ static int imp_bwd_edge(const T *X, const T *Y, const T *R, const T *G, const in
         if (num_sms <= 0) num_sms = 148;
       }
       const size_t smem = (size_t)BS_WARPS * BS_SLOTS * BS_SLOT_BYTES;
-      int64_t blocks = (nnodes + BS_WARPS - 1) / BS_WARPS;
+      int64_t blocks = (nedges + BS_WARPS * 8 - 1) / (BS_WARPS * 8);   // at least a few edges a warp
       blocks = blocks < num_sms ? blocks : num_sms;
       auto launch = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
